@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""SDDMM benchmark: P_ij = S_ij * (A_i . B_j) on seeded synthetic inputs, B200 engine vs host CPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C] [--k K] [--mode fp32|bf16|tf32|fp32_tc]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...      (N > 1: one rank per GPU)
+    python bench.py --impl reference ...      (the reference's own CPU SDDMM on the host cores)
+
+One step = one SDDMM over the whole sparse matrix.  For N > 1 the matrix is cut into
+nnz-balanced row ranges (one per rank), A is row-sliced, B is broadcast once over NCCL
+before the timed region, and no collective runs inside a step (strong scaling: the
+total work is fixed).  Rank 0 prints one JSON line.
+
+  value     GFLOP/s = 2*nnz*K / t with all operands resident in HBM; t = mean device time of a
+            step (CUDA events on the engine's stream around its kernels), max over ranks;
+            L2 is flushed between steps
+  e2e       same metric through upload_csr (pinned host buffers, H2D of S, A, B + device-side
+            plan) -> run -> download (D2H of P.val), host wall clock, max over ranks
+  roofline  algorithmic bytes of the dominant kernel / its mean device time, against the
+            measured HBM copy bandwidth (MEASURED_PEAKS.json) or the 6650 GB/s fallback
+  cpu_baseline  the reference's CPUBasic::run_csr (oracle/_ref, else the oracle port) on the host
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+CONFIG_K = {1: 32, 2: 32, 3: 64, 4: 32, 5: 32}
+CONFIG_NAME = {
+    1: "config1 small-uniform 656^2 nnz 18,964",
+    2: "config2 clustered 64x64 blocks 14,340^2 nnz 18.07M",
+    3: "config3 banded 3x3 blocks 503,712^2 nnz 36.8M",
+    4: "config4 power-law 2,601,977^2 nnz 36.2M",
+    5: "config5 poisson-rows 1,453,908^2 nnz 37.5M",
+}
+DEFAULT_CONFIG = 2
+FALLBACK_HBM_GBS = 6650.0
+L2_FLUSH_BYTES = 512 << 20
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback 6650 GB/s (MEASURED_PEAKS.json absent)"
+
+
+def measured_traffic(kernel, workload_key):
+    """DRAM bytes per launch from the committed ncu capture, if one covers this kernel and workload."""
+    p = ROOT / "profiles" / "dram_traffic.json"
+    if not p.exists():
+        return None
+    try:
+        return json.loads(p.read_text()).get(f"{kernel}:{workload_key}")
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.path = Path(f"/tmp/sddmm_clocks_{os.getpid()}.csv")
+        exe = shutil.which("nvidia-smi")
+        if exe:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen([exe, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(gpu_index),
+                                          "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            out["note"] = "nvidia-smi not found"
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.path.read_text().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); pw.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower() == "active":
+                    reasons.add(n)
+        self.path.unlink(missing_ok=True)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), power_w_max=float(max(pw)), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def pinned_copy(lib, arr):
+    """Copy a numpy array into pinned host memory from the engine library; returns (address, view)."""
+    import ctypes as C
+    p = C.c_void_p()
+    if lib.sddmm_b200_host_alloc(C.byref(p), arr.nbytes):
+        raise RuntimeError("pinned host allocation failed")
+    buf = (C.c_char * max(arr.nbytes, 1)).from_address(p.value)
+    view = np.frombuffer(buf, dtype=arr.dtype, count=arr.size)
+    view[...] = arr.ravel()
+    return p.value, view
+
+
+def cpu_reference(M, N, K, row_ptr, col_idx, s_val, A, B, max_nnz, reps):
+    """Time the reference's CPU SDDMM on a row-prefix sample of the workload (1 thread: it has no threading)."""
+    import oracle_lib
+    r_end = int(np.searchsorted(row_ptr, max_nnz, side="right") - 1) if row_ptr[M] > max_nnz else M
+    r_end = max(1, min(M, r_end))
+    nnz_s = int(row_ptr[r_end])
+    rp = np.ascontiguousarray(row_ptr[:r_end + 1])
+    ref = oracle_lib.Reference.try_load()
+    times = []
+    if ref is not None:
+        kind = "reference"
+        run, result, destroy = ref.problem(r_end, N, K, rp, col_idx[:nnz_s], s_val[:nnz_s], A[:r_end], B)
+        for _ in range(reps):
+            times.append(run() * 1e-9)
+        destroy()
+    else:
+        kind = "port"
+        orc = oracle_lib.Oracle()
+        Ac, Bc = np.ascontiguousarray(A[:r_end]), np.ascontiguousarray(B)
+        out = np.empty(nnz_s, np.float32)
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            orc.sddmm_csr_rows(0, r_end, K, rp, np.ascontiguousarray(col_idx[:nnz_s]), np.ascontiguousarray(s_val[:nnz_s]), Ac, Bc, out)
+            times.append(time.perf_counter() - t0)
+    t = float(np.median(times))
+    return {"value": 2.0 * nnz_s * K / t / 1e9, "unit": "GFLOP/s", "cores": 1, "kind": kind,
+            "sample": f"rows [0,{r_end}) of the workload = {nnz_s} nnz, median of {reps} runs of CPUBasic::run_csr, {t * 1e3:.1f} ms each",
+            "host_cores_available": os.cpu_count()}, t, nnz_s
+
+
+def workload_config(cfg, K, mode, world):
+    return {"workload": f"{CONFIG_NAME[cfg]}, K={K}, A/B uniform [-1,1), seeded synthetic", "config_id": cfg, "k": K,
+            "mode": mode, "partition": f"{world} nnz-balanced row range(s), B replicated", "l2": "flushed between steps (512 MiB write)"}
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    from dphpc_b200 import Dataset
+    cfg, K = args.config, args.k or CONFIG_K[args.config]
+    d = Dataset(cfg, K, args.scale)
+    total = args.steps + args.warmup
+    # bound each step so the whole run stays within a few minutes (CPUBasic does ~1-2 GFLOP/s)
+    budget_nnz = int(max(2e5, min(d.nnz, 150.0 / max(total, 1) * 1.0e9 / (2 * K))))
+    import oracle_lib
+    ref = oracle_lib.Reference.try_load()
+    r_end = int(np.searchsorted(d.row_ptr, budget_nnz, side="right") - 1) if d.nnz > budget_nnz else d.M
+    r_end = max(1, min(d.M, r_end))
+    nnz_s = int(d.row_ptr[r_end])
+    rp = np.ascontiguousarray(d.row_ptr[:r_end + 1])
+    if ref is not None:
+        run, _, destroy = ref.problem(r_end, d.N, K, rp, d.col_idx[:nnz_s], d.s_val[:nnz_s], d.A[:r_end], d.B)
+        step = lambda: run() * 1e-9  # noqa: E731
+    else:
+        orc = oracle_lib.Oracle()
+        Ac, Bc = np.ascontiguousarray(d.A[:r_end]), np.ascontiguousarray(d.B)
+        ci, sv = np.ascontiguousarray(d.col_idx[:nnz_s]), np.ascontiguousarray(d.s_val[:nnz_s])
+        out = np.empty(nnz_s, np.float32)
+
+        def step():
+            t0 = time.perf_counter()
+            orc.sddmm_csr_rows(0, r_end, K, rp, ci, sv, Ac, Bc, out)
+            return time.perf_counter() - t0
+        destroy = lambda: None  # noqa: E731
+    for _ in range(args.warmup):
+        step()
+    ts = [step() for _ in range(args.steps)]
+    destroy()
+    tm = float(np.mean(ts))
+    val = 2.0 * nnz_s * K / tm / 1e9
+    line = {
+        "impl": "reference", "metric": "SDDMM GFLOP/s (2*nnz*K/t)", "value": val, "unit": "GFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": tm * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, K, "fp32", 1),
+        "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": 1, "kind": "reference" if ref is not None else "port",
+                         "sample": f"each step = CPUBasic::run_csr over rows [0,{r_end}) = {nnz_s} of {d.nnz} nnz",
+                         "host_cores_available": os.cpu_count()},
+        "e2e": {"value": val, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def kernel_only_stats(eng, steps, warmup, flush):
+    """(mean ms per step, {kernel: mean ms}) with L2 flushed before every step."""
+    for _ in range(warmup):
+        eng.run(); eng.sync()
+    tot, per = [], {}
+    for _ in range(steps):
+        flush()
+        eng.run(); eng.sync()
+        tot.append(eng.last_run_ms())
+        for name, ms in eng.kernel_times():
+            per.setdefault(name, []).append(ms)
+    return float(np.mean(tot)), {k: float(np.mean(v)) for k, v in per.items()}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--config", type=int, default=DEFAULT_CONFIG, choices=[1, 2, 3, 4, 5])
+    ap.add_argument("--k", type=int, default=0)
+    ap.add_argument("--mode", default="fp32", choices=["fp32", "bf16", "tf32", "fp32_tc"])
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (profiling captures only)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-config table and the CPU baseline")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "engine" and args.scale == 1.0 else args.warmup
+
+    rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch  # device buffers for the L2 flush and the NCCL broadcast only
+    from dphpc_b200 import Dataset, Engine, load_engine_lib
+    from dphpc_b200.partition import row_cuts
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the SDDMM engine has no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    cfg, K = args.config, args.k or CONFIG_K[args.config]
+    d = Dataset(cfg, K, args.scale)
+    cuts = row_cuts(d.row_ptr, world)
+    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+    j0, j1 = int(d.row_ptr[r0]), int(d.row_ptr[r1])
+    rp_local = (d.row_ptr[r0:r1 + 1].astype(np.int64) - j0).astype(np.int32)
+    Mloc, nnz_loc = r1 - r0, j1 - j0
+    if Mloc < 1:
+        raise SystemExit(f"rank {rank}: empty row range; use fewer GPUs for this workload")
+
+    lib = load_engine_lib()
+    eng = Engine(local, args.mode)
+    # pinned host copies of this rank's shard (the buffers a host caller would own)
+    h_rp, _ = pinned_copy(lib, rp_local)
+    h_ci, _ = pinned_copy(lib, d.col_idx[j0:j1])
+    h_sv, _ = pinned_copy(lib, d.s_val[j0:j1])
+    h_A, _ = pinned_copy(lib, d.A[r0:r1])
+    h_B, _ = pinned_copy(lib, d.B)
+    h_P, p_view = pinned_copy(lib, np.zeros(max(nnz_loc, 1), np.float32))
+
+    # ---- resident operands: B broadcast once over NCCL (N > 1), then a device-to-device upload
+    if world > 1:
+        tB = torch.empty((d.N, K), dtype=torch.float32, device="cuda")
+        if rank == 0:
+            tB.copy_(torch.from_numpy(np.ascontiguousarray(d.B)))
+        dist.broadcast(tB, src=0)
+        t_rp = torch.from_numpy(rp_local).cuda()
+        t_ci = torch.from_numpy(np.ascontiguousarray(d.col_idx[j0:j1])).cuda()
+        t_sv = torch.from_numpy(np.ascontiguousarray(d.s_val[j0:j1])).cuda()
+        t_A = torch.from_numpy(np.ascontiguousarray(d.A[r0:r1])).cuda()
+        torch.cuda.synchronize()
+        eng.upload_csr_device(Mloc, d.N, K, nnz_loc, t_rp.data_ptr(), t_ci.data_ptr(), t_sv.data_ptr(), t_A.data_ptr(), tB.data_ptr())
+        del t_rp, t_ci, t_sv, t_A, tB
+    else:
+        eng.upload_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B)
+    eng.nnz = nnz_loc
+    plan = eng.plan()
+
+    flush_buf = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+
+    def flush():
+        flush_buf.fill_(1)
+        torch.cuda.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ---------------------------------------------------------------
+    for _ in range(args.warmup):
+        eng.run(); eng.sync()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    wall0 = time.perf_counter()
+    step_ms, kern = [], {}
+    for _ in range(args.steps):
+        flush()
+        eng.run(); eng.sync()
+        step_ms.append(eng.last_run_ms())
+        for name, ms in eng.kernel_times():
+            kern.setdefault(name, []).append(ms)
+    barrier()
+    wall = time.perf_counter() - wall0
+    # keep the GPU busy a little longer so the clock sampler sees it under load even for short runs
+    t_end = time.perf_counter() + (0.6 if rank == 0 else 0.0)
+    while time.perf_counter() < t_end:
+        eng.run(); eng.sync()
+    clocks = sampler.stop() if sampler else None
+    t_local = float(np.sum(step_ms))
+    if dist is not None:
+        tt = torch.tensor([t_local], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        t_total = float(tt.item())
+    else:
+        t_total = t_local
+    ms_per_step = t_total / args.steps
+    flops = 2.0 * d.nnz * K
+    value = flops / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer API ---------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        def e2e_step():
+            eng.upload_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B)
+            eng.run()
+            eng.download_raw(h_P)
+        for _ in range(2):
+            e2e_step()
+        n_e2e = max(3, min(args.steps, 10))
+        barrier()
+        ts = []
+        for _ in range(n_e2e):
+            t0 = time.perf_counter()
+            e2e_step()
+            ts.append(time.perf_counter() - t0)
+        t_e2e = float(np.mean(ts))
+        if dist is not None:
+            tt = torch.tensor([t_e2e], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t_e2e = float(tt.item())
+        h2d = 4 * (Mloc + 1) + 8 * nnz_loc + 4 * K * (Mloc + d.N)
+        e2e = {"value": flops / t_e2e / 1e9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(4 * nnz_loc),
+               "ms_per_step": t_e2e * 1e3, "steps": n_e2e,
+               "what": "upload_csr (pinned host S, A, B -> HBM, device-side validation + plan) + run + download (P.val -> pinned host); per rank bytes"}
+        eng.nnz = nnz_loc
+
+    # ---- roofline of the dominant kernel (this rank's shard) -------------------------------------
+    peak, peak_src = hbm_peak()
+    dom = max(kern, key=lambda k: np.mean(kern[k])) if kern else None
+    roofline = None
+    if dom:
+        dom_ms = float(np.mean(kern[dom]))
+        alg = eng.algorithmic_bytes()
+        if len(kern) > 1:
+            # split the compulsory bytes between the kernels by the nonzeros each one owns
+            share = plan["dense_nnz"] / max(1, plan["nnz"])
+            share = share if "dense" in dom else 1.0 - share
+            alg = alg * share
+        ach = alg / (dom_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                    "traffic": measured_traffic(dom, f"config{cfg}_k{K}_{args.mode}"), "algorithmic_bytes_per_launch": int(alg),
+                    "launch_ms": dom_ms, "peak_source": peak_src,
+                    "kernels_ms": {k: float(np.mean(v)) for k, v in kern.items()}}
+
+    line = None
+    if rank == 0:
+        line = {
+            "metric": "SDDMM GFLOP/s (2*nnz*K/t)", "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": {"fp32": "f32", "fp32_tc": "f32 (tf32x3 on dense tiles)", "tf32": "tf32", "bf16": "bf16"}[args.mode],
+            "data": "synthetic", "config": workload_config(cfg, K, args.mode, world),
+            "e2e": e2e, "gpu_launches": int(args.steps * plan["n_kernels"]), "roofline": roofline, "clocks": clocks,
+            "wall_s_timed_region": wall,
+            "plan": {k: plan[k] for k in ("nnz", "rows_nonempty", "cols_touched", "max_row_nnz", "rowtile_nnz", "rowtile_items",
+                                          "rowtile_rows_per_stage", "rowtile_grid", "rowtile_smem_bytes", "dense_nnz", "dense_tiles",
+                                          "rowgroup_nnz", "n_kernels")},
+        }
+        line["hbm_gb_per_s_algorithmic"] = eng.algorithmic_bytes() / (float(np.mean(step_ms)) * 1e-3) / 1e9
+
+    # ---- the other K=32 / K=64 configurations, kernel only (N = 1), and the CPU baseline --------------
+    if rank == 0 and world == 1 and not args.no_extra and args.scale == 1.0:
+        base, _, _ = cpu_reference(d.M, d.N, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, max_nnz=int(8e8 / K), reps=3)
+        line["cpu_baseline"] = base
+        per = {}
+        modes = {2: ["fp32", "fp32_tc", "tf32", "bf16"], 3: ["fp32"], 4: ["fp32"], 5: ["fp32", "bf16"]}
+        for c in (2, 3, 4, 5):
+            dd = d if c == cfg else Dataset(c, CONFIG_K[c], 1.0)
+            for m in modes[c]:
+                try:
+                    e2 = Engine(local, m)
+                    e2.upload_csr(dd.M, dd.N, dd.K, dd.row_ptr, dd.col_idx, dd.s_val, dd.A, dd.B)
+                    ms, ks = kernel_only_stats(e2, 10, 3, flush)
+                    ab = e2.algorithmic_bytes()
+                    per[f"config{c}_k{dd.K}_{m}"] = {"ms": ms, "gflops": 2.0 * dd.nnz * dd.K / ms / 1e6, "gb_per_s": ab / ms / 1e6,
+                                                    "hbm_frac": ab / ms / 1e6 / peak, "kernels_ms": ks}
+                    e2.close()
+                except Exception as ex:  # report, never hide
+                    per[f"config{c}_k{dd.K}_{m}"] = {"error": str(ex)}
+            if dd is not d:
+                dd.close()
+        line["per_config"] = per
+
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    eng.close()
+    for p in (h_rp, h_ci, h_sv, h_A, h_B, h_P):
+        lib.sddmm_b200_host_free(p)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,592 @@
+// C-ABI implementation of the B200 SDDMM engine (see include/sddmm_b200.h).
+//
+// One engine = one CUDA device, one stream, one device arena that is reused
+// across uploads.  upload_*() copies the operands, validates the pattern on the
+// device, builds the row-length histogram and the kernel plan; run() enqueues
+// the kernels between two CUDA events; download() copies P.val back.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/sddmm_b200.h"
+#include "kernel_rowtile.cuh"
+#include "plan_kernels.cuh"
+
+using namespace sddmm;
+
+namespace {
+
+constexpr size_t kAlign = 256;
+constexpr int kBlock = 256;
+constexpr int kMaxStageBytes = 64 * 1024;  // A rows staged per CTA
+
+struct Arena {
+    char *base = nullptr;
+    size_t cap = 0;
+};
+
+struct Carve {
+    size_t off = 0;
+    size_t take(size_t bytes) {
+        const size_t o = off;
+        off += (bytes + kAlign - 1) / kAlign * kAlign;
+        return o;
+    }
+};
+
+}  // namespace
+
+struct sddmm_b200_engine {
+    int device = 0;
+    int mode = SDDMM_B200_FP32;
+    uint32_t flags = 0;
+    cudaStream_t stream = nullptr;
+    static constexpr int kMaxKernels = 4;
+    cudaEvent_t ev[kMaxKernels + 1] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // ev[i], ev[i+1] bracket kernel i
+    const char *kernel_name[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};
+    int kernels_launched = 0;
+    int sm_count = 148;
+    char err[512] = {0};
+
+    Arena arena;
+    bool uploaded = false;
+    bool ran = false;
+    int64_t M = 0, N = 0, K = 0, nnz = 0;
+
+    // device views into the arena
+    int32_t *d_rp = nullptr, *d_col = nullptr;
+    float *d_sval = nullptr, *d_pval = nullptr;
+    float *d_A32 = nullptr, *d_B32 = nullptr;
+    __nv_bfloat16 *d_A16 = nullptr, *d_B16 = nullptr;
+    unsigned char *d_touched = nullptr;
+    uint32_t *d_rowstart = nullptr;
+    int2 *d_item_rows = nullptr;
+    int32_t *d_coo_rows = nullptr;
+    PlanCounters *d_pc = nullptr;
+    int32_t *d_err = nullptr;
+    int32_t *h_err = nullptr;  // pinned mirror of the device error word
+
+    // plan
+    sddmm_b200_plan_info plan;
+    bool use_scalar = false;
+    int cpl = 1;
+};
+
+namespace {
+
+int fail(sddmm_b200_engine *e, int code, const char *fmt, ...) {
+    if (e) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(e->err, sizeof(e->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define CU_TRY(e, call)                                                                                  \
+    do {                                                                                                 \
+        cudaError_t _st = (call);                                                                        \
+        if (_st != cudaSuccess) {                                                                        \
+            return fail((e), _st == cudaErrorMemoryAllocation ? SDDMM_B200_ERR_OOM : SDDMM_B200_ERR_CUDA, \
+                        "%s failed: %s (%s:%d)", #call, cudaGetErrorString(_st), __FILE__, __LINE__);    \
+        }                                                                                                \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) ok = true;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+int grid_for(int64_t n, int block, int cap) {
+    int64_t g = (n + block - 1) / block;
+    if (g < 1) g = 1;
+    if (g > cap) g = cap;
+    return static_cast<int>(g);
+}
+
+int ensure_arena(sddmm_b200_engine *e, size_t bytes) {
+    if (bytes <= e->arena.cap) return SDDMM_B200_OK;
+    if (e->arena.base) {
+        CU_TRY(e, cudaFree(e->arena.base));
+        e->arena.base = nullptr;
+        e->arena.cap = 0;
+    }
+    void *p = nullptr;
+    cudaError_t st = cudaMalloc(&p, bytes);
+    if (st != cudaSuccess) {
+        cudaGetLastError();
+        return fail(e, SDDMM_B200_ERR_OOM, "device arena of %zu bytes: %s", bytes, cudaGetErrorString(st));
+    }
+    e->arena.base = static_cast<char *>(p);
+    e->arena.cap = bytes;
+    return SDDMM_B200_OK;
+}
+
+template <typename ET>
+using RowTileFn = void (*)(const RowTileArgs);
+
+template <typename ET>
+RowTileFn<ET> pick_rowtile(int cpl) {
+    switch (cpl) {
+        case 1: return sddmm_rowtile_kernel<1, ET>;
+        case 2: return sddmm_rowtile_kernel<2, ET>;
+        case 4: return sddmm_rowtile_kernel<4, ET>;
+        case 8: return sddmm_rowtile_kernel<8, ET>;
+        default: return nullptr;
+    }
+}
+
+int round_up_cpl(int64_t K) {
+    const int64_t need = (K + 31) / 32;
+    if (need <= 1) return 1;
+    if (need <= 2) return 2;
+    if (need <= 4) return 4;
+    if (need <= 8) return 8;
+    return 0;
+}
+
+size_t elem_bytes(const sddmm_b200_engine *e) { return e->mode == SDDMM_B200_BF16 ? 2 : 4; }
+
+// Lay out the arena for the current dimensions and point the views into it.
+int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
+    Carve c;
+    const size_t nnz = static_cast<size_t>(e->nnz), M = static_cast<size_t>(e->M), N = static_cast<size_t>(e->N),
+                 K = static_cast<size_t>(e->K);
+    const size_t o_rp = c.take((M + 1) * 4);
+    const size_t o_col = c.take(nnz * 4 + 16);
+    const size_t o_sv = c.take(nnz * 4 + 16);
+    const size_t o_pv = c.take(nnz * 4 + 16);
+    const size_t o_A = c.take(M * K * 4);
+    const size_t o_B = c.take(N * K * 4);
+    const bool bf = e->mode == SDDMM_B200_BF16;
+    const size_t o_A16 = bf ? c.take(M * K * 2) : 0;
+    const size_t o_B16 = bf ? c.take(N * K * 2) : 0;
+    const size_t o_touch = c.take(N);
+    const size_t o_rs = c.take((nnz / 32 + 2) * 4);
+    const size_t o_items = c.take(static_cast<size_t>(std::max(n_items, 1)) * sizeof(int2));
+    const size_t o_coo = coo ? c.take(nnz * 4 + 16) : 0;
+    const size_t o_pc = c.take(sizeof(PlanCounters));
+    const size_t o_err = c.take(sizeof(int32_t));
+    int st = ensure_arena(e, c.off);
+    if (st) return st;
+    char *b = e->arena.base;
+    e->d_rp = reinterpret_cast<int32_t *>(b + o_rp);
+    e->d_col = reinterpret_cast<int32_t *>(b + o_col);
+    e->d_sval = reinterpret_cast<float *>(b + o_sv);
+    e->d_pval = reinterpret_cast<float *>(b + o_pv);
+    e->d_A32 = reinterpret_cast<float *>(b + o_A);
+    e->d_B32 = reinterpret_cast<float *>(b + o_B);
+    e->d_A16 = bf ? reinterpret_cast<__nv_bfloat16 *>(b + o_A16) : nullptr;
+    e->d_B16 = bf ? reinterpret_cast<__nv_bfloat16 *>(b + o_B16) : nullptr;
+    e->d_touched = reinterpret_cast<unsigned char *>(b + o_touch);
+    e->d_rowstart = reinterpret_cast<uint32_t *>(b + o_rs);
+    e->d_item_rows = reinterpret_cast<int2 *>(b + o_items);
+    e->d_coo_rows = coo ? reinterpret_cast<int32_t *>(b + o_coo) : nullptr;
+    e->d_pc = reinterpret_cast<PlanCounters *>(b + o_pc);
+    e->d_err = reinterpret_cast<int32_t *>(b + o_err);
+    return SDDMM_B200_OK;
+}
+
+// Work-item size: 2048 nonzeros, smaller for small matrices so that every SM gets work.
+int choose_item_nnz(const sddmm_b200_engine *e) {
+    const int64_t per = e->nnz / (static_cast<int64_t>(e->sm_count) * 4);
+    int64_t z = (per + 31) / 32 * 32;
+    z = std::max<int64_t>(256, std::min<int64_t>(2048, z));
+    return static_cast<int>(z);
+}
+
+int convert_storage(sddmm_b200_engine *e) {
+    if (e->mode != SDDMM_B200_BF16) return SDDMM_B200_OK;
+    const int cap = e->sm_count * 8;
+    k_f32_to_bf16<<<grid_for(e->M * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_A32, e->d_A16, e->M * e->K);
+    k_f32_to_bf16<<<grid_for(e->N * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_B32, e->d_B16, e->N * e->K);
+    CU_TRY(e, cudaGetLastError());
+    return SDDMM_B200_OK;
+}
+
+// Validation + histogram + plan, after the operands are in the arena.
+int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
+    const int cap = e->sm_count * 8;
+    cudaStream_t s = e->stream;
+    CU_TRY(e, cudaMemsetAsync(e->d_pc, 0, sizeof(PlanCounters), s));
+    CU_TRY(e, cudaMemsetAsync(e->d_err, 0, sizeof(int32_t), s));
+    CU_TRY(e, cudaMemsetAsync(e->d_touched, 0, static_cast<size_t>(e->N), s));
+    CU_TRY(e, cudaMemsetAsync(e->d_rowstart, 0, (static_cast<size_t>(e->nnz) / 32 + 2) * 4, s));
+    if (e->d_coo_rows) {
+        k_coo_to_row_ptr<<<grid_for(e->nnz + 1, kBlock, cap), kBlock, 0, s>>>(e->d_coo_rows, e->nnz, static_cast<int32_t>(e->M),
+                                                                              e->d_rp, e->d_pc);
+        // refuse to interpret a row_ptr built from unsorted rows
+        PlanCounters pc0;
+        CU_TRY(e, cudaMemcpyAsync(&pc0, e->d_pc, sizeof(pc0), cudaMemcpyDeviceToHost, s));
+        CU_TRY(e, cudaStreamSynchronize(s));
+        if (pc0.bad_coo) return fail(e, SDDMM_B200_ERR_INDEX, "COO row indices must be sorted and inside [0, M)");
+    }
+    k_row_stats<<<grid_for(e->M, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_rp, static_cast<int32_t>(e->M), e->nnz, e->d_rowstart, e->d_pc);
+    CU_TRY(e, cudaGetLastError());
+    PlanCounters pc;
+    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
+    CU_TRY(e, cudaStreamSynchronize(s));
+    if (pc.bad_row_ptr) return fail(e, SDDMM_B200_ERR_INDEX, "row_ptr must start at 0, end at nnz and be non-decreasing");
+    if (e->nnz > 0) {
+        k_col_scan<<<grid_for(e->nnz, kBlock, cap), kBlock, 0, s>>>(e->d_col, e->nnz, static_cast<int32_t>(e->N), e->d_rowstart,
+                                                                    e->d_touched, e->d_pc);
+        k_count_bytes<<<grid_for(e->N, kBlock, cap), kBlock, 0, s>>>(e->d_touched, e->N, &e->d_pc->cols_touched);
+        k_item_rows<<<grid_for(n_items, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_rp, static_cast<int32_t>(e->M), e->nnz, item_nnz, n_items,
+                                                                          e->d_item_rows);
+        CU_TRY(e, cudaGetLastError());
+    }
+    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
+    CU_TRY(e, cudaStreamSynchronize(s));
+    if (pc.bad_col) return fail(e, SDDMM_B200_ERR_INDEX, "column index outside [0, N)");
+
+    sddmm_b200_plan_info &p = e->plan;
+    std::memset(&p, 0, sizeof(p));
+    p.rows = e->M; p.cols = e->N; p.k = e->K; p.nnz = e->nnz;
+    p.rows_nonempty = static_cast<int64_t>(pc.rows_nonempty);
+    p.cols_touched = static_cast<int64_t>(pc.cols_touched);
+    p.max_row_nnz = pc.max_row_nnz;
+    for (int b = 0; b < SDDMM_B200_HIST_BINS; ++b) p.row_len_hist[b] = static_cast<int64_t>(pc.hist[b]);
+    p.cols_sorted = pc.unsorted_cols ? 0 : 1;
+    p.mode = e->mode;
+    p.n_devices = 1;
+
+    // ---- row-tile kernel launch shape -----------------------------------------
+    const size_t eb = elem_bytes(e);
+    e->cpl = round_up_cpl(e->K);
+    e->use_scalar = (e->K % 4 != 0) || e->cpl == 0 || static_cast<size_t>(e->K) * eb > kMaxStageBytes;
+    if (e->mode == SDDMM_B200_BF16 && (e->use_scalar || e->K % 8 != 0))
+        return fail(e, SDDMM_B200_ERR_UNSUPPORTED, "bf16 storage needs K %% 8 == 0 and K <= 256 (K = %lld)", (long long)e->K);
+    p.rowtile_nnz = e->nnz;
+    p.rowtile_items = n_items;
+    p.rowtile_item_nnz = item_nnz;
+    p.rowtile_block = kBlock;
+    if (e->nnz == 0) {
+        p.n_kernels = 0;
+        return SDDMM_B200_OK;
+    }
+    if (e->use_scalar) {
+        p.rowtile_rows_per_stage = 0;
+        p.rowtile_smem_bytes = 0;
+        p.rowtile_grid = grid_for(e->nnz, kBlock, e->sm_count * 8);
+        p.n_kernels = 1;
+        return SDDMM_B200_OK;
+    }
+    const double mean_len = static_cast<double>(e->nnz) / static_cast<double>(std::max<int64_t>(1, p.rows_nonempty));
+    int64_t R = static_cast<int64_t>(item_nnz / std::max(1.0, mean_len)) + 1;
+    R = (R + 7) / 8 * 8;
+    const int64_t r_max = std::max<int64_t>(1, static_cast<int64_t>(kMaxStageBytes / (static_cast<size_t>(e->K) * eb)));
+    R = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(R, r_max), e->M));
+    p.rowtile_rows_per_stage = static_cast<int32_t>(R);
+    const size_t a_bytes = (static_cast<size_t>(R) * e->K * eb + 15) & ~size_t(15);
+    p.rowtile_smem_bytes = static_cast<int32_t>(a_bytes + (R + 1) * 4);
+
+    const void *fn = (e->mode == SDDMM_B200_BF16) ? reinterpret_cast<const void *>(pick_rowtile<__nv_bfloat16>(e->cpl))
+                                                  : reinterpret_cast<const void *>(pick_rowtile<float>(e->cpl));
+    CU_TRY(e, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p.rowtile_smem_bytes));
+    int occ = 0;
+    CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kBlock, p.rowtile_smem_bytes));
+    if (occ < 1) return fail(e, SDDMM_B200_ERR_CUDA, "row-tile kernel does not fit on an SM (smem %d B)", p.rowtile_smem_bytes);
+    p.rowtile_grid = std::min(n_items, e->sm_count * occ);
+    p.n_kernels = 1;
+    return SDDMM_B200_OK;
+}
+
+int check_dims(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz) {
+    if (M < 1 || N < 1 || K < 1 || nnz < 0) return fail(e, SDDMM_B200_ERR_ARG, "need M, N, K >= 1 and nnz >= 0");
+    if (M >= (int64_t(1) << 31) - 1 || N >= (int64_t(1) << 31) - 1 || nnz >= (int64_t(1) << 31) - 64)
+        return fail(e, SDDMM_B200_ERR_ARG, "int32 index range exceeded");
+    return SDDMM_B200_OK;
+}
+
+int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz, const int32_t *row_ptr,
+                  const int32_t *coo_rows, const int32_t *col_idx, const float *s_val, const float *A, const float *B,
+                  cudaMemcpyKind kind) {
+    e->uploaded = false;
+    e->ran = false;
+    e->M = M; e->N = N; e->K = K; e->nnz = nnz;
+    const int item_nnz = choose_item_nnz(e);
+    const int n_items = static_cast<int>((nnz + item_nnz - 1) / item_nnz);
+    int st = carve_arena(e, coo_rows != nullptr, n_items);
+    if (st) return st;
+    cudaStream_t s = e->stream;
+    if (row_ptr) CU_TRY(e, cudaMemcpyAsync(e->d_rp, row_ptr, static_cast<size_t>(M + 1) * 4, kind, s));
+    if (coo_rows && nnz) CU_TRY(e, cudaMemcpyAsync(e->d_coo_rows, coo_rows, static_cast<size_t>(nnz) * 4, kind, s));
+    if (nnz) {
+        CU_TRY(e, cudaMemcpyAsync(e->d_col, col_idx, static_cast<size_t>(nnz) * 4, kind, s));
+        CU_TRY(e, cudaMemcpyAsync(e->d_sval, s_val, static_cast<size_t>(nnz) * 4, kind, s));
+    }
+    CU_TRY(e, cudaMemcpyAsync(e->d_A32, A, static_cast<size_t>(M * K) * 4, kind, s));
+    CU_TRY(e, cudaMemcpyAsync(e->d_B32, B, static_cast<size_t>(N * K) * 4, kind, s));
+    st = convert_storage(e);
+    if (st) return st;
+    st = build_plan(e, item_nnz, n_items);
+    if (st) return st;
+    e->uploaded = true;
+    return SDDMM_B200_OK;
+}
+
+// event after kernel `idx` (ev[0] is recorded by run() before the first launch)
+int mark_kernel(sddmm_b200_engine *e, const char *name) {
+    CU_TRY(e, cudaGetLastError());
+    const int idx = e->kernels_launched;
+    e->kernel_name[idx] = name;
+    CU_TRY(e, cudaEventRecord(e->ev[idx + 1], e->stream));
+    e->kernels_launched = idx + 1;
+    return SDDMM_B200_OK;
+}
+
+int launch_all(sddmm_b200_engine *e) {
+    const sddmm_b200_plan_info &p = e->plan;
+    e->kernels_launched = 0;
+    if (e->nnz == 0) return SDDMM_B200_OK;
+    if (e->use_scalar) {
+        sddmm_scalar_kernel<<<p.rowtile_grid, kBlock, 0, e->stream>>>(e->d_rp, e->d_col, e->d_sval, e->d_pval, e->d_A32, e->d_B32,
+                                                                      static_cast<int32_t>(e->M), static_cast<int32_t>(e->K), e->nnz);
+        return mark_kernel(e, "sddmm_scalar_kernel");
+    }
+    RowTileArgs a;
+    a.row_ptr = e->d_rp; a.col_idx = e->d_col; a.s_val = e->d_sval; a.p_val = e->d_pval;
+    a.item_rows = e->d_item_rows; a.item_ids = nullptr;
+    a.skip_tile_bitmap = nullptr; a.skip_tiles_per_row = 0;
+    a.err = e->d_err; a.nnz = e->nnz;
+    a.M = static_cast<int32_t>(e->M); a.K = static_cast<int32_t>(e->K);
+    a.n_items = p.rowtile_items; a.item_nnz = p.rowtile_item_nnz; a.rows_per_stage = p.rowtile_rows_per_stage;
+    if (e->mode == SDDMM_B200_BF16) {
+        a.A = e->d_A16; a.B = e->d_B16;
+        pick_rowtile<__nv_bfloat16>(e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, e->stream>>>(a);
+    } else {
+        a.A = e->d_A32; a.B = e->d_B32;
+        pick_rowtile<float>(e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, e->stream>>>(a);
+    }
+    return mark_kernel(e, "sddmm_rowtile_kernel");
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *sddmm_b200_version(void) { return "sddmm_b200 0.1 (sm_100a)"; }
+
+int sddmm_b200_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t flags) {
+    if (!out) return SDDMM_B200_ERR_ARG;
+    *out = nullptr;
+    if (mode < SDDMM_B200_FP32 || mode > SDDMM_B200_FP32_TC) return SDDMM_B200_ERR_ARG;
+    int n = sddmm_b200_device_count();
+    if (n <= 0 || device < 0 || device >= n) return SDDMM_B200_ERR_CUDA;
+    sddmm_b200_engine *e = new (std::nothrow) sddmm_b200_engine();
+    if (!e) return SDDMM_B200_ERR_OOM;
+    e->device = device;
+    e->mode = mode;
+    e->flags = flags;
+    DeviceGuard g(device);
+    bool ok = g.ok;
+    ok = ok && cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess;
+    for (int i = 0; i <= sddmm_b200_engine::kMaxKernels; ++i) ok = ok && cudaEventCreate(&e->ev[i]) == cudaSuccess;
+    ok = ok && cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess;
+    ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&e->h_err), sizeof(int32_t), cudaHostAllocDefault) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        sddmm_b200_destroy(e);
+        return SDDMM_B200_ERR_CUDA;
+    }
+    *e->h_err = 0;
+    *out = e;
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_destroy(sddmm_b200_engine *e) {
+    if (!e) return SDDMM_B200_OK;
+    {
+        DeviceGuard g(e->device);
+        if (e->stream) cudaStreamSynchronize(e->stream);
+        if (e->arena.base) cudaFree(e->arena.base);
+        if (e->h_err) cudaFreeHost(e->h_err);
+        for (int i = 0; i <= sddmm_b200_engine::kMaxKernels; ++i)
+            if (e->ev[i]) cudaEventDestroy(e->ev[i]);
+        if (e->stream) cudaStreamDestroy(e->stream);
+    }
+    delete e;
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_upload_csr(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, const int32_t *row_ptr,
+                          const int32_t *col_idx, const float *s_val, const float *A, const float *B) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!row_ptr || !A || !B) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    if (M < 1) return fail(e, SDDMM_B200_ERR_ARG, "need M >= 1");
+    const int64_t nnz = row_ptr[M];
+    int st = check_dims(e, M, N, K, nnz);
+    if (st) return st;
+    if (nnz > 0 && (!col_idx || !s_val)) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    DeviceGuard g(e->device);
+    return upload_common(e, M, N, K, nnz, row_ptr, nullptr, col_idx, s_val, A, B, cudaMemcpyHostToDevice);
+}
+
+int sddmm_b200_upload_coo(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz, const int32_t *row_idx,
+                          const int32_t *col_idx, const float *s_val, const float *A, const float *B) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!A || !B) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    int st = check_dims(e, M, N, K, nnz);
+    if (st) return st;
+    if (nnz > 0 && (!row_idx || !col_idx || !s_val)) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    DeviceGuard g(e->device);
+    static const int32_t dummy = 0;
+    return upload_common(e, M, N, K, nnz, nullptr, nnz ? row_idx : &dummy, col_idx, s_val, A, B, cudaMemcpyHostToDevice);
+}
+
+int sddmm_b200_upload_csr_device(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, const int32_t *row_ptr,
+                                 const int32_t *col_idx, const float *s_val, const float *A, const float *B) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!row_ptr || !A || !B) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    if (M < 1) return fail(e, SDDMM_B200_ERR_ARG, "need M >= 1");
+    DeviceGuard g(e->device);
+    int32_t last = 0;
+    CU_TRY(e, cudaMemcpy(&last, row_ptr + M, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    const int64_t nnz = last;
+    int st = check_dims(e, M, N, K, nnz);
+    if (st) return st;
+    if (nnz > 0 && (!col_idx || !s_val)) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    return upload_common(e, M, N, K, nnz, row_ptr, nullptr, col_idx, s_val, A, B, cudaMemcpyDeviceToDevice);
+}
+
+int sddmm_b200_update_dense(sddmm_b200_engine *e, const float *A, const float *B) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "update_dense before upload");
+    DeviceGuard g(e->device);
+    if (A) CU_TRY(e, cudaMemcpyAsync(e->d_A32, A, static_cast<size_t>(e->M * e->K) * 4, cudaMemcpyHostToDevice, e->stream));
+    if (B) CU_TRY(e, cudaMemcpyAsync(e->d_B32, B, static_cast<size_t>(e->N * e->K) * 4, cudaMemcpyHostToDevice, e->stream));
+    int st = convert_storage(e);
+    if (st) return st;
+    CU_TRY(e, cudaStreamSynchronize(e->stream));
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_update_values(sddmm_b200_engine *e, const float *s_val) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "update_values before upload");
+    if (!s_val && e->nnz) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    DeviceGuard g(e->device);
+    if (e->nnz) CU_TRY(e, cudaMemcpyAsync(e->d_sval, s_val, static_cast<size_t>(e->nnz) * 4, cudaMemcpyHostToDevice, e->stream));
+    CU_TRY(e, cudaStreamSynchronize(e->stream));
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_run(sddmm_b200_engine *e) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "run before upload");
+    DeviceGuard g(e->device);
+    CU_TRY(e, cudaEventRecord(e->ev[0], e->stream));
+    int st = launch_all(e);
+    if (st) return st;
+    CU_TRY(e, cudaMemcpyAsync(e->h_err, e->d_err, sizeof(int32_t), cudaMemcpyDeviceToHost, e->stream));
+    e->ran = true;
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_sync(sddmm_b200_engine *e) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    DeviceGuard g(e->device);
+    CU_TRY(e, cudaStreamSynchronize(e->stream));
+    if (e->ran && *e->h_err != kDevOk)
+        return fail(e, SDDMM_B200_ERR_DEVICE_WAIT, "device-side bounded wait ran out (code %d)", *e->h_err);
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_download(sddmm_b200_engine *e, float *p_val) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!e->uploaded || !e->ran) return fail(e, SDDMM_B200_ERR_STATE, "download before run");
+    if (!p_val && e->nnz) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    DeviceGuard g(e->device);
+    if (e->nnz) CU_TRY(e, cudaMemcpyAsync(p_val, e->d_pval, static_cast<size_t>(e->nnz) * 4, cudaMemcpyDeviceToHost, e->stream));
+    return sddmm_b200_sync(e);
+}
+
+int sddmm_b200_p_device(sddmm_b200_engine *e, float **p) {
+    if (!e || !p) return SDDMM_B200_ERR_ARG;
+    if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "p_device before upload");
+    *p = e->d_pval;
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_last_run_ms(sddmm_b200_engine *e, float *ms) {
+    if (!e || !ms) return SDDMM_B200_ERR_ARG;
+    if (!e->ran) return fail(e, SDDMM_B200_ERR_STATE, "last_run_ms before run");
+    DeviceGuard g(e->device);
+    *ms = 0.f;
+    if (e->kernels_launched == 0) return SDDMM_B200_OK;
+    CU_TRY(e, cudaEventSynchronize(e->ev[e->kernels_launched]));
+    CU_TRY(e, cudaEventElapsedTime(ms, e->ev[0], e->ev[e->kernels_launched]));
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_last_kernel_ms(sddmm_b200_engine *e, int index, float *ms, const char **name) {
+    if (!e || !ms) return SDDMM_B200_ERR_ARG;
+    if (!e->ran) return fail(e, SDDMM_B200_ERR_STATE, "last_kernel_ms before run");
+    if (index < 0 || index >= e->kernels_launched) return fail(e, SDDMM_B200_ERR_ARG, "kernel index %d of %d", index, e->kernels_launched);
+    DeviceGuard g(e->device);
+    CU_TRY(e, cudaEventSynchronize(e->ev[index + 1]));
+    CU_TRY(e, cudaEventElapsedTime(ms, e->ev[index], e->ev[index + 1]));
+    if (name) *name = e->kernel_name[index];
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info) {
+    if (!e || !info) return SDDMM_B200_ERR_ARG;
+    if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "get_plan before upload");
+    *info = e->plan;
+    return SDDMM_B200_OK;
+}
+
+int64_t sddmm_b200_algorithmic_bytes(sddmm_b200_engine *e) {
+    if (!e || !e->uploaded) return -1;
+    const int64_t eb = static_cast<int64_t>(elem_bytes(e));
+    return eb * e->K * (e->plan.rows_nonempty + e->plan.cols_touched) + 12 * e->nnz + 4 * (e->M + 1);
+}
+
+int64_t sddmm_b200_flops(sddmm_b200_engine *e) {
+    if (!e || !e->uploaded) return -1;
+    return 2 * e->nnz * e->K;
+}
+
+const char *sddmm_b200_last_error(sddmm_b200_engine *e) { return e ? e->err : "null engine"; }
+
+void *sddmm_b200_stream(sddmm_b200_engine *e) { return e ? static_cast<void *>(e->stream) : nullptr; }
+
+int sddmm_b200_host_alloc(void **ptr, int64_t bytes) {
+    if (!ptr || bytes < 0) return SDDMM_B200_ERR_ARG;
+    cudaError_t st = cudaHostAlloc(ptr, static_cast<size_t>(std::max<int64_t>(bytes, 1)), cudaHostAllocDefault);
+    if (st != cudaSuccess) {
+        cudaGetLastError();
+        *ptr = nullptr;
+        return st == cudaErrorMemoryAllocation ? SDDMM_B200_ERR_OOM : SDDMM_B200_ERR_CUDA;
+    }
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_host_free(void *ptr) {
+    if (!ptr) return SDDMM_B200_OK;
+    return cudaFreeHost(ptr) == cudaSuccess ? SDDMM_B200_OK : SDDMM_B200_ERR_CUDA;
+}
+
+}  // extern "C"

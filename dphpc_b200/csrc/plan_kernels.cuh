@@ -1,0 +1,145 @@
+// Upload-time kernels: validation of the uploaded pattern, the row-length
+// histogram, COO -> row_ptr, the nnz-balanced work-item table and storage
+// conversion.  They replace host loops of the reference
+// (CSR::_dispatch, src/matrices/CSR.hpp:214-264; GPUPreprocessing::init_csr,
+// src/competitors/gpu/gpu_preprocessing.hpp:56-128; gpu_convert_kernel,
+// src/competitors/gpu/gpu_convert.cu:8-18) and run once per upload, outside
+// the timed compute phase.
+#pragma once
+
+#include "device_utils.cuh"
+#include "../../include/sddmm_b200.h"
+
+namespace sddmm {
+
+struct PlanCounters {
+    unsigned long long hist[SDDMM_B200_HIST_BINS];
+    unsigned long long rows_nonempty;
+    unsigned long long cols_touched;
+    unsigned long long dense_nnz;
+    unsigned long long rowgroup_nnz;
+    int max_row_nnz;
+    int bad_row_ptr;   // row_ptr not monotone / wrong ends
+    int bad_col;       // column index outside [0, N)
+    int unsorted_cols; // a column index smaller than its predecessor inside a row
+    int bad_coo;       // COO row index out of range or decreasing
+    int dense_tiles;
+    int rowgroups;
+    int residual_items;
+};
+
+__device__ __forceinline__ int len_bin(int len) {
+    if (len <= 0) return 0;
+    int b = 32 - __clz(len);  // len in [2^(b-1), 2^b)
+    return b < SDDMM_B200_HIST_BINS ? b : SDDMM_B200_HIST_BINS - 1;
+}
+
+// one thread per row: monotonicity, histogram, max, nonempty count, row-start bits
+__global__ void k_row_stats(const int32_t *__restrict__ rp, int32_t M, int64_t nnz, uint32_t *__restrict__ row_start_bits,
+                            PlanCounters *__restrict__ pc) {
+    __shared__ unsigned int sh[SDDMM_B200_HIST_BINS];
+    __shared__ unsigned int s_nonempty;
+    __shared__ int s_max;
+    if (threadIdx.x < SDDMM_B200_HIST_BINS) sh[threadIdx.x] = 0;
+    if (threadIdx.x == 0) { s_nonempty = 0; s_max = 0; }
+    __syncthreads();
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i < M) {
+        const int a = rp[i], b = rp[i + 1];
+        const int len = b - a;
+        if (len < 0 || a < 0 || b > nnz) {
+            pc->bad_row_ptr = 1;
+        } else {
+            atomicAdd(&sh[len_bin(len)], 1u);
+            if (len > 0) {
+                atomicAdd(&s_nonempty, 1u);
+                atomicMax(&s_max, len);
+                atomicOr(&row_start_bits[a >> 5], 1u << (a & 31));
+            }
+        }
+        if (i == 0 && a != 0) pc->bad_row_ptr = 1;
+        if (i == M - 1 && b != nnz) pc->bad_row_ptr = 1;
+    }
+    __syncthreads();
+    if (threadIdx.x < SDDMM_B200_HIST_BINS && sh[threadIdx.x]) atomicAdd(&pc->hist[threadIdx.x], (unsigned long long)sh[threadIdx.x]);
+    if (threadIdx.x == 0) {
+        if (s_nonempty) atomicAdd(&pc->rows_nonempty, (unsigned long long)s_nonempty);
+        if (s_max) atomicMax(&pc->max_row_nnz, s_max);
+    }
+}
+
+// one thread per nonzero: column range, touched-column flags, in-row ordering
+__global__ void k_col_scan(const int32_t *__restrict__ col, int64_t nnz, int32_t N, const uint32_t *__restrict__ row_start_bits,
+                           unsigned char *__restrict__ touched, PlanCounters *__restrict__ pc) {
+    for (int64_t j = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; j < nnz;
+         j += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int c = col[j];
+        if (c < 0 || c >= N) {
+            pc->bad_col = 1;
+            continue;
+        }
+        if (!touched[c]) touched[c] = 1;
+        const bool is_start = (row_start_bits[j >> 5] >> (j & 31)) & 1u;
+        if (!is_start && j > 0 && col[j - 1] > c) pc->unsorted_cols = 1;
+    }
+}
+
+__global__ void k_count_bytes(const unsigned char *__restrict__ flags, int64_t n, unsigned long long *__restrict__ out) {
+    unsigned int local = 0;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        local += flags[i] ? 1u : 0u;
+    for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(kFullMask, local, off);
+    if ((threadIdx.x & 31) == 0 && local) atomicAdd(out, (unsigned long long)local);
+}
+
+// COO (sorted by row) -> row_ptr.  Thread j owns the rows in (row[j-1], row[j]].
+__global__ void k_coo_to_row_ptr(const int32_t *__restrict__ row, int64_t nnz, int32_t M, int32_t *__restrict__ rp,
+                                 PlanCounters *__restrict__ pc) {
+    for (int64_t j = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; j <= nnz;
+         j += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int prev = (j == 0) ? -1 : row[j - 1];
+        const int cur = (j == nnz) ? M : row[j];
+        if (prev < -1 || prev >= M || cur < 0 || cur > M || (j < nnz && cur >= M) || cur < prev) {
+            pc->bad_coo = 1;
+            continue;
+        }
+        for (int r = prev + 1; r <= cur; ++r) rp[r] = static_cast<int32_t>(j);
+    }
+}
+
+// row_ptr slice re-based to start at zero (multi-device row-range shards)
+__global__ void k_rebase(int32_t *__restrict__ rp, int64_t n, int32_t base) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        rp[i] -= base;
+}
+
+// one thread per work item: rows holding its first and last nonzero
+__global__ void k_item_rows(const int32_t *__restrict__ rp, int32_t M, int64_t nnz, int32_t item_nnz, int32_t n_items,
+                            int2 *__restrict__ item_rows) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_items) return;
+    const int64_t j0 = static_cast<int64_t>(t) * item_nnz;
+    const int64_t j1 = min(nnz, j0 + item_nnz) - 1;
+    int2 out;
+    {
+        int lo = 0, hi = M;
+        while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (rp[mid] <= j0) lo = mid; else hi = mid; }
+        out.x = lo;
+    }
+    {
+        int lo = out.x, hi = M;
+        while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (rp[mid] <= j1) lo = mid; else hi = mid; }
+        out.y = lo;
+    }
+    item_rows[t] = out;
+}
+
+__global__ void k_f32_to_bf16(const float *__restrict__ in, __nv_bfloat16 *__restrict__ out, int64_t n) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        out[i] = __float2bfloat16_rn(in[i]);
+}
+
+}  // namespace sddmm

@@ -1,0 +1,160 @@
+/*
+ * sddmm_b200.h -- C ABI of the B200 (sm_100a) SDDMM engine.
+ *
+ *   P_ij = S_ij * (A_i . B_j)   for every (i,j) on the sparsity pattern of S
+ *
+ * A is dense M x K row-major, B is dense N x K row-major (i.e. already the
+ * transposed right-hand operand), S and P share one CSR (or COO) pattern with
+ * int32 indices.  Values are fp32 in host memory in every mode.
+ *
+ * This is the boundary a host program binds instead of the per-competitor
+ * CUDA wrappers of francois141/dphpc.  Each entry point names the reference
+ * interface it stands in for (paths are relative to that project's root).
+ *
+ * Conventions: plain C types only, caller-owned buffers, every call returns an
+ * int status (0 = ok), a human-readable reason is kept per engine and returned
+ * by sddmm_b200_last_error().  No call throws, none falls back to a CPU path:
+ * without a CUDA device every compute entry point returns SDDMM_B200_ERR_CUDA.
+ */
+#ifndef SDDMM_B200_H
+#define SDDMM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct sddmm_b200_engine sddmm_b200_engine;
+
+/* status codes */
+enum {
+    SDDMM_B200_OK            = 0,
+    SDDMM_B200_ERR_ARG       = 1,  /* null pointer, negative size, K < 1 ...       */
+    SDDMM_B200_ERR_INDEX     = 2,  /* row_ptr not monotone / col out of range / COO rows unsorted */
+    SDDMM_B200_ERR_OOM       = 3,  /* device or host allocation failed            */
+    SDDMM_B200_ERR_CUDA      = 4,  /* any other CUDA runtime failure              */
+    SDDMM_B200_ERR_STATE     = 5,  /* call order violated (run before upload ...) */
+    SDDMM_B200_ERR_UNSUPPORTED = 6,
+    SDDMM_B200_ERR_COMM      = 7,  /* NCCL could not be loaded or failed          */
+    SDDMM_B200_ERR_DEVICE_WAIT = 8 /* a bounded device-side wait ran out          */
+};
+
+/* arithmetic modes */
+enum {
+    SDDMM_B200_FP32 = 0,  /* fp32 storage, fp32 FMA everywhere (parity bar: rel 1e-5)                  */
+    SDDMM_B200_TF32 = 1,  /* fp32 storage; >=50%-full tiles on tcgen05 kind::tf32 (rel 1e-2)           */
+    SDDMM_B200_BF16 = 2,  /* A and B stored as bf16 on the device, fp32 accumulate (rel 1e-2); K % 8 == 0, K <= 256 */
+    SDDMM_B200_FP32_TC = 3 /* fp32 storage; dense tiles on tcgen05 with a 3-term tf32 split (rel 1e-5) */
+};
+
+/* flags for sddmm_b200_create */
+enum {
+    SDDMM_B200_FLAG_NO_DENSE_TILES = 1u << 0, /* never take the tensor-core tile path */
+    SDDMM_B200_FLAG_NO_ROW_GROUPS  = 1u << 1  /* never merge rows with identical column lists */
+};
+
+#define SDDMM_B200_HIST_BINS 20
+
+typedef struct sddmm_b200_plan_info {
+    int64_t rows, cols, k, nnz;
+    int64_t rows_nonempty;         /* M+ : rows with at least one nonzero            */
+    int64_t cols_touched;          /* N+ : distinct column indices present           */
+    int64_t max_row_nnz;
+    int64_t row_len_hist[SDDMM_B200_HIST_BINS]; /* bin 0: empty rows, bin b>=1: 2^(b-1) <= len < 2^b */
+    int32_t cols_sorted;           /* 1 if col_idx is non-decreasing inside every row */
+    int32_t mode;
+    /* generic (row-tile) kernel */
+    int64_t rowtile_nnz;           /* nonzeros handled by the row-tile kernel        */
+    int32_t rowtile_items;         /* nnz-balanced work items                        */
+    int32_t rowtile_item_nnz;      /* nonzeros per work item                         */
+    int32_t rowtile_rows_per_stage;/* A rows staged in shared memory at a time       */
+    int32_t rowtile_grid, rowtile_block, rowtile_smem_bytes;
+    /* dense-tile (tensor-core) kernel */
+    int64_t dense_nnz;             /* nonzeros handled by the dense-tile kernel      */
+    int32_t dense_tiles;           /* tiles at least half full                        */
+    int32_t dense_tile_rows, dense_tile_cols;
+    int32_t dense_grid, dense_block, dense_smem_bytes;
+    /* row groups (consecutive rows with identical column lists) */
+    int64_t rowgroup_nnz;
+    int32_t rowgroup_groups;
+    int32_t n_kernels;             /* kernels one run() launches                      */
+    int32_t n_devices;
+} sddmm_b200_plan_info;
+
+/* ---- life cycle ---------------------------------------------------------
+ * Replaces the cudaMalloc / cudaFree blocks every reference competitor has in
+ * init_csr / cleanup_csr (src/competitors/gpu/gpu_convert.hpp:20-50, 58-74):
+ * the engine owns one device arena that is reused across uploads. */
+int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t flags);
+int sddmm_b200_destroy(sddmm_b200_engine *e);
+
+/* ---- upload (host buffers) ----------------------------------------------
+ * Replaces the H2D half of Competitor<T>::init_csr / init_coo
+ * (src/benchmark/competitor.hpp:27-28; e.g. src/competitors/gpu/gpu_basic.hpp:33-60)
+ * and the host-side preprocessing of GPUPreprocessing::init_csr
+ * (src/competitors/gpu/gpu_preprocessing.hpp:56-128): validation, the
+ * row-length histogram and the kernel plan are all built on the device here.
+ * row_ptr has M+1 entries, col_idx/s_val have row_ptr[M] entries. */
+int sddmm_b200_upload_csr(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K,
+                          const int32_t *row_ptr, const int32_t *col_idx, const float *s_val,
+                          const float *A, const float *B);
+/* COO entries must be sorted by row (the reference's COO<T> always is,
+ * src/matrices/COO.hpp:39); row_ptr is derived on the device. */
+int sddmm_b200_upload_coo(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz,
+                          const int32_t *row_idx, const int32_t *col_idx, const float *s_val,
+                          const float *A, const float *B);
+/* Same as upload_csr but every pointer is a DEVICE pointer on the engine's
+ * device (e.g. B received by an NCCL broadcast). The data is copied into the
+ * engine's own aligned arena.  No reference counterpart (the reference keeps
+ * nothing resident between runs). */
+int sddmm_b200_upload_csr_device(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K,
+                                 const int32_t *row_ptr, const int32_t *col_idx, const float *s_val,
+                                 const float *A, const float *B);
+/* Replace only the dense operands / only S's values, keeping pattern and plan
+ * (host pointers). */
+int sddmm_b200_update_dense(sddmm_b200_engine *e, const float *A, const float *B);
+int sddmm_b200_update_values(sddmm_b200_engine *e, const float *s_val);
+
+/* ---- compute --------------------------------------------------------------
+ * Replaces Competitor<T>::run_csr / run_coo (src/benchmark/competitor.hpp:30-31;
+ * e.g. GPUConvert::run_csr, src/competitors/gpu/gpu_convert.cu:54-74).
+ * run() only enqueues on the engine's stream; sync() blocks until done and
+ * reports device-side errors. */
+int sddmm_b200_run(sddmm_b200_engine *e);
+int sddmm_b200_sync(sddmm_b200_engine *e);
+
+/* ---- download ---------------------------------------------------------------
+ * Replaces the D2H half of cleanup_csr / cleanup_coo
+ * (src/competitors/gpu/gpu_convert.hpp:58-64): writes nnz floats, in the order
+ * of the uploaded col_idx. */
+int sddmm_b200_download(sddmm_b200_engine *e, float *p_val);
+/* device pointer to the nnz output values (valid until the next upload). */
+int sddmm_b200_p_device(sddmm_b200_engine *e, float **p_val_device);
+
+/* ---- introspection ----------------------------------------------------------
+ * Device time of the last run() (CUDA events on the engine's stream), standing
+ * in for the cudaEvent pair of Benchmark<T>::timing (src/benchmark/benchmark.hpp:160-164). */
+int sddmm_b200_last_run_ms(sddmm_b200_engine *e, float *ms);
+/* Device time and name of kernel `index` (0 .. plan.n_kernels-1) of the last run(). */
+int sddmm_b200_last_kernel_ms(sddmm_b200_engine *e, int index, float *ms, const char **name);
+int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info);
+/* compulsory traffic e*K*(M+ + N+) + 12*nnz + 4*(M+1) with e = bytes per stored
+ * element of A/B; extends the read-only model of plots/plot_roofline.py:30 */
+int64_t sddmm_b200_algorithmic_bytes(sddmm_b200_engine *e);
+int64_t sddmm_b200_flops(sddmm_b200_engine *e); /* 2*nnz*K (plots/plot_roofline.py:29 without the +nnz) */
+const char *sddmm_b200_last_error(sddmm_b200_engine *e);
+/* raw CUDA stream (cudaStream_t) the engine launches on, for external event timing */
+void *sddmm_b200_stream(sddmm_b200_engine *e);
+int sddmm_b200_device_count(void);
+const char *sddmm_b200_version(void);
+
+/* pinned host memory helpers (so callers without a CUDA toolchain can stage
+ * inputs for full-rate copies) */
+int sddmm_b200_host_alloc(void **ptr, int64_t bytes);
+int sddmm_b200_host_free(void *ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SDDMM_B200_H */

@@ -1,0 +1,261 @@
+"""Parity of the CUDA engine (through the C ABI) against the CPU oracle.  Needs a B200.
+
+Bar: pattern untouched (the engine returns values in the order of the uploaded col_idx), values within
+  |p - p_ref| <= tol * |s_ij| * sum_k |a_ik b_jk|
+with tol = 1e-5 for the fp32 modes and 1e-2 for tf32 / bf16 -- "rel 1e-5 / 1e-2" made robust to the
+cancellation that A, B in [-1, 1) produce.  p_ref is the oracle restating the reference's CPUBasic.
+"""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle_lib
+from dphpc_b200 import Dataset, Engine, SddmmError
+
+pytestmark = pytest.mark.gpu
+
+GOLD = json.loads((Path(__file__).parent / "golden" / "sddmm_golden.json").read_text())
+TOL = {"fp32": 1e-5, "fp32_tc": 1e-5, "tf32": 1e-2, "bf16": 1e-2}
+MODES = ["fp32", "bf16", "tf32", "fp32_tc"]
+
+
+@pytest.fixture(scope="module")
+def engines():
+    es = {m: Engine(0, m) for m in MODES}
+    yield es
+    for e in es.values():
+        e.close()
+
+
+def check(engine, mode, oracle, M, N, K, rp, ci, sv, A, B, coo=False, what=""):
+    rp, ci = np.ascontiguousarray(rp, np.int32), np.ascontiguousarray(ci, np.int32)
+    sv = np.ascontiguousarray(sv, np.float32)
+    A, B = np.ascontiguousarray(A, np.float32), np.ascontiguousarray(B, np.float32)
+    rows = oracle.coo_rows(M, rp)
+    if coo:
+        p = engine.sddmm_coo(M, N, K, rows, ci, sv, A, B)
+    else:
+        p = engine.sddmm_csr(M, N, K, rp, ci, sv, A, B)
+    p_ref = oracle.sddmm_csr(M, K, rp, ci, sv, A, B)
+    bound = oracle_lib.abs_dot_bound(rows, ci, sv, A, B)
+    oracle_lib.assert_values_close(p, p_ref, bound, TOL[mode], what or f"{mode} {M}x{N} K={K}")
+    return p
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", sorted(GOLD["tiny"]))
+def test_tiny_golden_cases(engines, oracle, mode, name):
+    # sddmm_coo1..4 and DummyDataset: K = 2 or 3 -> scalar path; bf16 storage cannot take K % 4 != 0
+    g = GOLD["tiny"][name]
+    A, B = np.array(g["A"], np.float32), np.array(g["B"], np.float32)
+    e = engines[mode]
+    if mode == "bf16":
+        with pytest.raises(SddmmError) as ei:
+            e.sddmm_csr(g["M"], B.shape[0], g["K"], g["row_ptr"], g["col_idx"], g["s_val"], A, B)
+        assert ei.value.code == 6
+        return
+    p = e.sddmm_csr(g["M"], B.shape[0], g["K"], g["row_ptr"], g["col_idx"], g["s_val"], A, B)
+    assert p.tolist() == g["p_csr"]  # small integers: exact in every summation order
+    p = e.sddmm_coo(g["M"], B.shape[0], g["K"], g["coo_rows"], g["coo_cols"], g["s_val"], A, B)
+    assert p.tolist() == g["p_coo"]
+
+
+@pytest.mark.parametrize("mode", ["fp32", "fp32_tc"])
+@pytest.mark.parametrize("name", sorted(GOLD["random"]))
+def test_random_golden_cases(engines, oracle, mode, name):
+    g = GOLD["random"][name]
+    f = lambda b: np.array(b, np.uint32).view(np.float32)  # noqa: E731
+    A, B = f(g["A_bits"]).reshape(g["M"], g["K"]), f(g["B_bits"]).reshape(g["N"], g["K"])
+    p = check(engines[mode], mode, oracle, g["M"], g["N"], g["K"], g["row_ptr"], g["col_idx"], f(g["s_val_bits"]), A, B)
+    # and directly against the reference's stored output
+    rows = oracle.coo_rows(g["M"], np.array(g["row_ptr"], np.int32))
+    bound = oracle_lib.abs_dot_bound(rows, np.array(g["col_idx"]), f(g["s_val_bits"]), A, B)
+    oracle_lib.assert_values_close(p, f(g["p_bits"]), bound, 1e-5, name)
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("cfg,scale,K", [(1, 1.0, 32), (2, 0.05, 32), (2, 0.12, 32), (3, 0.004, 64), (4, 0.002, 32),
+                                         (4, 0.02, 32), (5, 0.003, 32), (5, 0.002, 128), (5, 0.002, 64), (5, 0.001, 256)])
+def test_synthetic_configs_small(engines, oracle, mode, cfg, scale, K):
+    d = Dataset(cfg, K, scale)
+    check(engines[mode], mode, oracle, d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, what=f"{mode} cfg{cfg} K={K}")
+    check(engines[mode], mode, oracle, d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, coo=True,
+          what=f"{mode} cfg{cfg} K={K} coo")
+
+
+def test_config2_unaligned_blocks(engines, oracle):
+    d = Dataset(2, 32, 0.1, variant=1)
+    for mode in ("fp32", "fp32_tc", "tf32"):
+        check(engines[mode], mode, oracle, d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, what=f"{mode} unaligned")
+
+
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 8, 12, 20, 31, 32, 33, 36, 64, 96, 100, 128, 160, 256, 260])
+def test_any_k(engines, oracle, K):
+    # the reference's kernels need K % 8 == 0 or K % 32 == 0 (src/competitors/gpu/gpu_basic.cu:77-80,
+    # gpu_shared.cu:98-101); the engine takes any K >= 1
+    d = Dataset(uniform=(301, 257, 6000), K=K, seed=K)
+    check(engines["fp32"], "fp32", oracle, d.M, d.N, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    if K % 8 == 0 and K <= 256:
+        check(engines["bf16"], "bf16", oracle, d.M, d.N, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+
+
+@pytest.mark.parametrize("M,N,K,density", [(500, 500, 32, 0.3), (250, 250, 32, 0.7), (10000, 10000, 32, 0.001)])
+def test_reference_random_suite(engines, oracle, M, N, K, density):
+    # sddmm_random_coo / _dense_coo / _sparse_coo / sddmm_csr_coo (tests/matrix_test.cc:184-246)
+    d = Dataset(uniform=(M, N, int(M * N * density)), K=K, seed=M)
+    for mode in MODES:
+        p_csr = check(engines[mode], mode, oracle, M, N, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        p_coo = check(engines[mode], mode, oracle, M, N, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, coo=True)
+        assert np.array_equal(p_csr, p_coo)  # COO(P_csr) == P_coo, bit for bit
+
+
+def test_edge_shapes(engines, oracle):
+    e = engines["fp32"]
+    rng = np.random.default_rng(5)
+
+    def dense(m, k):
+        return (rng.random((m, k), dtype=np.float32) * 2 - 1).astype(np.float32)
+
+    # a single 50 000-nnz row next to empty rows; M = 1; N = 1; fully dense 66x66; diagonal; non-square
+    N = 60000
+    cols = np.sort(rng.choice(N, 50000, replace=False)).astype(np.int32)
+    rp = np.array([0, 0, 50000, 50000, 50000], np.int32)
+    check(e, "fp32", oracle, 4, N, 32, rp, cols, rng.random(50000, dtype=np.float32), dense(4, 32), dense(N, 32), what="one long row")
+    check(e, "fp32", oracle, 1, 7, 8, [0, 3], [0, 2, 6], [1, 2, 3], dense(1, 8), dense(7, 8), what="M=1")
+    check(e, "fp32", oracle, 5, 1, 4, [0, 1, 1, 2, 3, 3], [0, 0, 0], [1, 2, 3], dense(5, 4), dense(1, 4), what="N=1")
+    rp = (np.arange(67) * 66).astype(np.int32)
+    ci = np.tile(np.arange(66, dtype=np.int32), 66)
+    for mode in MODES:
+        check(engines[mode], mode, oracle, 66, 66, 32, rp, ci, rng.random(66 * 66, dtype=np.float32), dense(66, 32), dense(66, 32),
+              what=f"{mode} dense 66x66")
+    n = 3000
+    check(e, "fp32", oracle, n, n, 32, np.arange(n + 1), rng.permutation(n), rng.random(n, dtype=np.float32), dense(n, 32),
+          dense(n, 32), what="latin")
+    d = Dataset(uniform=(4562 // 4, 5761 // 4, 40000), K=32, seed=9)
+    check(e, "fp32", oracle, d.M, d.N, 32, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, what="non-square")
+    # trailing empty rows and an empty first row
+    check(e, "fp32", oracle, 6, 9, 16, [0, 0, 2, 2, 5, 5, 5], [1, 8, 0, 3, 4], [1, 1, 1, 1, 1], dense(6, 16), dense(9, 16), what="empty rows")
+
+
+def test_empty_matrix(engines):
+    e = engines["fp32"]
+    p = e.sddmm_csr(3, 3, 4, [0, 0, 0, 0], np.zeros(0, np.int32), np.zeros(0, np.float32), np.ones((3, 4)), np.ones((3, 4)))
+    assert p.size == 0
+    assert e.plan()["n_kernels"] == 0
+
+
+def test_stale_output_is_overwritten(engines, oracle):
+    # the reference's test helper reuses one P object that still holds S's values (tests/matrix_test.cc:66-67)
+    d = Dataset(1, 32, 1.0)
+    e = engines["fp32"]
+    e.upload_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    out = np.full(d.nnz, 123.0, np.float32)
+    e.run()
+    e.download(out)
+    assert np.array_equal(out, e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B))
+
+
+def test_bad_inputs_are_rejected(engines):
+    e = engines["fp32"]
+    A = np.ones((3, 4), np.float32)
+    with pytest.raises(SddmmError) as ei:
+        e.sddmm_csr(3, 3, 4, [0, 2, 1, 3], [0, 1, 2], [1, 1, 1], A, A)  # row_ptr decreases
+    assert ei.value.code == 2
+    with pytest.raises(SddmmError) as ei:
+        e.sddmm_csr(3, 3, 4, [0, 1, 2, 3], [0, 3, 2], [1, 1, 1], A, A)  # column out of range
+    assert ei.value.code == 2
+    with pytest.raises(SddmmError) as ei:
+        e.sddmm_coo(3, 3, 4, [1, 0, 2], [0, 1, 2], [1, 1, 1], A, A)  # COO rows not sorted
+    assert ei.value.code == 2
+    with pytest.raises(SddmmError) as ei:
+        e.upload_csr(3, 3, 0, [0, 1, 2, 3], [0, 1, 2], [1, 1, 1], np.zeros((3, 0)), np.zeros((3, 0)))
+    assert ei.value.code == 1
+    # the engine is still usable afterwards
+    assert e.sddmm_csr(3, 3, 4, [0, 1, 2, 3], [0, 1, 2], [1, 1, 1], A, A).tolist() == [4.0, 4.0, 4.0]
+    fresh = Engine(0, "fp32")
+    with pytest.raises(SddmmError) as ei:
+        fresh.run()
+    assert ei.value.code == 5
+    fresh.close()
+
+
+def test_plan_reports_histogram_and_counts(engines):
+    d = Dataset(4, 32, 0.01)
+    e = engines["fp32"]
+    e.upload_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    p = e.plan()
+    lens = np.diff(d.row_ptr)
+    assert p["rows_nonempty"] == int((lens > 0).sum())
+    assert p["cols_touched"] == np.unique(d.col_idx).size
+    assert p["max_row_nnz"] == int(lens.max())
+    hist = np.zeros(20, np.int64)
+    for L in lens:
+        hist[min(19, int(L).bit_length())] += 1
+    assert p["row_len_hist"] == hist.tolist()
+    assert p["cols_sorted"] == 1
+    assert e.flops() == 2 * d.nnz * d.K
+    assert e.algorithmic_bytes() == 4 * d.K * (p["rows_nonempty"] + p["cols_touched"]) + 12 * d.nnz + 4 * (d.M + 1)
+
+
+def test_unsorted_columns_inside_rows(engines, oracle):
+    # not something the reference's containers produce, but nothing in the math needs sorted columns
+    d = Dataset(uniform=(200, 300, 5000), K=32, seed=2)
+    ci = d.col_idx.copy()
+    rng = np.random.default_rng(0)
+    for i in range(d.M):
+        a, b = d.row_ptr[i], d.row_ptr[i + 1]
+        ci[a:b] = rng.permutation(ci[a:b])
+    for mode in ("fp32", "fp32_tc"):
+        engines[mode].upload_csr(d.M, d.N, d.K, d.row_ptr, ci, d.s_val, d.A, d.B)
+        assert engines[mode].plan()["cols_sorted"] == 0
+        check(engines[mode], mode, oracle, d.M, d.N, d.K, d.row_ptr, ci, d.s_val, d.A, d.B, what="unsorted")
+
+
+def test_update_values_and_dense_keep_the_plan(engines, oracle):
+    d = Dataset(5, 32, 0.003)
+    e = engines["fp32"]
+    p1 = e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    e.update_values(d.s_val * 2)
+    e.run()
+    assert np.array_equal(e.download(), p1 * 2)  # scaling by 2 is exact: linearity in S
+    e.update_dense(A=d.A * 0.5)
+    e.run()
+    assert np.array_equal(e.download(), p1)
+
+
+# ---- full BASELINE sizes: size-independent properties + sampled comparison --------------------------
+@pytest.mark.parametrize("cfg,K,mode", [(2, 32, "fp32"), (2, 32, "fp32_tc"), (2, 32, "tf32"), (3, 64, "fp32"), (4, 32, "fp32"),
+                                        (5, 32, "fp32"), (5, 32, "bf16")])
+def test_full_size_properties(engines, oracle, cfg, K, mode):
+    d = Dataset(cfg, K, 1.0)
+    e = engines[mode]
+    p = e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    assert np.isfinite(p).all()
+    # (a) a slice of rows from the middle and the ends against the oracle
+    for r0 in (0, d.M // 2, d.M - 2000):
+        r1 = r0 + 2000
+        a, b = int(d.row_ptr[r0]), int(d.row_ptr[r1])
+        ref = np.zeros(d.nnz, np.float32)
+        oracle.sddmm_csr_rows(r0, r1, d.K, d.row_ptr, d.col_idx, d.s_val, np.ascontiguousarray(d.A), np.ascontiguousarray(d.B), ref)
+        rows = np.repeat(np.arange(r0, r1), np.diff(d.row_ptr[r0:r1 + 1]))
+        bound = oracle_lib.abs_dot_bound(rows, d.col_idx[a:b], d.s_val[a:b], d.A, d.B)
+        oracle_lib.assert_values_close(p[a:b], ref[a:b], bound, TOL[mode], f"cfg{cfg} rows {r0}..{r1}")
+    # (b) 200 000 random nonzeros against a float64 dot product
+    rng = np.random.default_rng(cfg)
+    idx = np.sort(rng.choice(d.nnz, 200000, replace=False))
+    rows = (np.searchsorted(d.row_ptr, idx, side="right") - 1).astype(np.int64)
+    want = oracle_lib.dot_f64(rows, d.col_idx[idx], d.s_val[idx], d.A, d.B)
+    bound = oracle_lib.abs_dot_bound(rows, d.col_idx[idx], d.s_val[idx], d.A, d.B)
+    oracle_lib.assert_values_close(p[idx], want, bound, max(TOL[mode], 2e-6 * 1), f"cfg{cfg} sampled")
+    # (c) linearity in S (exact: doubling is exact in fp32) and determinism
+    e.update_values(d.s_val * 2)
+    e.run()
+    assert np.array_equal(e.download(), p * 2)
+    e.update_values(d.s_val)
+    e.run()
+    assert np.array_equal(e.download(), p)
+    # (d) COO upload gives the same bits
+    if cfg in (2, 5):
+        assert np.array_equal(e.sddmm_coo(d.M, d.N, d.K, d.row_idx(), d.col_idx, d.s_val, d.A, d.B), p)
