@@ -12,7 +12,9 @@ from pathlib import Path
 import numpy as np
 
 PKG = Path(__file__).resolve().parent
-ENGINE_LIB = PKG / "libsddmm_b200.so"
+import os
+
+ENGINE_LIB = Path(os.environ.get("SDDMM_B200_LIB", PKG / "libsddmm_b200.so"))  # override: A/B-test another build
 DATASETS_LIB = PKG / "libsddmm_datasets.so"
 
 FP32, TF32, BF16, FP32_TC = 0, 1, 2, 3

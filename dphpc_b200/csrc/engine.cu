@@ -4,16 +4,19 @@
 // across uploads.  upload_*() copies the operands, validates the pattern on the
 // device, builds the row-length histogram and the kernel plan; run() enqueues
 // the kernels between two CUDA events; download() copies P.val back.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
 
 #include "../../include/sddmm_b200.h"
+#include "kernel_dense_tile.cuh"
 #include "kernel_rowtile.cuh"
 #include "plan_kernels.cuh"
 
@@ -24,6 +27,7 @@ namespace {
 constexpr size_t kAlign = 256;
 constexpr int kBlock = 256;
 constexpr int kMaxStageBytes = 64 * 1024;  // A rows staged per CTA
+constexpr int kDenseMinCount = 2048;       // a 64x64 tile is "dense" from half full
 
 struct Arena {
     char *base = nullptr;
@@ -70,6 +74,22 @@ struct sddmm_b200_engine {
     PlanCounters *d_pc = nullptr;
     int32_t *d_err = nullptr;
     int32_t *h_err = nullptr;  // pinned mirror of the device error word
+
+    // dense-tile (tensor-core) path
+    bool dense_possible = false;   // buffers carved for this upload
+    int64_t tile_grid = 0;         // (M/64 rounded up) * (N/64 rounded up)
+    int32_t tiles_per_row = 0;
+    int32_t dense_cap = 0;
+    int32_t *d_tile_counts = nullptr;
+    uint32_t *d_tile_bitmap = nullptr;
+    int32_t *d_dense_ids = nullptr;
+    DenseTileDesc *d_dense_descs = nullptr;
+    int32_t *d_item_covered = nullptr;
+    int32_t *d_item_ids = nullptr;
+    float *d_Ahi = nullptr, *d_Alo = nullptr, *d_Bhi = nullptr, *d_Blo = nullptr;
+    CUtensorMap map_a_hi, map_b_hi, map_a_lo, map_b_lo;
+    int32_t n_dense = 0;
+    int32_t n_residual_items = 0;
 
     // plan
     sddmm_b200_plan_info plan;
@@ -138,12 +158,12 @@ template <typename ET>
 using RowTileFn = void (*)(const RowTileArgs);
 
 template <typename ET>
-RowTileFn<ET> pick_rowtile(int cpl) {
+RowTileFn<ET> pick_rowtile(int cpl, bool exact) {
     switch (cpl) {
-        case 1: return sddmm_rowtile_kernel<1, ET>;
-        case 2: return sddmm_rowtile_kernel<2, ET>;
-        case 4: return sddmm_rowtile_kernel<4, ET>;
-        case 8: return sddmm_rowtile_kernel<8, ET>;
+        case 1: return exact ? sddmm_rowtile_kernel<1, true, ET> : sddmm_rowtile_kernel<1, false, ET>;
+        case 2: return exact ? sddmm_rowtile_kernel<2, true, ET> : sddmm_rowtile_kernel<2, false, ET>;
+        case 4: return exact ? sddmm_rowtile_kernel<4, true, ET> : sddmm_rowtile_kernel<4, false, ET>;
+        case 8: return exact ? sddmm_rowtile_kernel<8, true, ET> : sddmm_rowtile_kernel<8, false, ET>;
         default: return nullptr;
     }
 }
@@ -179,9 +199,38 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     const size_t o_coo = coo ? c.take(nnz * 4 + 16) : 0;
     const size_t o_pc = c.take(sizeof(PlanCounters));
     const size_t o_err = c.take(sizeof(int32_t));
+    // dense-tile path: only carved when the mode, K and the size of the 64x64 tile grid allow it
+    e->tiles_per_row = static_cast<int32_t>((N + 63) / 64);
+    e->tile_grid = static_cast<int64_t>((M + 63) / 64) * e->tiles_per_row;
+    const bool tc_mode = e->mode == SDDMM_B200_TF32 || e->mode == SDDMM_B200_FP32_TC;
+    e->dense_possible = tc_mode && !(e->flags & SDDMM_B200_FLAG_NO_DENSE_TILES) && K % 32 == 0 && K <= 256 &&
+                        e->tile_grid <= (int64_t(1) << 22) && nnz >= kDenseMinCount;
+    e->dense_cap = e->dense_possible ? static_cast<int32_t>(std::min<int64_t>(e->tile_grid, e->nnz / kDenseMinCount + 1)) : 0;
+    const bool split = e->dense_possible && e->mode == SDDMM_B200_FP32_TC;
+    const size_t tg = static_cast<size_t>(e->tile_grid);
+    const size_t o_tc = e->dense_possible ? c.take(tg * 4) : 0;
+    const size_t o_tb = e->dense_possible ? c.take((tg / 32 + 1) * 4) : 0;
+    const size_t o_di = e->dense_possible ? c.take(static_cast<size_t>(e->dense_cap) * 4) : 0;
+    const size_t o_dd = e->dense_possible ? c.take(static_cast<size_t>(e->dense_cap) * sizeof(DenseTileDesc)) : 0;
+    const size_t o_ic = e->dense_possible ? c.take(static_cast<size_t>(std::max(n_items, 1)) * 4) : 0;
+    const size_t o_ii = e->dense_possible ? c.take(static_cast<size_t>(std::max(n_items, 1)) * 4) : 0;
+    const size_t o_ahi = split ? c.take(M * K * 4) : 0;
+    const size_t o_alo = split ? c.take(M * K * 4) : 0;
+    const size_t o_bhi = split ? c.take(N * K * 4) : 0;
+    const size_t o_blo = split ? c.take(N * K * 4) : 0;
     int st = ensure_arena(e, c.off);
     if (st) return st;
     char *b = e->arena.base;
+    e->d_tile_counts = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_tc) : nullptr;
+    e->d_tile_bitmap = e->dense_possible ? reinterpret_cast<uint32_t *>(b + o_tb) : nullptr;
+    e->d_dense_ids = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_di) : nullptr;
+    e->d_dense_descs = e->dense_possible ? reinterpret_cast<DenseTileDesc *>(b + o_dd) : nullptr;
+    e->d_item_covered = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_ic) : nullptr;
+    e->d_item_ids = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_ii) : nullptr;
+    e->d_Ahi = split ? reinterpret_cast<float *>(b + o_ahi) : nullptr;
+    e->d_Alo = split ? reinterpret_cast<float *>(b + o_alo) : nullptr;
+    e->d_Bhi = split ? reinterpret_cast<float *>(b + o_bhi) : nullptr;
+    e->d_Blo = split ? reinterpret_cast<float *>(b + o_blo) : nullptr;
     e->d_rp = reinterpret_cast<int32_t *>(b + o_rp);
     e->d_col = reinterpret_cast<int32_t *>(b + o_col);
     e->d_sval = reinterpret_cast<float *>(b + o_sv);
@@ -201,6 +250,10 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
 
 // Work-item size: 2048 nonzeros, smaller for small matrices so that every SM gets work.
 int choose_item_nnz(const sddmm_b200_engine *e) {
+    if (const char *env = std::getenv("SDDMM_B200_ITEM_NNZ")) {  // tuning knob: nonzeros per work item
+        const long v = std::atol(env);
+        if (v >= 32 && v <= (1 << 20)) return static_cast<int>((v + 31) / 32 * 32);
+    }
     const int64_t per = e->nnz / (static_cast<int64_t>(e->sm_count) * 4);
     int64_t z = (per + 31) / 32 * 32;
     z = std::max<int64_t>(256, std::min<int64_t>(2048, z));
@@ -208,11 +261,90 @@ int choose_item_nnz(const sddmm_b200_engine *e) {
 }
 
 int convert_storage(sddmm_b200_engine *e) {
-    if (e->mode != SDDMM_B200_BF16) return SDDMM_B200_OK;
     const int cap = e->sm_count * 8;
+    if (e->d_Ahi) {  // hi/lo operands of the 3-product tensor-core scheme
+        k_split_tf32<<<grid_for(e->M * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_A32, e->d_Ahi, e->d_Alo, e->M * e->K);
+        k_split_tf32<<<grid_for(e->N * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_B32, e->d_Bhi, e->d_Blo, e->N * e->K);
+        CU_TRY(e, cudaGetLastError());
+    }
+    if (e->mode != SDDMM_B200_BF16) return SDDMM_B200_OK;
     k_f32_to_bf16<<<grid_for(e->M * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_A32, e->d_A16, e->M * e->K);
     k_f32_to_bf16<<<grid_for(e->N * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_B32, e->d_B16, e->N * e->K);
     CU_TRY(e, cudaGetLastError());
+    return SDDMM_B200_OK;
+}
+
+// 2-D tensor map over a row-major rows x K fp32 matrix: box = 32 floats (one 128-byte
+// k-block) x 64 rows, 128-byte swizzle, out-of-range rows read as zero.
+int make_operand_map(sddmm_b200_engine *e, CUtensorMap *map, const float *base, int64_t rows, int64_t K) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CU_TRY(e, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return fail(e, SDDMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K) * 4};
+    const cuuint32_t box[2] = {32, 64};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), gdim, gstride, box, estride,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(e, SDDMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    return SDDMM_B200_OK;
+}
+
+// Find the 64x64 tiles that are at least half full, build their row descriptors and the list
+// of work items the row-tile kernel still has to visit.
+int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item_nnz, int n_items) {
+    e->n_dense = 0;
+    e->n_residual_items = n_items;
+    if (!e->dense_possible || base_pc.unsorted_cols || base_pc.dup_cols || base_pc.max_row_nnz < 32) return SDDMM_B200_OK;
+    const int cap = e->sm_count * 8;
+    cudaStream_t s = e->stream;
+    const size_t tg = static_cast<size_t>(e->tile_grid);
+    CU_TRY(e, cudaMemsetAsync(e->d_tile_counts, 0, tg * 4, s));
+    CU_TRY(e, cudaMemsetAsync(e->d_tile_bitmap, 0, (tg / 32 + 1) * 4, s));
+    CU_TRY(e, cudaMemsetAsync(e->d_item_covered, 0, static_cast<size_t>(n_items) * 4, s));
+    k_tile_count<<<grid_for(e->M * 32, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_rp, e->d_col, static_cast<int32_t>(e->M), e->tiles_per_row,
+                                                                       e->d_tile_counts);
+    k_tile_select<<<grid_for(e->tile_grid, kBlock, cap), kBlock, 0, s>>>(e->d_tile_counts, e->tile_grid, kDenseMinCount, e->d_tile_bitmap,
+                                                                         e->d_dense_ids, e->dense_cap, e->d_pc);
+    CU_TRY(e, cudaGetLastError());
+    PlanCounters pc;
+    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
+    CU_TRY(e, cudaStreamSynchronize(s));
+    const int n_dense = std::min(pc.dense_tiles, e->dense_cap);
+    if (n_dense <= 0) return SDDMM_B200_OK;
+    k_tile_rows<DenseTileDesc><<<grid_for(static_cast<int64_t>(n_dense) * 64, kBlock, 1 << 30), kBlock, 0, s>>>(
+        e->d_rp, e->d_col, static_cast<int32_t>(e->M), e->tiles_per_row, e->d_dense_ids, n_dense, e->d_dense_descs, item_nnz,
+        e->d_item_covered);
+    k_residual_items<<<grid_for(n_items, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_item_covered, n_items, item_nnz, e->nnz, e->d_item_ids,
+                                                                          e->d_pc);
+    CU_TRY(e, cudaGetLastError());
+    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
+    CU_TRY(e, cudaStreamSynchronize(s));
+    const bool split = e->mode == SDDMM_B200_FP32_TC;
+    int st = make_operand_map(e, &e->map_a_hi, split ? e->d_Ahi : e->d_A32, e->M, e->K);
+    if (!st) st = make_operand_map(e, &e->map_b_hi, split ? e->d_Bhi : e->d_B32, e->N, e->K);
+    if (!st) st = make_operand_map(e, &e->map_a_lo, split ? e->d_Alo : e->d_A32, e->M, e->K);
+    if (!st) st = make_operand_map(e, &e->map_b_lo, split ? e->d_Blo : e->d_B32, e->N, e->K);
+    if (st) return st;
+    CU_TRY(e, cudaFuncSetAttribute(sddmm_dense_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DenseSmem::kDynamicBytes));
+    e->n_dense = n_dense;
+    e->n_residual_items = pc.residual_items;
+    sddmm_b200_plan_info &p = e->plan;
+    p.dense_tiles = n_dense;
+    p.dense_nnz = static_cast<int64_t>(pc.dense_nnz);
+    p.dense_tile_rows = p.dense_tile_cols = kDenseTile;
+    p.dense_block = kDenseThreads;
+    p.dense_smem_bytes = static_cast<int32_t>(DenseSmem::kDynamicBytes);
+    p.dense_grid = std::min((n_dense + 1) / 2, e->sm_count * 2);
     return SDDMM_B200_OK;
 }
 
@@ -268,12 +400,23 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
     e->use_scalar = (e->K % 4 != 0) || e->cpl == 0 || static_cast<size_t>(e->K) * eb > kMaxStageBytes;
     if (e->mode == SDDMM_B200_BF16 && (e->use_scalar || e->K % 8 != 0))
         return fail(e, SDDMM_B200_ERR_UNSUPPORTED, "bf16 storage needs K %% 8 == 0 and K <= 256 (K = %lld)", (long long)e->K);
-    p.rowtile_nnz = e->nnz;
-    p.rowtile_items = n_items;
     p.rowtile_item_nnz = item_nnz;
     p.rowtile_block = kBlock;
+    e->n_dense = 0;
+    e->n_residual_items = n_items;
     if (e->nnz == 0) {
         p.n_kernels = 0;
+        return SDDMM_B200_OK;
+    }
+    if (!e->use_scalar) {
+        int st = build_dense_plan(e, pc, item_nnz, n_items);
+        if (st) return st;
+    }
+    p.rowtile_nnz = e->nnz - p.dense_nnz;
+    p.rowtile_items = e->n_residual_items;
+    const int dense_kernels = e->n_dense > 0 ? 1 : 0;
+    if (e->n_residual_items == 0) {
+        p.n_kernels = dense_kernels;
         return SDDMM_B200_OK;
     }
     if (e->use_scalar) {
@@ -292,14 +435,14 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
     const size_t a_bytes = (static_cast<size_t>(R) * e->K * eb + 15) & ~size_t(15);
     p.rowtile_smem_bytes = static_cast<int32_t>(a_bytes + (R + 1) * 4);
 
-    const void *fn = (e->mode == SDDMM_B200_BF16) ? reinterpret_cast<const void *>(pick_rowtile<__nv_bfloat16>(e->cpl))
-                                                  : reinterpret_cast<const void *>(pick_rowtile<float>(e->cpl));
+    const void *fn = (e->mode == SDDMM_B200_BF16) ? reinterpret_cast<const void *>(pick_rowtile<__nv_bfloat16>(e->cpl, e->K == 32 * e->cpl))
+                                                  : reinterpret_cast<const void *>(pick_rowtile<float>(e->cpl, e->K == 32 * e->cpl));
     CU_TRY(e, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p.rowtile_smem_bytes));
     int occ = 0;
     CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kBlock, p.rowtile_smem_bytes));
     if (occ < 1) return fail(e, SDDMM_B200_ERR_CUDA, "row-tile kernel does not fit on an SM (smem %d B)", p.rowtile_smem_bytes);
-    p.rowtile_grid = std::min(n_items, e->sm_count * occ);
-    p.n_kernels = 1;
+    p.rowtile_grid = std::min(e->n_residual_items, e->sm_count * occ);
+    p.n_kernels = 1 + dense_kernels;
     return SDDMM_B200_OK;
 }
 
@@ -356,19 +499,32 @@ int launch_all(sddmm_b200_engine *e) {
                                                                       static_cast<int32_t>(e->M), static_cast<int32_t>(e->K), e->nnz);
         return mark_kernel(e, "sddmm_scalar_kernel");
     }
+    if (e->n_dense > 0) {
+        DenseArgs d;
+        d.tile_ids = e->d_dense_ids; d.descs = e->d_dense_descs; d.s_val = e->d_sval; d.p_val = e->d_pval; d.err = e->d_err;
+        d.n_tiles = e->n_dense; d.tiles_per_row = e->tiles_per_row; d.k_blocks = static_cast<int32_t>(e->K / 32);
+        d.split = e->mode == SDDMM_B200_FP32_TC ? 1 : 0;
+        sddmm_dense_tile_kernel<<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a_hi, e->map_b_hi,
+                                                                                                  e->map_a_lo, e->map_b_lo);
+        int st = mark_kernel(e, "sddmm_dense_tile_kernel");
+        if (st) return st;
+        if (e->n_residual_items == 0) return SDDMM_B200_OK;
+    }
     RowTileArgs a;
     a.row_ptr = e->d_rp; a.col_idx = e->d_col; a.s_val = e->d_sval; a.p_val = e->d_pval;
-    a.item_rows = e->d_item_rows; a.item_ids = nullptr;
-    a.skip_tile_bitmap = nullptr; a.skip_tiles_per_row = 0;
+    a.item_rows = e->d_item_rows;
+    a.item_ids = e->n_dense > 0 ? e->d_item_ids : nullptr;
+    a.skip_tile_bitmap = e->n_dense > 0 ? e->d_tile_bitmap : nullptr;
+    a.skip_tiles_per_row = e->tiles_per_row;
     a.err = e->d_err; a.nnz = e->nnz;
     a.M = static_cast<int32_t>(e->M); a.K = static_cast<int32_t>(e->K);
     a.n_items = p.rowtile_items; a.item_nnz = p.rowtile_item_nnz; a.rows_per_stage = p.rowtile_rows_per_stage;
     if (e->mode == SDDMM_B200_BF16) {
         a.A = e->d_A16; a.B = e->d_B16;
-        pick_rowtile<__nv_bfloat16>(e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, e->stream>>>(a);
+        pick_rowtile<__nv_bfloat16>(e->cpl, e->K == 32 * e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, e->stream>>>(a);
     } else {
         a.A = e->d_A32; a.B = e->d_B32;
-        pick_rowtile<float>(e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, e->stream>>>(a);
+        pick_rowtile<float>(e->cpl, e->K == 32 * e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, e->stream>>>(a);
     }
     return mark_kernel(e, "sddmm_rowtile_kernel");
 }

@@ -1,0 +1,305 @@
+// Dense-tile SDDMM kernel: 64x64 tiles of S that are at least half full are
+// computed as dense A_tile * B_tile^T products on the 5th-generation tensor
+// cores (tcgen05.mma, fp32 accumulators in tensor memory) and then sampled
+// through a per-row presence mask.
+//
+// A job is a PAIR of dense tiles.  Their 64 A rows each are stacked into one
+// 128-row operand, their 64 B rows each into one 128-row operand, and ONE
+// M=128, N=128 MMA computes both 64x64 products on the diagonal blocks of the
+// accumulator (the two off-diagonal blocks are never read; tensor throughput is
+// not what bounds this path).  Accumulator row r lives in TMEM lane r.
+//
+// Per job:
+//   producer thread   TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no
+//                     multicast) of the operand rows into shared memory,
+//                     completion on an mbarrier; then issues the tcgen05.mma
+//                     k-steps and tcgen05.commit
+//   8 epilogue warps  tcgen05.ld the accumulator (thread = row), park it in
+//                     shared memory, then one warp per tile row streams that
+//                     row: lane l owns columns l and l+32, a 64-bit presence
+//                     mask says which of them are nonzeros of S, the rank of
+//                     the column inside the mask is the offset from the row's
+//                     first nonzero in the tile.  S.val is read and P.val is
+//                     written in CSR order in contiguous runs; col_idx is not
+//                     read at all (the mask, built once per upload, replaces it).
+//
+// Modes: 1 product (tf32 operands, rel 1e-2) or 3 products with a hi/lo split
+// of A and B (hi*hi + hi*lo + lo*hi, rel ~5e-7: fp32-grade results).
+// K must be a multiple of 32; every 32-wide k-block is one 128-byte swizzle atom.
+//
+// Every wait on an mbarrier is bounded; on a timeout the CTA sets the error
+// word, stops issuing work, and still frees its tensor memory.
+#pragma once
+
+#include <cuda.h>
+
+#include "device_utils.cuh"
+
+namespace sddmm {
+
+constexpr int kDenseTile = 64;               // tile edge
+constexpr int kDenseEpiWarps = 8;
+constexpr int kDenseThreads = (kDenseEpiWarps + 1) * 32;   // + producer/MMA warp
+constexpr int kDenseAccStride = 65;          // floats per accumulator row in smem (odd: conflict-free column writes)
+constexpr uint32_t kOperandBytes = 128 * 128;  // 128 rows x one 128-byte k-block
+constexpr uint32_t kHalfOperandBytes = 64 * 128;
+constexpr int kTmemCols = 128;
+
+// Per dense tile: first nonzero of each of its 64 rows inside the tile's column
+// range (CSR position), and which of the 64 columns are present.
+struct DenseTileDesc {
+    int32_t start[kDenseTile];
+    unsigned long long mask[kDenseTile];
+};
+
+struct DenseArgs {
+    const int32_t *tile_ids;        // n_tiles dense tiles: id = tile_row * tiles_per_row + tile_col
+    const DenseTileDesc *descs;     // n_tiles
+    const float *s_val;
+    float *p_val;
+    int32_t *err;
+    int32_t n_tiles;
+    int32_t tiles_per_row;
+    int32_t k_blocks;               // K / 32
+    int32_t split;                  // 0: one tf32 product, 1: three products on hi/lo operands
+};
+
+// shared memory carve-up (dynamic, 1024-byte aligned by hand)
+struct DenseSmem {
+    static constexpr uint32_t kAhi = 0;
+    static constexpr uint32_t kBhi = kAhi + kOperandBytes;
+    static constexpr uint32_t kAlo = kBhi + kOperandBytes;
+    static constexpr uint32_t kBlo = kAlo + kOperandBytes;
+    static constexpr uint32_t kAcc = kBlo + kOperandBytes;
+    static constexpr uint32_t kAccBytes = 128 * kDenseAccStride * 4;
+    static constexpr uint32_t kStart = kAcc + kAccBytes;          // 128 int32
+    static constexpr uint32_t kMask = kStart + 128 * 4;           // 128 u64 (8-byte aligned: kAccBytes % 8 == 0)
+    static constexpr uint32_t kBars = kMask + 128 * 8;            // 4 mbarriers
+    static constexpr uint32_t kTmemPtr = kBars + 4 * 8;
+    static constexpr uint32_t kTotal = kTmemPtr + 16;
+    static constexpr uint32_t kDynamicBytes = kTotal + 1024;      // slack for the manual 1024-byte alignment
+};
+
+__device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart, sm_100 descriptor version 1
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+    d |= static_cast<uint64_t>(1) << 16;                       // leading byte offset (unused for swizzled K-major)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;               // stride byte offset: next 8-row group
+    d |= static_cast<uint64_t>(1) << 46;                       // descriptor version
+    d |= static_cast<uint64_t>(2) << 61;                       // SWIZZLE_128B
+    return d;
+}
+
+// kind::tf32, fp32 accumulate, both operands K-major, M = 128, N = 128
+constexpr uint32_t kIdescTf32 = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(kIdescTf32), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void epi_barrier() {  // the 8 epilogue warps only
+    asm volatile("bar.sync 1, %0;" ::"n"(kDenseEpiWarps * 32) : "memory");
+}
+
+__global__ void __launch_bounds__(kDenseThreads, 2)
+sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMap map_a_hi,
+                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                        const __grid_constant__ CUtensorMap map_b_lo) {
+    extern __shared__ unsigned char dense_smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(dense_smem_raw) + 1023) & ~uintptr_t(1023));
+    float *sAcc = reinterpret_cast<float *>(smem + DenseSmem::kAcc);
+    int32_t *sStart = reinterpret_cast<int32_t *>(smem + DenseSmem::kStart);
+    unsigned long long *sMask = reinterpret_cast<unsigned long long *>(smem + DenseSmem::kMask);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + DenseSmem::kBars);
+    uint64_t *ops_full = &bars[0], *ops_free = &bars[1], *acc_full = &bars[2], *acc_free = &bars[3];
+    uint32_t *tmem_ptr_smem = reinterpret_cast<uint32_t *>(smem + DenseSmem::kTmemPtr);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int n_jobs = (args.n_tiles + 1) >> 1;
+
+    if (tid == 0) {
+        mbar_init(ops_full, 1);
+        mbar_init(ops_free, 1);
+        mbar_init(acc_full, 1);
+        mbar_init(acc_free, kDenseEpiWarps);
+        fence_mbar_init();
+    }
+    if (warp == 0) {  // one warp allocates the tensor memory for the CTA
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_proxy_async_smem();
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    if (warp == kDenseEpiWarps) {
+        // ===================== producer + MMA issuer (one thread) =====================
+        if (lane == 0) {
+            uint32_t it = 0;  // k-block iterations issued so far (phase of ops_full / ops_free)
+            uint32_t jb = 0;  // jobs issued so far (phase of acc_free)
+            bool ok = true;
+            const uint32_t a_hi = smem_u32(smem + DenseSmem::kAhi), b_hi = smem_u32(smem + DenseSmem::kBhi);
+            const uint32_t a_lo = smem_u32(smem + DenseSmem::kAlo), b_lo = smem_u32(smem + DenseSmem::kBlo);
+            for (int job = blockIdx.x; job < n_jobs && ok; job += gridDim.x, ++jb) {
+                const int t0 = args.tile_ids[2 * job];
+                const bool has1 = (2 * job + 1) < args.n_tiles;
+                const int t1 = has1 ? args.tile_ids[2 * job + 1] : t0;
+                const int r0 = (t0 / args.tiles_per_row) * kDenseTile, c0 = (t0 % args.tiles_per_row) * kDenseTile;
+                const int r1 = (t1 / args.tiles_per_row) * kDenseTile, c1 = (t1 % args.tiles_per_row) * kDenseTile;
+                for (int kb = 0; kb < args.k_blocks && ok; ++kb, ++it) {
+                    // operands of the previous iteration fully consumed by the tensor core?
+                    if (!mbar_wait_bounded(ops_free, (it & 1u) ^ 1u)) { ok = false; break; }
+                    const uint32_t bytes = (args.split ? 4u : 2u) * kOperandBytes;
+                    mbar_expect_tx(ops_full, bytes);
+                    const int x = kb * 32;
+                    tma_load_2d(smem + DenseSmem::kAhi, &map_a_hi, x, r0, ops_full);
+                    tma_load_2d(smem + DenseSmem::kAhi + kHalfOperandBytes, &map_a_hi, x, r1, ops_full);
+                    tma_load_2d(smem + DenseSmem::kBhi, &map_b_hi, x, c0, ops_full);
+                    tma_load_2d(smem + DenseSmem::kBhi + kHalfOperandBytes, &map_b_hi, x, c1, ops_full);
+                    if (args.split) {
+                        tma_load_2d(smem + DenseSmem::kAlo, &map_a_lo, x, r0, ops_full);
+                        tma_load_2d(smem + DenseSmem::kAlo + kHalfOperandBytes, &map_a_lo, x, r1, ops_full);
+                        tma_load_2d(smem + DenseSmem::kBlo, &map_b_lo, x, c0, ops_full);
+                        tma_load_2d(smem + DenseSmem::kBlo + kHalfOperandBytes, &map_b_lo, x, c1, ops_full);
+                    }
+                    if (!mbar_wait_bounded(ops_full, it & 1u)) { ok = false; break; }
+                    if (kb == 0) {
+                        // accumulator drained by the epilogue of the previous job?
+                        if (!mbar_wait_bounded(acc_free, (jb & 1u) ^ 1u)) { ok = false; break; }
+                    }
+                    tcgen05_fence_after();
+                    uint32_t accumulate = (kb > 0) ? 1u : 0u;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {  // 4 k-steps of 8 tf32 = 32 bytes inside the swizzle atom
+                        const uint32_t adv = static_cast<uint32_t>(ks) * 32u;
+                        if (args.split) {
+                            umma_tf32(tmem_base, umma_smem_desc(a_lo + adv), umma_smem_desc(b_hi + adv), accumulate);
+                            umma_tf32(tmem_base, umma_smem_desc(a_hi + adv), umma_smem_desc(b_lo + adv), 1u);
+                            umma_tf32(tmem_base, umma_smem_desc(a_hi + adv), umma_smem_desc(b_hi + adv), 1u);
+                        } else {
+                            umma_tf32(tmem_base, umma_smem_desc(a_hi + adv), umma_smem_desc(b_hi + adv), accumulate);
+                        }
+                        accumulate = 1u;
+                    }
+                    umma_commit(ops_free);  // arrives once the MMAs above have read their operands
+                }
+                if (ok) umma_commit(acc_full);  // arrives once the accumulator of this job is complete
+            }
+            if (!ok) atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
+        }
+    } else {
+        // ===================== epilogue warps =====================
+        const int q = warp & 3;               // TMEM lane quarter this warp may read: rows 32q .. 32q+31
+        const int h = warp >> 2;              // which 32 of the tile's 64 columns this warp moves
+        const int tile_of_q = q >> 1;         // rows 0-63: first tile, rows 64-127: second tile
+        uint32_t jb = 0;
+        bool ok = true;
+        for (int job = blockIdx.x; job < n_jobs; job += gridDim.x, ++jb) {
+            const bool has1 = (2 * job + 1) < args.n_tiles;
+            // row descriptors of both tiles -> shared memory (threads 0..127: one row each)
+            if (tid < 128) {
+                const int which = tid >> 6;
+                if (which == 0 || has1) {
+                    const DenseTileDesc *d = args.descs + (2 * job + which);
+                    sStart[tid] = d->start[tid & 63];
+                    sMask[tid] = d->mask[tid & 63];
+                } else {
+                    sStart[tid] = 0;
+                    sMask[tid] = 0ull;
+                }
+            }
+            if (ok && !mbar_wait_bounded(acc_full, jb & 1u)) {
+                ok = false;
+                atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
+            }
+            if (ok) {
+                tcgen05_fence_after();
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + static_cast<uint32_t>(64 * tile_of_q + 32 * h);
+                tmem_ld_32x32b_x32(taddr, v);
+                tcgen05_fence_before();
+                float *row = sAcc + (32 * q + lane) * kDenseAccStride + 32 * h;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) row[c] = __uint_as_float(v[c]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_free);   // tensor memory may be overwritten by the next job
+            epi_barrier();                          // accumulator + descriptors visible to all epilogue warps
+            if (ok) {
+                // stream the 128 tile rows: warp w takes rows w, w+8, ...; 8 rows in flight per warp
+#pragma unroll 1
+                for (int rb = warp; rb < 128; rb += 8 * kDenseEpiWarps) {
+                    float sv0[8], sv1[8];
+                    int p0[8], p1[8];
+                    bool on0[8], on1[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int r = rb + u * kDenseEpiWarps;
+                        const unsigned long long m = sMask[r];
+                        const uint32_t mlo = static_cast<uint32_t>(m), mhi = static_cast<uint32_t>(m >> 32);
+                        const uint32_t below = (1u << lane) - 1u;
+                        const int st = sStart[r];
+                        on0[u] = (mlo >> lane) & 1u;
+                        on1[u] = (mhi >> lane) & 1u;
+                        p0[u] = st + __popc(mlo & below);
+                        p1[u] = st + __popc(mlo) + __popc(mhi & below);
+                        sv0[u] = on0[u] ? __ldcs(args.s_val + p0[u]) : 0.f;
+                        sv1[u] = on1[u] ? __ldcs(args.s_val + p1[u]) : 0.f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int r = rb + u * kDenseEpiWarps;
+                        const float *arow = sAcc + r * kDenseAccStride;
+                        if (on0[u]) __stcs(args.p_val + p0[u], arow[lane] * sv0[u]);
+                        if (on1[u]) __stcs(args.p_val + p1[u], arow[lane + 32] * sv1[u]);
+                    }
+                }
+            }
+            epi_barrier();  // all rows streamed before the next job overwrites sAcc / descriptors
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+}  // namespace sddmm

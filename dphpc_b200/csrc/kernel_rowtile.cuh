@@ -3,22 +3,25 @@
 // Work decomposition (no atomics, exactly one writer per nonzero):
 //   * the nonzero index space [0, nnz) is cut into items of `item_nnz`
 //     consecutive nonzeros (nnz-balanced, independent of the row-length
-//     distribution); `item_row[t]` is the row that holds the first nonzero of
-//     item t (built once per upload on the device);
+//     distribution); `item_rows[t]` holds the rows of the first and last
+//     nonzero of item t (built once per upload on the device);
 //   * a CTA walks the rows its item spans in stages of at most
 //     `rows_per_stage` rows: the row_ptr slice and the A rows of the stage are
 //     brought into shared memory, the A rows by ONE bulk async copy
 //     (cp.async.bulk, completion on an mbarrier), since consecutive rows of a
 //     row-major A are one contiguous byte range;
-//   * a warp takes 32 consecutive nonzeros: one coalesced 128-byte load each of
-//     col_idx and S.val, a binary search of the staged row_ptr slice for the
-//     row of each nonzero, then each 8-lane group gathers the B rows of its 8
-//     nonzeros (8 independent 16-byte loads per lane in flight, each B row read
-//     as one contiguous line by the group), multiplies with the A chunks held
-//     in shared memory and reduces over K with a transposing shuffle tree that
-//     leaves nonzero g on lane g -> one coalesced 128-byte store of P per warp.
+//   * a warp takes a 32-aligned window of 32 consecutive nonzeros: each 8-lane
+//     group reads the 8 column indices of its nonzeros as two 16-byte loads,
+//     gathers the 8 B rows (8 independent 16-byte loads per lane in flight, a B
+//     row is read as one contiguous line by the group), multiplies with the A
+//     chunks and reduces over K with a transposing shuffle tree that leaves
+//     nonzero g on lane g -> one coalesced 128-byte store of P per warp;
+//   * the A chunks come from registers while a window lies inside one row
+//     (long rows: A_i is reused across all its nonzeros), otherwise from the
+//     staged tile in shared memory through per-nonzero row offsets.
 //
-// CPL = chunks per lane (a chunk is 4 K-elements).  K <= 32*CPL, K % 4 == 0.
+// A "chunk" is 4 consecutive K elements.  CPL = chunks per lane, so K <= 32*CPL.
+// EXACT = (K == 32*CPL): no chunk-range predicates in the inner loop.
 #pragma once
 
 #include "device_utils.cuh"
@@ -44,23 +47,33 @@ struct RowTileArgs {
     int32_t rows_per_stage;   // R
 };
 
-template <int CPL, typename ET>
-__global__ void __launch_bounds__(256) sddmm_rowtile_kernel(const RowTileArgs args) {
+constexpr int kRowTileWarps = 8;
+#ifndef SDDMM_ROWTILE_MINB1
+#define SDDMM_ROWTILE_MINB1 4   // resident CTAs per SM the compiler must allow for, K <= 32
+#endif
+#ifndef SDDMM_ROWTILE_MINBN
+#define SDDMM_ROWTILE_MINBN 2   // same, K > 32
+#endif
+
+template <int CPL, bool EXACT, typename ET>
+__global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE_MINB1 : SDDMM_ROWTILE_MINBN) sddmm_rowtile_kernel(const RowTileArgs args) {
     using chunk_t = typename ChunkOf<ET>::type;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(16) int32_t sRowOff[kRowTileWarps][32];
 
     const int K = args.K;
     const int R = args.rows_per_stage;
-    const int nchunks = K >> 2;
+    const int nchunks = EXACT ? 8 * CPL : (K >> 2);
+    const uint32_t row_bytes = static_cast<uint32_t>(nchunks) * sizeof(chunk_t);
     ET *sA = reinterpret_cast<ET *>(smem_raw);
-    const uint32_t a_stage_bytes = (static_cast<uint32_t>(R) * K * sizeof(ET) + 15u) & ~15u;
+    const chunk_t *sAc = reinterpret_cast<const chunk_t *>(smem_raw);
+    const uint32_t a_stage_bytes = (static_cast<uint32_t>(R) * row_bytes + 15u) & ~15u;
     int32_t *sRp = reinterpret_cast<int32_t *>(smem_raw + a_stage_bytes);
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const int nwarps = blockDim.x >> 5;
     const int gl = lane & 7;          // lane inside its 8-lane group
     const int gbase = lane & ~7;      // first lane of the group
 
@@ -72,7 +85,9 @@ __global__ void __launch_bounds__(256) sddmm_rowtile_kernel(const RowTileArgs ar
     __syncthreads();
     uint32_t phase = 0;
 
-    const chunk_t *Bc = reinterpret_cast<const chunk_t *>(args.B);
+    // this lane's chunk of every B row
+    const unsigned char *Bl = reinterpret_cast<const unsigned char *>(args.B) + gl * sizeof(chunk_t);
+    constexpr int QS = (CPL >= 2) ? 2 : 1;  // chunks gathered per nonzero per step
 
     for (int it = blockIdx.x; it < args.n_items; it += gridDim.x) {
         const int item = args.item_ids ? args.item_ids[it] : it;
@@ -85,86 +100,159 @@ __global__ void __launch_bounds__(256) sddmm_rowtile_kernel(const RowTileArgs ar
             const int nr = min(R, r_hi - r0 + 1);
             for (int t = tid; t <= nr; t += blockDim.x) sRp[t] = args.row_ptr[r0 + t];
             if (tid == 0) {
-                const uint32_t bytes = static_cast<uint32_t>(nr) * K * sizeof(ET);
+                const uint32_t bytes = static_cast<uint32_t>(nr) * row_bytes;
                 mbar_expect_tx(&bar, bytes);
-                bulk_g2s(sA, reinterpret_cast<const ET *>(args.A) + static_cast<int64_t>(r0) * K, bytes, &bar);
+                bulk_g2s(sA, reinterpret_cast<const unsigned char *>(args.A) + static_cast<uint64_t>(r0) * row_bytes, bytes, &bar);
             }
             __syncthreads();
+
+            const int64_t s_lo = max(j_lo, static_cast<int64_t>(sRp[0]));
+            const int64_t s_hi = min(j_hi, static_cast<int64_t>(sRp[nr]));
+            int cached_row = -1;      // row whose A chunks sit in areg
+            int64_t cached_end = 0;   // first nonzero index past that row
+            float4 areg[CPL];
+#pragma unroll
+            for (int q = 0; q < CPL; ++q) areg[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+            // 32-aligned warp windows so every col/val/P access is a full 128-byte line.  The column
+            // indices and S values of the NEXT window are requested before the current one is
+            // processed, so the gather of B rows never waits behind an index load.
+            int64_t wb = (s_lo & ~int64_t(31)) + warp * 32;
+            int4 pc0 = make_int4(0, 0, 0, 0), pc1 = make_int4(0, 0, 0, 0);
+            float ps = 0.f;
+            auto request_window = [&](int64_t w) {
+                const int64_t jw = w + lane;
+                if ((w >= s_lo) && (w + 32 <= s_hi)) {
+                    pc0 = __ldcs(reinterpret_cast<const int4 *>(args.col_idx + w + gbase));
+                    pc1 = __ldcs(reinterpret_cast<const int4 *>(args.col_idx + w + gbase + 4));
+                    ps = __ldcs(args.s_val + jw);
+                } else {
+                    pc0.x = 0;
+                    ps = 0.f;
+                    if ((jw >= s_lo) && (jw < s_hi)) {
+                        pc0.x = __ldcs(args.col_idx + jw);
+                        ps = __ldcs(args.s_val + jw);
+                    }
+                }
+            };
+            if (wb < s_hi) request_window(wb);   // in flight while the A rows land
             if (!mbar_wait_bounded(&bar, phase)) {
                 atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
                 return;  // every thread of the CTA waits on the same phase, so all leave together
             }
             phase ^= 1u;
-
-            const int64_t s_lo = max(j_lo, static_cast<int64_t>(sRp[0]));
-            const int64_t s_hi = min(j_hi, static_cast<int64_t>(sRp[nr]));
-            // 32-aligned warp windows so every col/val/P access is a full 128-byte line
-            for (int64_t wb = (s_lo & ~int64_t(31)) + warp * 32; wb < s_hi; wb += nwarps * 32) {
+            for (; wb < s_hi; wb += kRowTileWarps * 32) {
                 const int64_t j = wb + lane;
-                bool valid = (j >= s_lo) && (j < s_hi);
-                int c = 0;
-                float s = 0.f;
-                if (valid) {
-                    c = __ldcs(args.col_idx + j);
-                    s = __ldcs(args.s_val + j);
-                }
-                // row of nonzero j inside the staged slice: largest t with sRp[t] <= j
-                const int jj = static_cast<int>(min(max(j, s_lo), s_hi - 1));
-                int lo = 0, hi = nr;
-                while (hi - lo > 1) {
-                    const int mid = (lo + hi) >> 1;
-                    if (sRp[mid] <= jj) lo = mid; else hi = mid;
-                }
-                const int lr = lo;
-                if (valid && args.skip_tile_bitmap) {
-                    const int64_t bit = static_cast<int64_t>((r0 + lr) >> 6) * args.skip_tiles_per_row + (c >> 6);
-                    if ((args.skip_tile_bitmap[bit >> 5] >> (bit & 31)) & 1u) valid = false;
-                }
-                const unsigned vmask = __ballot_sync(kFullMask, valid);
-                if (vmask == 0u) continue;
+                const bool full = (wb >= s_lo) && (wb + 32 <= s_hi);   // warp-uniform
+                bool valid = full || ((j >= s_lo) && (j < s_hi));
 
+                // ---- column indices of this group's 8 nonzeros, S value of this lane's nonzero ----
+                int ci[8];
+                const float s = ps;
+                if (full) {
+                    ci[0] = pc0.x; ci[1] = pc0.y; ci[2] = pc0.z; ci[3] = pc0.w;
+                    ci[4] = pc1.x; ci[5] = pc1.y; ci[6] = pc1.z; ci[7] = pc1.w;
+                } else {
+                    const int c_own = pc0.x;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ci[i] = __shfl_sync(kFullMask, c_own, gbase + i);  // invalid -> row 0 of B, result unused
+                }
+                if (wb + kRowTileWarps * 32 < s_hi) request_window(wb + kRowTileWarps * 32);
+
+                // ---- row of every nonzero of the window --------------------------------------
+                bool uni;
+                int lr;
+                if (full && cached_row >= 0 && wb + 32 <= cached_end) {
+                    uni = true;
+                    lr = cached_row;
+                } else {
+                    // largest t with sRp[t] <= j (out-of-window lanes are clamped so rows stay monotone)
+                    const int jj = static_cast<int>(min(max(j, s_lo), s_hi - 1));
+                    int lo = 0, hi = nr;
+                    while (hi - lo > 1) {
+                        const int mid = (lo + hi) >> 1;
+                        if (sRp[mid] <= jj) lo = mid; else hi = mid;
+                    }
+                    lr = lo;
+                    const int rf = __shfl_sync(kFullMask, lr, 0), rl = __shfl_sync(kFullMask, lr, 31);
+                    uni = (rf == rl);
+                    if (uni) {
+                        if (rf != cached_row) {
+                            cached_row = rf;
+#pragma unroll
+                            for (int q = 0; q < CPL; ++q) {
+                                const int ch = gl + 8 * q;
+                                areg[q] = (EXACT || ch < nchunks) ? chunk_to_f4(sAc[rf * nchunks + ch]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        }
+                        cached_end = sRp[rf + 1];
+                    }
+                }
+                if (args.skip_tile_bitmap) {
+                    if (valid) {
+                        const int c_own = __ldg(args.col_idx + j);
+                        const int64_t bit = static_cast<int64_t>((r0 + lr) >> 6) * args.skip_tiles_per_row + (c_own >> 6);
+                        if ((args.skip_tile_bitmap[bit >> 5] >> (bit & 31)) & 1u) valid = false;
+                    }
+                    if (__ballot_sync(kFullMask, valid) == 0u) continue;
+                }
+
+                // ---- gather B rows, multiply with A chunks --------------------------------------
                 float acc[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-                int ci[8], ri[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    ci[i] = __shfl_sync(kFullMask, c, gbase + i);
-                    ri[i] = __shfl_sync(kFullMask, lr, gbase + i);
-                }
-                const unsigned gmask = (vmask >> gbase) & 0xffu;
 
-                constexpr int QS = (CPL >= 2) ? 2 : 1;  // chunks gathered per nonzero per step
+                if (uni) {
 #pragma unroll
-                for (int q0 = 0; q0 < CPL; q0 += QS) {
-                    chunk_t bq[8][QS];
+                    for (int q0 = 0; q0 < CPL; q0 += QS) {
+                        chunk_t bq[8][QS];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-#pragma unroll
-                        for (int qq = 0; qq < QS; ++qq) {
-                            const int ch = gl + 8 * (q0 + qq);
-                            if (((gmask >> i) & 1u) && ch < nchunks) {
-                                bq[i][qq] = ldg_chunk(Bc + static_cast<int64_t>(ci[i]) * nchunks + ch);
-                            } else {
-                                bq[i][qq] = zero_chunk(chunk_t());
-                            }
-                        }
-                    }
-                    int cur = -1;
-                    float4 a[QS];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        if (ri[i] != cur) {
-                            cur = ri[i];
-                            const chunk_t *sArow = reinterpret_cast<const chunk_t *>(sA) + static_cast<int64_t>(cur) * nchunks;
+                        for (int i = 0; i < 8; ++i) {
+                            const unsigned char *brow = Bl + static_cast<uint64_t>(static_cast<uint32_t>(ci[i])) * row_bytes;
 #pragma unroll
                             for (int qq = 0; qq < QS; ++qq) {
                                 const int ch = gl + 8 * (q0 + qq);
-                                a[qq] = (ch < nchunks) ? chunk_to_f4(sArow[ch]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                bq[i][qq] = (EXACT || ch < nchunks)
+                                                ? ldg_chunk(reinterpret_cast<const chunk_t *>(brow) + 8 * (q0 + qq))
+                                                : zero_chunk(chunk_t());
                             }
                         }
 #pragma unroll
-                        for (int qq = 0; qq < QS; ++qq) acc[i] = dot4(a[qq], chunk_to_f4(bq[i][qq]), acc[i]);
+                        for (int i = 0; i < 8; ++i)
+#pragma unroll
+                            for (int qq = 0; qq < QS; ++qq) acc[i] = dot4(areg[q0 + qq], chunk_to_f4(bq[i][qq]), acc[i]);
+                    }
+                } else {
+                    // per-nonzero row offsets (in chunks) of this group's 8 nonzeros, through a warp-private smem line
+                    __syncwarp();
+                    sRowOff[warp][lane] = lr * nchunks;  // row start in chunks
+                    __syncwarp();
+                    const int4 o0 = *reinterpret_cast<const int4 *>(&sRowOff[warp][gbase]);
+                    const int4 o1 = *reinterpret_cast<const int4 *>(&sRowOff[warp][gbase + 4]);
+                    const int ro[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+                    for (int q0 = 0; q0 < CPL; q0 += QS) {
+                        chunk_t bq[8][QS];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const unsigned char *brow = Bl + static_cast<uint64_t>(static_cast<uint32_t>(ci[i])) * row_bytes;
+#pragma unroll
+                            for (int qq = 0; qq < QS; ++qq) {
+                                const int ch = gl + 8 * (q0 + qq);
+                                bq[i][qq] = (EXACT || ch < nchunks)
+                                                ? ldg_chunk(reinterpret_cast<const chunk_t *>(brow) + 8 * (q0 + qq))
+                                                : zero_chunk(chunk_t());
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                            for (int qq = 0; qq < QS; ++qq) {
+                                const int ch = gl + 8 * (q0 + qq);
+                                const float4 a = (EXACT || ch < nchunks) ? chunk_to_f4(sAc[ro[i] + ch]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                acc[i] = dot4(a, chunk_to_f4(bq[i][qq]), acc[i]);
+                            }
+                        }
                     }
                 }
                 const float dot = group8_transpose_reduce(acc, gl);

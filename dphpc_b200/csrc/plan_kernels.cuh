@@ -22,6 +22,7 @@ struct PlanCounters {
     int bad_row_ptr;   // row_ptr not monotone / wrong ends
     int bad_col;       // column index outside [0, N)
     int unsorted_cols; // a column index smaller than its predecessor inside a row
+    int dup_cols;      // a column index equal to its predecessor inside a row
     int bad_coo;       // COO row index out of range or decreasing
     int dense_tiles;
     int rowgroups;
@@ -80,7 +81,11 @@ __global__ void k_col_scan(const int32_t *__restrict__ col, int64_t nnz, int32_t
         }
         if (!touched[c]) touched[c] = 1;
         const bool is_start = (row_start_bits[j >> 5] >> (j & 31)) & 1u;
-        if (!is_start && j > 0 && col[j - 1] > c) pc->unsorted_cols = 1;
+        if (!is_start && j > 0) {
+            const int prev = col[j - 1];
+            if (prev > c) pc->unsorted_cols = 1;
+            if (prev == c) pc->dup_cols = 1;
+        }
     }
 }
 
@@ -134,6 +139,116 @@ __global__ void k_item_rows(const int32_t *__restrict__ rp, int32_t M, int64_t n
         out.y = lo;
     }
     item_rows[t] = out;
+}
+
+// ---- dense-tile detection (64x64 aligned tiles at least half full) -----------------------
+// One warp per row: lanes take contiguous chunks of the (sorted) row so that runs of
+// nonzeros inside one tile are counted locally and flushed with one atomic per run.
+__global__ void k_tile_count(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t tiles_per_row,
+                             int32_t *__restrict__ counts) {
+    const int64_t w = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= M) return;
+    const int a = rp[w], b = rp[w + 1];
+    const int len = b - a;
+    if (len == 0) return;
+    const int per = (len + 31) >> 5;
+    const int lo = a + lane * per, hi = min(b, lo + per);
+    const int64_t base = static_cast<int64_t>(w >> 6) * tiles_per_row;
+    int cur = -1, run = 0;
+    for (int j = lo; j < hi; ++j) {
+        const int t = col[j] >> 6;
+        if (t != cur) {
+            if (run) atomicAdd(&counts[base + cur], run);
+            cur = t;
+            run = 0;
+        }
+        ++run;
+    }
+    if (run) atomicAdd(&counts[base + cur], run);
+}
+
+// tiles with >= min_count nonzeros: set their bit, append them to the dense list
+__global__ void k_tile_select(const int32_t *__restrict__ counts, int64_t n_tiles, int32_t min_count, uint32_t *__restrict__ bitmap,
+                              int32_t *__restrict__ dense_ids, int32_t cap, PlanCounters *__restrict__ pc) {
+    for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < n_tiles;
+         t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int c = counts[t];
+        if (c >= min_count) {
+            const int slot = atomicAdd(&pc->dense_tiles, 1);
+            if (slot < cap) {
+                dense_ids[slot] = static_cast<int32_t>(t);
+                atomicOr(&bitmap[t >> 5], 1u << (t & 31));
+                atomicAdd(&pc->dense_nnz, static_cast<unsigned long long>(c));
+            }
+        }
+    }
+}
+
+// one thread per (dense tile, row): first CSR position of the row inside the tile's column
+// range, presence mask of its 64 columns; also credits the covered nonzeros to their work items
+template <typename Desc>
+__global__ void k_tile_rows(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t tiles_per_row,
+                            const int32_t *__restrict__ dense_ids, int32_t n_dense, Desc *__restrict__ descs, int32_t item_nnz,
+                            int32_t *__restrict__ item_covered) {
+    const int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (g >= static_cast<int64_t>(n_dense) * 64) return;
+    const int t = static_cast<int>(g >> 6), r = static_cast<int>(g & 63);
+    const int id = dense_ids[t];
+    const int row = (id / tiles_per_row) * 64 + r;
+    const int c0 = (id % tiles_per_row) * 64;
+    int start = 0;
+    unsigned long long mask = 0ull;
+    if (row < M) {
+        int lo = rp[row], hi = rp[row + 1];
+        const int end = hi;
+        while (lo < hi) {  // first position with col >= c0
+            const int mid = (lo + hi) >> 1;
+            if (col[mid] < c0) lo = mid + 1; else hi = mid;
+        }
+        start = lo;
+        int n = 0;
+        for (int j = lo; j < end; ++j) {
+            const int c = col[j] - c0;
+            if (c >= 64) break;
+            mask |= 1ull << c;
+            ++n;
+        }
+        // credit [start, start+n) to the work items it overlaps
+        int j = start, left = n;
+        while (left > 0) {
+            const int item = j / item_nnz;
+            const int take = min(left, (item + 1) * item_nnz - j);
+            atomicAdd(&item_covered[item], take);
+            j += take;
+            left -= take;
+        }
+    }
+    descs[t].start[r] = start;
+    descs[t].mask[r] = mask;
+}
+
+// work items that still hold nonzeros outside the dense tiles
+__global__ void k_residual_items(const int32_t *__restrict__ item_covered, int32_t n_items, int32_t item_nnz, int64_t nnz,
+                                 int32_t *__restrict__ item_ids, PlanCounters *__restrict__ pc) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_items) return;
+    const int64_t size = min(nnz, static_cast<int64_t>(t + 1) * item_nnz) - static_cast<int64_t>(t) * item_nnz;
+    if (item_covered[t] < size) item_ids[atomicAdd(&pc->residual_items, 1)] = t;
+}
+
+// hi/lo split for the 3-product tf32 scheme: hi = tf32(x), lo = tf32(x - hi)
+__global__ void k_split_tf32(const float *__restrict__ in, float *__restrict__ hi, float *__restrict__ lo, int64_t n) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const float x = in[i];
+        uint32_t h, l;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+        const float hf = __uint_as_float(h);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hf));
+        hi[i] = hf;
+        lo[i] = __uint_as_float(l);
+    }
 }
 
 __global__ void k_f32_to_bf16(const float *__restrict__ in, __nv_bfloat16 *__restrict__ out, int64_t n) {
