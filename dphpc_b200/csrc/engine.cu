@@ -45,13 +45,21 @@ struct Carve {
 
 }  // namespace
 
+#ifdef SDDMM_DENSE_TRACE
+unsigned long long *sddmm_trace_ptr = nullptr;
+#endif
+
 struct sddmm_b200_engine {
     int device = 0;
     int mode = SDDMM_B200_FP32;
     uint32_t flags = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t side_stream = nullptr;   // residual row-tile kernel runs here, concurrently with the dense tiles
     static constexpr int kMaxKernels = 4;
-    cudaEvent_t ev[kMaxKernels + 1] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // ev[i], ev[i+1] bracket kernel i
+    cudaEvent_t ev_begin[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};  // per kernel, on the stream it runs on
+    cudaEvent_t ev_end[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t ev_run0 = nullptr, ev_run1 = nullptr;   // whole run(), on the main stream
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     const char *kernel_name[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};
     int kernels_launched = 0;
     int sm_count = 148;
@@ -86,8 +94,8 @@ struct sddmm_b200_engine {
     DenseTileDesc *d_dense_descs = nullptr;
     int32_t *d_item_covered = nullptr;
     int32_t *d_item_ids = nullptr;
-    float *d_Ahi = nullptr, *d_Alo = nullptr, *d_Bhi = nullptr, *d_Blo = nullptr;
-    CUtensorMap map_a_hi, map_b_hi, map_a_lo, map_b_lo;
+    float *d_Ax = nullptr, *d_Bx = nullptr;   // fp32_tc: [lo|hi|hi] and [hi|lo|hi] rows, 3K long
+    CUtensorMap map_a, map_b;
     int32_t n_dense = 0;
     int32_t n_residual_items = 0;
 
@@ -214,10 +222,8 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     const size_t o_dd = e->dense_possible ? c.take(static_cast<size_t>(e->dense_cap) * sizeof(DenseTileDesc)) : 0;
     const size_t o_ic = e->dense_possible ? c.take(static_cast<size_t>(std::max(n_items, 1)) * 4) : 0;
     const size_t o_ii = e->dense_possible ? c.take(static_cast<size_t>(std::max(n_items, 1)) * 4) : 0;
-    const size_t o_ahi = split ? c.take(M * K * 4) : 0;
-    const size_t o_alo = split ? c.take(M * K * 4) : 0;
-    const size_t o_bhi = split ? c.take(N * K * 4) : 0;
-    const size_t o_blo = split ? c.take(N * K * 4) : 0;
+    const size_t o_ax = split ? c.take(M * K * 12) : 0;
+    const size_t o_bx = split ? c.take(N * K * 12) : 0;
     int st = ensure_arena(e, c.off);
     if (st) return st;
     char *b = e->arena.base;
@@ -227,10 +233,8 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     e->d_dense_descs = e->dense_possible ? reinterpret_cast<DenseTileDesc *>(b + o_dd) : nullptr;
     e->d_item_covered = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_ic) : nullptr;
     e->d_item_ids = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_ii) : nullptr;
-    e->d_Ahi = split ? reinterpret_cast<float *>(b + o_ahi) : nullptr;
-    e->d_Alo = split ? reinterpret_cast<float *>(b + o_alo) : nullptr;
-    e->d_Bhi = split ? reinterpret_cast<float *>(b + o_bhi) : nullptr;
-    e->d_Blo = split ? reinterpret_cast<float *>(b + o_blo) : nullptr;
+    e->d_Ax = split ? reinterpret_cast<float *>(b + o_ax) : nullptr;
+    e->d_Bx = split ? reinterpret_cast<float *>(b + o_bx) : nullptr;
     e->d_rp = reinterpret_cast<int32_t *>(b + o_rp);
     e->d_col = reinterpret_cast<int32_t *>(b + o_col);
     e->d_sval = reinterpret_cast<float *>(b + o_sv);
@@ -262,9 +266,9 @@ int choose_item_nnz(const sddmm_b200_engine *e) {
 
 int convert_storage(sddmm_b200_engine *e) {
     const int cap = e->sm_count * 8;
-    if (e->d_Ahi) {  // hi/lo operands of the 3-product tensor-core scheme
-        k_split_tf32<<<grid_for(e->M * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_A32, e->d_Ahi, e->d_Alo, e->M * e->K);
-        k_split_tf32<<<grid_for(e->N * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_B32, e->d_Bhi, e->d_Blo, e->N * e->K);
+    if (e->d_Ax) {  // hi/lo-concatenated operands of the fp32-grade tensor-core mode
+        k_split_concat_tf32<<<grid_for(e->M * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_A32, e->d_Ax, e->M, static_cast<int32_t>(e->K), 1);
+        k_split_concat_tf32<<<grid_for(e->N * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_B32, e->d_Bx, e->N, static_cast<int32_t>(e->K), 0);
         CU_TRY(e, cudaGetLastError());
     }
     if (e->mode != SDDMM_B200_BF16) return SDDMM_B200_OK;
@@ -330,10 +334,9 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
     CU_TRY(e, cudaStreamSynchronize(s));
     const bool split = e->mode == SDDMM_B200_FP32_TC;
-    int st = make_operand_map(e, &e->map_a_hi, split ? e->d_Ahi : e->d_A32, e->M, e->K);
-    if (!st) st = make_operand_map(e, &e->map_b_hi, split ? e->d_Bhi : e->d_B32, e->N, e->K);
-    if (!st) st = make_operand_map(e, &e->map_a_lo, split ? e->d_Alo : e->d_A32, e->M, e->K);
-    if (!st) st = make_operand_map(e, &e->map_b_lo, split ? e->d_Blo : e->d_B32, e->N, e->K);
+    const int64_t kx = split ? 3 * e->K : e->K;
+    int st = make_operand_map(e, &e->map_a, split ? e->d_Ax : e->d_A32, e->M, kx);
+    if (!st) st = make_operand_map(e, &e->map_b, split ? e->d_Bx : e->d_B32, e->N, kx);
     if (st) return st;
     CU_TRY(e, cudaFuncSetAttribute(sddmm_dense_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DenseSmem::kDynamicBytes));
     e->n_dense = n_dense;
@@ -480,12 +483,16 @@ int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t
     return SDDMM_B200_OK;
 }
 
-// event after kernel `idx` (ev[0] is recorded by run() before the first launch)
-int mark_kernel(sddmm_b200_engine *e, const char *name) {
+// events right before / right after kernel number `kernels_launched`, on the stream it is launched on
+int begin_kernel(sddmm_b200_engine *e, cudaStream_t st) {
+    CU_TRY(e, cudaEventRecord(e->ev_begin[e->kernels_launched], st));
+    return SDDMM_B200_OK;
+}
+int mark_kernel(sddmm_b200_engine *e, const char *name, cudaStream_t st) {
     CU_TRY(e, cudaGetLastError());
     const int idx = e->kernels_launched;
     e->kernel_name[idx] = name;
-    CU_TRY(e, cudaEventRecord(e->ev[idx + 1], e->stream));
+    CU_TRY(e, cudaEventRecord(e->ev_end[idx], st));
     e->kernels_launched = idx + 1;
     return SDDMM_B200_OK;
 }
@@ -494,20 +501,38 @@ int launch_all(sddmm_b200_engine *e) {
     const sddmm_b200_plan_info &p = e->plan;
     e->kernels_launched = 0;
     if (e->nnz == 0) return SDDMM_B200_OK;
+    int st = SDDMM_B200_OK;
     if (e->use_scalar) {
+        if ((st = begin_kernel(e, e->stream))) return st;
         sddmm_scalar_kernel<<<p.rowtile_grid, kBlock, 0, e->stream>>>(e->d_rp, e->d_col, e->d_sval, e->d_pval, e->d_A32, e->d_B32,
                                                                       static_cast<int32_t>(e->M), static_cast<int32_t>(e->K), e->nnz);
-        return mark_kernel(e, "sddmm_scalar_kernel");
+        return mark_kernel(e, "sddmm_scalar_kernel", e->stream);
+    }
+    // the two kernels write disjoint nonzeros: when both run, the row-tile kernel goes to the side stream
+    static const bool no_side = std::getenv("SDDMM_B200_NO_SIDE_STREAM") != nullptr;   // tuning / debugging knob
+    const bool both = e->n_dense > 0 && e->n_residual_items > 0 && !no_side;
+    cudaStream_t rt_stream = both ? e->side_stream : e->stream;
+    if (both) {
+        CU_TRY(e, cudaEventRecord(e->ev_fork, e->stream));
+        CU_TRY(e, cudaStreamWaitEvent(e->side_stream, e->ev_fork, 0));
     }
     if (e->n_dense > 0) {
         DenseArgs d;
         d.tile_ids = e->d_dense_ids; d.descs = e->d_dense_descs; d.s_val = e->d_sval; d.p_val = e->d_pval; d.err = e->d_err;
-        d.n_tiles = e->n_dense; d.tiles_per_row = e->tiles_per_row; d.k_blocks = static_cast<int32_t>(e->K / 32);
-        d.split = e->mode == SDDMM_B200_FP32_TC ? 1 : 0;
-        sddmm_dense_tile_kernel<<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a_hi, e->map_b_hi,
-                                                                                                  e->map_a_lo, e->map_b_lo);
-        int st = mark_kernel(e, "sddmm_dense_tile_kernel");
-        if (st) return st;
+        d.n_tiles = e->n_dense; d.tiles_per_row = e->tiles_per_row;
+        d.k_blocks = static_cast<int32_t>((e->mode == SDDMM_B200_FP32_TC ? 3 * e->K : e->K) / 32);
+        d.reserved = 0;
+        d.nnz = e->nnz;
+        d.trace = nullptr;
+#ifdef SDDMM_DENSE_TRACE
+        static unsigned long long *trace_buf = nullptr;
+        if (!trace_buf) { cudaMalloc(&trace_buf, 4 * 6 * 16 * 8); sddmm_trace_ptr = trace_buf; }
+        cudaMemsetAsync(trace_buf, 0, 4 * 6 * 16 * 8, e->stream);
+        d.trace = trace_buf;
+#endif
+        if ((st = begin_kernel(e, e->stream))) return st;
+        sddmm_dense_tile_kernel<<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a, e->map_b);
+        if ((st = mark_kernel(e, "sddmm_dense_tile_kernel", e->stream))) return st;
         if (e->n_residual_items == 0) return SDDMM_B200_OK;
     }
     RowTileArgs a;
@@ -519,14 +544,20 @@ int launch_all(sddmm_b200_engine *e) {
     a.err = e->d_err; a.nnz = e->nnz;
     a.M = static_cast<int32_t>(e->M); a.K = static_cast<int32_t>(e->K);
     a.n_items = p.rowtile_items; a.item_nnz = p.rowtile_item_nnz; a.rows_per_stage = p.rowtile_rows_per_stage;
+    if ((st = begin_kernel(e, rt_stream))) return st;
     if (e->mode == SDDMM_B200_BF16) {
         a.A = e->d_A16; a.B = e->d_B16;
-        pick_rowtile<__nv_bfloat16>(e->cpl, e->K == 32 * e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, e->stream>>>(a);
+        pick_rowtile<__nv_bfloat16>(e->cpl, e->K == 32 * e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, rt_stream>>>(a);
     } else {
         a.A = e->d_A32; a.B = e->d_B32;
-        pick_rowtile<float>(e->cpl, e->K == 32 * e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, e->stream>>>(a);
+        pick_rowtile<float>(e->cpl, e->K == 32 * e->cpl)<<<p.rowtile_grid, kBlock, p.rowtile_smem_bytes, rt_stream>>>(a);
     }
-    return mark_kernel(e, "sddmm_rowtile_kernel");
+    if ((st = mark_kernel(e, "sddmm_rowtile_kernel", rt_stream))) return st;
+    if (both) {
+        CU_TRY(e, cudaEventRecord(e->ev_join, e->side_stream));
+        CU_TRY(e, cudaStreamWaitEvent(e->stream, e->ev_join, 0));
+    }
+    return SDDMM_B200_OK;
 }
 
 }  // namespace
@@ -558,7 +589,12 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     DeviceGuard g(device);
     bool ok = g.ok;
     ok = ok && cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess;
-    for (int i = 0; i <= sddmm_b200_engine::kMaxKernels; ++i) ok = ok && cudaEventCreate(&e->ev[i]) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&e->side_stream, cudaStreamNonBlocking) == cudaSuccess;
+    for (int i = 0; i < sddmm_b200_engine::kMaxKernels; ++i)
+        ok = ok && cudaEventCreate(&e->ev_begin[i]) == cudaSuccess && cudaEventCreate(&e->ev_end[i]) == cudaSuccess;
+    ok = ok && cudaEventCreate(&e->ev_run0) == cudaSuccess && cudaEventCreate(&e->ev_run1) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess;
     ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&e->h_err), sizeof(int32_t), cudaHostAllocDefault) == cudaSuccess;
     if (!ok) {
@@ -578,8 +614,14 @@ int sddmm_b200_destroy(sddmm_b200_engine *e) {
         if (e->stream) cudaStreamSynchronize(e->stream);
         if (e->arena.base) cudaFree(e->arena.base);
         if (e->h_err) cudaFreeHost(e->h_err);
-        for (int i = 0; i <= sddmm_b200_engine::kMaxKernels; ++i)
-            if (e->ev[i]) cudaEventDestroy(e->ev[i]);
+        if (e->side_stream) cudaStreamSynchronize(e->side_stream);
+        for (int i = 0; i < sddmm_b200_engine::kMaxKernels; ++i) {
+            if (e->ev_begin[i]) cudaEventDestroy(e->ev_begin[i]);
+            if (e->ev_end[i]) cudaEventDestroy(e->ev_end[i]);
+        }
+        for (cudaEvent_t ev : {e->ev_run0, e->ev_run1, e->ev_fork, e->ev_join})
+            if (ev) cudaEventDestroy(ev);
+        if (e->side_stream) cudaStreamDestroy(e->side_stream);
         if (e->stream) cudaStreamDestroy(e->stream);
     }
     delete e;
@@ -652,9 +694,33 @@ int sddmm_b200_run(sddmm_b200_engine *e) {
     if (!e) return SDDMM_B200_ERR_ARG;
     if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "run before upload");
     DeviceGuard g(e->device);
-    CU_TRY(e, cudaEventRecord(e->ev[0], e->stream));
+    CU_TRY(e, cudaEventRecord(e->ev_run0, e->stream));
     int st = launch_all(e);
     if (st) return st;
+    CU_TRY(e, cudaEventRecord(e->ev_run1, e->stream));
+#ifdef SDDMM_DENSE_TRACE
+    if (e->n_dense > 0 && std::getenv("SDDMM_B200_TRACE_FILE")) {
+        // debugging aid: dump the per-CTA time stamps of the dense-tile kernel
+        static unsigned long long host[4 * 6 * 16];
+        cudaStreamSynchronize(e->stream);
+        void *dev = nullptr;
+        // the buffer address is the static in launch_all; fetch it through a second static
+        dev = sddmm_trace_ptr;
+        if (dev) {
+            cudaMemcpy(host, dev, sizeof(host), cudaMemcpyDeviceToHost);
+            FILE *f = std::fopen(std::getenv("SDDMM_B200_TRACE_FILE"), "w");
+            if (f) {
+                for (int c = 0; c < 4; ++c)
+                    for (int j = 0; j < 6; ++j) {
+                        std::fprintf(f, "cta %d job %d:", c, j);
+                        for (int k = 0; k < 11; ++k) std::fprintf(f, " %llu", host[(c * 6 + j) * 16 + k]);
+                        std::fprintf(f, "\n");
+                    }
+                std::fclose(f);
+            }
+        }
+    }
+#endif
     CU_TRY(e, cudaMemcpyAsync(e->h_err, e->d_err, sizeof(int32_t), cudaMemcpyDeviceToHost, e->stream));
     e->ran = true;
     return SDDMM_B200_OK;
@@ -691,8 +757,8 @@ int sddmm_b200_last_run_ms(sddmm_b200_engine *e, float *ms) {
     DeviceGuard g(e->device);
     *ms = 0.f;
     if (e->kernels_launched == 0) return SDDMM_B200_OK;
-    CU_TRY(e, cudaEventSynchronize(e->ev[e->kernels_launched]));
-    CU_TRY(e, cudaEventElapsedTime(ms, e->ev[0], e->ev[e->kernels_launched]));
+    CU_TRY(e, cudaEventSynchronize(e->ev_run1));
+    CU_TRY(e, cudaEventElapsedTime(ms, e->ev_run0, e->ev_run1));
     return SDDMM_B200_OK;
 }
 
@@ -701,8 +767,8 @@ int sddmm_b200_last_kernel_ms(sddmm_b200_engine *e, int index, float *ms, const 
     if (!e->ran) return fail(e, SDDMM_B200_ERR_STATE, "last_kernel_ms before run");
     if (index < 0 || index >= e->kernels_launched) return fail(e, SDDMM_B200_ERR_ARG, "kernel index %d of %d", index, e->kernels_launched);
     DeviceGuard g(e->device);
-    CU_TRY(e, cudaEventSynchronize(e->ev[index + 1]));
-    CU_TRY(e, cudaEventElapsedTime(ms, e->ev[index], e->ev[index + 1]));
+    CU_TRY(e, cudaEventSynchronize(e->ev_end[index]));
+    CU_TRY(e, cudaEventElapsedTime(ms, e->ev_begin[index], e->ev_end[index]));
     if (name) *name = e->kernel_name[index];
     return SDDMM_B200_OK;
 }

@@ -23,9 +23,12 @@
 //                     written in CSR order in contiguous runs; col_idx is not
 //                     read at all (the mask, built once per upload, replaces it).
 //
-// Modes: 1 product (tf32 operands, rel 1e-2) or 3 products with a hi/lo split
-// of A and B (hi*hi + hi*lo + lo*hi, rel ~5e-7: fp32-grade results).
-// K must be a multiple of 32; every 32-wide k-block is one 128-byte swizzle atom.
+// Modes: plain tf32 operands (rel 1e-2), or fp32-grade results from tf32 tensor cores: the
+// engine stores A' = [A_lo | A_hi | A_hi] and B' = [B_hi | B_lo | B_hi] (hi = tf32(x),
+// lo = tf32(x - hi)), so that A'.B'^T = lo*hi + hi*lo + hi*hi is just a 3x longer K for this
+// kernel -- one code path for both modes.
+// K' must be a multiple of 32; every 32-wide k-block is one 128-byte swizzle atom.  Operand
+// k-blocks go through a two-stage ring so the TMA of one block overlaps the MMA of the other.
 //
 // Every wait on an mbarrier is bounded; on a timeout the CTA sets the error
 // word, stops issuing work, and still frees its tensor memory.
@@ -60,22 +63,35 @@ struct DenseArgs {
     int32_t *err;
     int32_t n_tiles;
     int32_t tiles_per_row;
-    int32_t k_blocks;               // K / 32
-    int32_t split;                  // 0: one tf32 product, 1: three products on hi/lo operands
+    int32_t k_blocks;               // operand row length / 32
+    int32_t reserved;
+    int64_t nnz;                    // bound of every S.val / P.val position (checked builds only)
+    unsigned long long *trace;      // SDDMM_DENSE_TRACE builds: per-CTA time stamps; nullptr otherwise
 };
+
+#ifdef SDDMM_DENSE_TRACE
+__device__ __forceinline__ unsigned long long dense_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define DENSE_STAMP(slot) do { if (args.trace && blockIdx.x < 4 && jb < 6) args.trace[(blockIdx.x * 6 + jb) * 16 + (slot)] = dense_now(); } while (0)
+#define DENSE_STAMP_E(slot) do { if (tid == 0) DENSE_STAMP(slot); } while (0)
+#else
+#define DENSE_STAMP(slot) do { } while (0)
+#define DENSE_STAMP_E(slot) do { } while (0)
+#endif
 
 // shared memory carve-up (dynamic, 1024-byte aligned by hand)
 struct DenseSmem {
-    static constexpr uint32_t kAhi = 0;
-    static constexpr uint32_t kBhi = kAhi + kOperandBytes;
-    static constexpr uint32_t kAlo = kBhi + kOperandBytes;
-    static constexpr uint32_t kBlo = kAlo + kOperandBytes;
-    static constexpr uint32_t kAcc = kBlo + kOperandBytes;
+    static constexpr uint32_t kStageBytes = 2 * kOperandBytes;   // A block + B block
+    static constexpr uint32_t kStage0 = 0;                        // stage s: A at s*kStageBytes, B right after it
+    static constexpr uint32_t kAcc = 2 * kStageBytes;
     static constexpr uint32_t kAccBytes = 128 * kDenseAccStride * 4;
     static constexpr uint32_t kStart = kAcc + kAccBytes;          // 128 int32
     static constexpr uint32_t kMask = kStart + 128 * 4;           // 128 u64 (8-byte aligned: kAccBytes % 8 == 0)
-    static constexpr uint32_t kBars = kMask + 128 * 8;            // 4 mbarriers
-    static constexpr uint32_t kTmemPtr = kBars + 4 * 8;
+    static constexpr uint32_t kBars = kMask + 128 * 8;            // 6 mbarriers
+    static constexpr uint32_t kTmemPtr = kBars + 6 * 8;
     static constexpr uint32_t kTotal = kTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kTotal + 1024;      // slack for the manual 1024-byte alignment
 };
@@ -116,17 +132,21 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// TMEM -> registers, 32 lanes x 32 columns.  The load is asynchronous: its destination registers
+// are only defined after tcgen05.wait::ld, so both instructions live in ONE asm statement --
+// otherwise the compiler is free to consume or recycle the registers in between.
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
           "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
           "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        : "r"(taddr)
+        : "memory");
 }
 
 __device__ __forceinline__ void epi_barrier() {  // the 8 epilogue warps only
@@ -134,16 +154,15 @@ __device__ __forceinline__ void epi_barrier() {  // the 8 epilogue warps only
 }
 
 __global__ void __launch_bounds__(kDenseThreads, 2)
-sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMap map_a_hi,
-                        const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                        const __grid_constant__ CUtensorMap map_b_lo) {
+sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMap map_a,
+                        const __grid_constant__ CUtensorMap map_b) {
     extern __shared__ unsigned char dense_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(dense_smem_raw) + 1023) & ~uintptr_t(1023));
     float *sAcc = reinterpret_cast<float *>(smem + DenseSmem::kAcc);
     int32_t *sStart = reinterpret_cast<int32_t *>(smem + DenseSmem::kStart);
     unsigned long long *sMask = reinterpret_cast<unsigned long long *>(smem + DenseSmem::kMask);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + DenseSmem::kBars);
-    uint64_t *ops_full = &bars[0], *ops_free = &bars[1], *acc_full = &bars[2], *acc_free = &bars[3];
+    uint64_t *ops_full = &bars[0], *ops_free = &bars[2], *acc_full = &bars[4], *acc_free = &bars[5];   // ops_*: one per stage
     uint32_t *tmem_ptr_smem = reinterpret_cast<uint32_t *>(smem + DenseSmem::kTmemPtr);
 
     const int tid = threadIdx.x;
@@ -152,13 +171,16 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     const int n_jobs = (args.n_tiles + 1) >> 1;
 
     if (tid == 0) {
-        mbar_init(ops_full, 1);
-        mbar_init(ops_free, 1);
+        mbar_init(&ops_full[0], 1);
+        mbar_init(&ops_full[1], 1);
+        mbar_init(&ops_free[0], 1);
+        mbar_init(&ops_free[1], 1);
         mbar_init(acc_full, 1);
         mbar_init(acc_free, kDenseEpiWarps);
         fence_mbar_init();
     }
     if (warp == 0) {  // one warp allocates the tensor memory for the CTA
+        __syncwarp();  // lane 0 comes out of the barrier-init branch: re-converge before the warp-wide alloc
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -170,56 +192,62 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
 
     if (warp == kDenseEpiWarps) {
         // ===================== producer + MMA issuer (one thread) =====================
+        // Iterations = (job, k-block) pairs of this CTA in order.  Iteration `it` uses operand stage
+        // it & 1; its TMA is issued one iteration ahead of its MMA.
         if (lane == 0) {
-            uint32_t it = 0;  // k-block iterations issued so far (phase of ops_full / ops_free)
-            uint32_t jb = 0;  // jobs issued so far (phase of acc_free)
+            const int kbs = args.k_blocks;
+            const int my_jobs = (n_jobs - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+            const uint32_t total = static_cast<uint32_t>(my_jobs) * static_cast<uint32_t>(kbs);
             bool ok = true;
-            const uint32_t a_hi = smem_u32(smem + DenseSmem::kAhi), b_hi = smem_u32(smem + DenseSmem::kBhi);
-            const uint32_t a_lo = smem_u32(smem + DenseSmem::kAlo), b_lo = smem_u32(smem + DenseSmem::kBlo);
-            for (int job = blockIdx.x; job < n_jobs && ok; job += gridDim.x, ++jb) {
+
+            auto issue_tma = [&](uint32_t it) -> bool {
+                const uint32_t st = it & 1u, ph = (it >> 1) & 1u;
+                const int job = static_cast<int>(blockIdx.x) + static_cast<int>(it / kbs) * static_cast<int>(gridDim.x);
+                const int kb = static_cast<int>(it % kbs);
                 const int t0 = args.tile_ids[2 * job];
-                const bool has1 = (2 * job + 1) < args.n_tiles;
-                const int t1 = has1 ? args.tile_ids[2 * job + 1] : t0;
+                const int t1 = ((2 * job + 1) < args.n_tiles) ? args.tile_ids[2 * job + 1] : t0;
                 const int r0 = (t0 / args.tiles_per_row) * kDenseTile, c0 = (t0 % args.tiles_per_row) * kDenseTile;
                 const int r1 = (t1 / args.tiles_per_row) * kDenseTile, c1 = (t1 % args.tiles_per_row) * kDenseTile;
-                for (int kb = 0; kb < args.k_blocks && ok; ++kb, ++it) {
-                    // operands of the previous iteration fully consumed by the tensor core?
-                    if (!mbar_wait_bounded(ops_free, (it & 1u) ^ 1u)) { ok = false; break; }
-                    const uint32_t bytes = (args.split ? 4u : 2u) * kOperandBytes;
-                    mbar_expect_tx(ops_full, bytes);
-                    const int x = kb * 32;
-                    tma_load_2d(smem + DenseSmem::kAhi, &map_a_hi, x, r0, ops_full);
-                    tma_load_2d(smem + DenseSmem::kAhi + kHalfOperandBytes, &map_a_hi, x, r1, ops_full);
-                    tma_load_2d(smem + DenseSmem::kBhi, &map_b_hi, x, c0, ops_full);
-                    tma_load_2d(smem + DenseSmem::kBhi + kHalfOperandBytes, &map_b_hi, x, c1, ops_full);
-                    if (args.split) {
-                        tma_load_2d(smem + DenseSmem::kAlo, &map_a_lo, x, r0, ops_full);
-                        tma_load_2d(smem + DenseSmem::kAlo + kHalfOperandBytes, &map_a_lo, x, r1, ops_full);
-                        tma_load_2d(smem + DenseSmem::kBlo, &map_b_lo, x, c0, ops_full);
-                        tma_load_2d(smem + DenseSmem::kBlo + kHalfOperandBytes, &map_b_lo, x, c1, ops_full);
-                    }
-                    if (!mbar_wait_bounded(ops_full, it & 1u)) { ok = false; break; }
-                    if (kb == 0) {
-                        // accumulator drained by the epilogue of the previous job?
-                        if (!mbar_wait_bounded(acc_free, (jb & 1u) ^ 1u)) { ok = false; break; }
-                    }
-                    tcgen05_fence_after();
-                    uint32_t accumulate = (kb > 0) ? 1u : 0u;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {  // 4 k-steps of 8 tf32 = 32 bytes inside the swizzle atom
-                        const uint32_t adv = static_cast<uint32_t>(ks) * 32u;
-                        if (args.split) {
-                            umma_tf32(tmem_base, umma_smem_desc(a_lo + adv), umma_smem_desc(b_hi + adv), accumulate);
-                            umma_tf32(tmem_base, umma_smem_desc(a_hi + adv), umma_smem_desc(b_lo + adv), 1u);
-                            umma_tf32(tmem_base, umma_smem_desc(a_hi + adv), umma_smem_desc(b_hi + adv), 1u);
-                        } else {
-                            umma_tf32(tmem_base, umma_smem_desc(a_hi + adv), umma_smem_desc(b_hi + adv), accumulate);
-                        }
-                        accumulate = 1u;
-                    }
-                    umma_commit(ops_free);  // arrives once the MMAs above have read their operands
+                // stage free again?  (consumed by the MMAs of iteration it - 2)
+                if (!mbar_wait_bounded(&ops_free[st], ph ^ 1u)) return false;
+                unsigned char *sa = smem + DenseSmem::kStage0 + st * DenseSmem::kStageBytes;
+                unsigned char *sb = sa + kOperandBytes;
+                mbar_expect_tx(&ops_full[st], DenseSmem::kStageBytes);
+                const int x = kb * 32;
+                tma_load_2d(sa, &map_a, x, r0, &ops_full[st]);
+                tma_load_2d(sa + kHalfOperandBytes, &map_a, x, r1, &ops_full[st]);
+                tma_load_2d(sb, &map_b, x, c0, &ops_full[st]);
+                tma_load_2d(sb + kHalfOperandBytes, &map_b, x, c1, &ops_full[st]);
+                return true;
+            };
+
+            if (total > 0) ok = issue_tma(0);
+            uint32_t jb = 0;  // jobs whose MMAs have been issued (phase of acc_free / acc_full)
+            for (uint32_t it = 0; it < total && ok; ++it) {
+                const uint32_t st = it & 1u, ph = (it >> 1) & 1u;
+                const int kb = static_cast<int>(it % kbs);
+                if (it + 1 < total && !issue_tma(it + 1)) { ok = false; break; }
+                if (!mbar_wait_bounded(&ops_full[st], ph)) { ok = false; break; }
+                DENSE_STAMP(1);
+                if (kb == 0) {
+                    // accumulator drained by the epilogue of the previous job?
+                    if (!mbar_wait_bounded(acc_free, (jb & 1u) ^ 1u)) { ok = false; break; }
                 }
-                if (ok) umma_commit(acc_full);  // arrives once the accumulator of this job is complete
+                DENSE_STAMP(2);
+                tcgen05_fence_after();
+                const uint32_t a_s = smem_u32(smem + DenseSmem::kStage0 + st * DenseSmem::kStageBytes);
+                const uint32_t b_s = a_s + kOperandBytes;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {  // 4 k-steps of 8 tf32 = 32 bytes inside the swizzle atom
+                    const uint32_t adv = static_cast<uint32_t>(ks) * 32u;
+                    umma_tf32(tmem_base, umma_smem_desc(a_s + adv), umma_smem_desc(b_s + adv), (kb > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(&ops_free[st]);  // arrives once the MMAs above have read their operands
+                if (kb == kbs - 1) {
+                    umma_commit(acc_full);   // arrives once the accumulator of this job is complete
+                    DENSE_STAMP(3);
+                    ++jb;
+                }
             }
             if (!ok) atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
         }
@@ -232,6 +260,7 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
         bool ok = true;
         for (int job = blockIdx.x; job < n_jobs; job += gridDim.x, ++jb) {
             const bool has1 = (2 * job + 1) < args.n_tiles;
+            DENSE_STAMP_E(4);
             // row descriptors of both tiles -> shared memory (threads 0..127: one row each)
             if (tid < 128) {
                 const int which = tid >> 6;
@@ -244,10 +273,16 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                     sMask[tid] = 0ull;
                 }
             }
-            if (ok && !mbar_wait_bounded(acc_full, jb & 1u)) {
-                ok = false;
-                atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
+            if (ok) {   // one lane polls, then the warp re-converges before the warp-wide tcgen05.ld
+                int got = 1;
+                if (lane == 0) {
+                    got = mbar_wait_bounded(acc_full, jb & 1u) ? 1 : 0;
+                    if (!got) atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
+                }
+                __syncwarp();
+                ok = __shfl_sync(kFullMask, got, 0) != 0;
             }
+            DENSE_STAMP_E(5);
             if (ok) {
                 tcgen05_fence_after();
                 uint32_t v[32];
@@ -259,8 +294,10 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                 for (int c = 0; c < 32; ++c) row[c] = __uint_as_float(v[c]);
             }
             __syncwarp();
+            DENSE_STAMP_E(6);
             if (lane == 0) mbar_arrive(acc_free);   // tensor memory may be overwritten by the next job
             epi_barrier();                          // accumulator + descriptors visible to all epilogue warps
+            DENSE_STAMP_E(7);
             if (ok) {
                 // stream the 128 tile rows: warp w takes rows w, w+8, ...; 8 rows in flight per warp
 #pragma unroll 1
@@ -289,9 +326,11 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                         if (on0[u]) __stcs(args.p_val + p0[u], arow[lane] * sv0[u]);
                         if (on1[u]) __stcs(args.p_val + p1[u], arow[lane + 32] * sv1[u]);
                     }
+                    DENSE_STAMP_E(rb < 64 ? 8 : 9);
                 }
             }
             epi_barrier();  // all rows streamed before the next job overwrites sAcc / descriptors
+            DENSE_STAMP_E(10);
         }
     }
 

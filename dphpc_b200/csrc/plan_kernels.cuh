@@ -237,8 +237,13 @@ __global__ void k_residual_items(const int32_t *__restrict__ item_covered, int32
     if (item_covered[t] < size) item_ids[atomicAdd(&pc->residual_items, 1)] = t;
 }
 
-// hi/lo split for the 3-product tf32 scheme: hi = tf32(x), lo = tf32(x - hi)
-__global__ void k_split_tf32(const float *__restrict__ in, float *__restrict__ hi, float *__restrict__ lo, int64_t n) {
+// fp32-grade products from tf32 tensor cores: with hi = tf32(x), lo = tf32(x - hi),
+//   a.b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi   (the dropped lo*lo term is ~2^-22 relative).
+// The three products become ONE dot product of 3K-long rows:
+//   first_operand = 1:  out row = [ lo | hi | hi ]     (used for A)
+//   first_operand = 0:  out row = [ hi | lo | hi ]     (used for B)
+__global__ void k_split_concat_tf32(const float *__restrict__ in, float *__restrict__ out, int64_t rows, int32_t K, int first_operand) {
+    const int64_t n = rows * K;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const float x = in[i];
@@ -246,8 +251,12 @@ __global__ void k_split_tf32(const float *__restrict__ in, float *__restrict__ h
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
         const float hf = __uint_as_float(h);
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hf));
-        hi[i] = hf;
-        lo[i] = __uint_as_float(l);
+        const float lf = __uint_as_float(l);
+        const int64_t r = i / K, k = i - r * K;
+        float *o = out + r * 3 * K + k;
+        o[0] = first_operand ? lf : hf;
+        o[K] = first_operand ? hf : lf;
+        o[2 * K] = hf;
     }
 }
 
