@@ -3,7 +3,7 @@
 Every output nonzero depends on one A row, one B row and one S value, so the
 SDDMM shards by row ranges with no exchange in the compute step: rank g gets
 rows [cut[g], cut[g+1]), the matching slices of col_idx / S.val / A, and all of B.
-The cut points are the first rows whose row_ptr reaches g * nnz / G -- the same
+The cut points are the row boundaries closest to g * nnz / G -- the same
 "equal nonzeros per worker" goal as the reference's per-thread dispatcher
 (CSR<T>::_dispatch, src/matrices/CSR.hpp:214-264), computed by one binary search
 per cut instead of a search over segment capacities.
@@ -19,8 +19,11 @@ def row_cuts(row_ptr: np.ndarray, parts: int) -> np.ndarray:
     M = row_ptr.size - 1
     nnz = int(row_ptr[M])
     targets = (np.arange(1, parts, dtype=np.int64) * nnz) // parts
-    inner = np.searchsorted(row_ptr, targets, side="left").astype(np.int64)
-    cuts = np.concatenate(([0], np.minimum(inner, M), [M]))
+    hi = np.minimum(np.searchsorted(row_ptr, targets, side="left").astype(np.int64), M)   # first boundary at or past the target
+    lo = np.maximum(hi - 1, 0)
+    rp = row_ptr.astype(np.int64)
+    inner = np.where(targets - rp[lo] < rp[hi] - targets, lo, hi)                          # the closer row boundary wins
+    cuts = np.concatenate(([0], inner, [M]))
     return np.maximum.accumulate(cuts)
 
 

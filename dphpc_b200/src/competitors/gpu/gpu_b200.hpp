@@ -34,7 +34,8 @@ public:
     explicit GPUB200(int mode = SDDMM_B200_FP32, int device = 0, const std::string &name = "GPU-B200")
         : SDDMM::Competitor<T>(name), mode_(mode), device_(device) {}
 
-    ~GPUB200() override { sddmm_b200_destroy(engine_); }
+    // (the reference's base class has a non-virtual destructor: hold competitors through make_shared, as its main.cpp does)
+    ~GPUB200() { sddmm_b200_destroy(engine_); }
     GPUB200(const GPUB200 &) = delete;
     GPUB200 &operator=(const GPUB200 &) = delete;
 

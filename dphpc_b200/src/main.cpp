@@ -1,0 +1,80 @@
+// sddmm_bench: benchmark driver for the GPU-B200 competitor on the seeded synthetic configurations.
+// Command line of the reference's driver (src/main.cpp:285-349: --K/-k, --no_csv_header, --num_runs;
+// --data_folder is accepted and ignored: no matrix files are read) plus --config, --scale, --mode.
+// The first competitor is the correctness baseline of the harness; here that is GPU-B200 in fp32
+// mode (the independent CPU check lives in the test-suite, not in this binary).
+#include <cstdlib>
+#include <cstring>
+#include <iostream>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "benchmark/benchmark.hpp"
+
+namespace {
+
+struct Options {
+    int K = 0, num_runs = 3, config = 0, variant = 0;
+    double scale = 1.0;
+    bool header = true;
+    std::vector<std::string> modes{"fp32", "fp32_tc"};   // tf32 / bf16 on request: their 1e-2 error fails the 1e-3 check
+};
+
+int mode_id(const std::string &m) {
+    if (m == "fp32") return SDDMM_B200_FP32;
+    if (m == "tf32") return SDDMM_B200_TF32;
+    if (m == "bf16") return SDDMM_B200_BF16;
+    if (m == "fp32_tc") return SDDMM_B200_FP32_TC;
+    return -1;
+}
+
+void usage() {
+    std::cerr << "usage: sddmm_bench [--config 1..5 (default: all)] [-k K] [--num_runs R] [--scale s] [--mode fp32,tf32,...] [--no_csv_header]\n";
+}
+
+}  // namespace
+
+int main(int argc, char **argv) {
+    Options o;
+    for (int i = 1; i < argc; ++i) {
+        const std::string a = argv[i];
+        auto next = [&]() -> const char * { return (i + 1 < argc) ? argv[++i] : ""; };
+        if (a == "-k" || a == "--K") o.K = std::atoi(next());
+        else if (a == "--num_runs") o.num_runs = std::atoi(next());
+        else if (a == "--config") o.config = std::atoi(next());
+        else if (a == "--variant") o.variant = std::atoi(next());
+        else if (a == "--scale") o.scale = std::atof(next());
+        else if (a == "--no_csv_header") o.header = false;
+        else if (a == "-d" || a == "--data_folder") next();
+        else if (a == "--mode") {
+            o.modes.clear();
+            std::string list = next(), item;
+            for (size_t p = 0; p <= list.size(); ++p) {
+                if (p == list.size() || list[p] == ',') { if (!item.empty()) o.modes.push_back(item); item.clear(); }
+                else item += list[p];
+            }
+        } else { usage(); return 2; }
+    }
+    if (sddmm_b200_device_count() < 1) {
+        std::cerr << "sddmm_bench: no CUDA device; the engine has no CPU path" << std::endl;
+        return 1;
+    }
+    std::vector<std::shared_ptr<SDDMM::Competitor<float>>> competitors;
+    competitors.push_back(std::make_shared<Competitors::GPUB200>(SDDMM_B200_FP32, 0, "GPU-B200"));
+    for (const std::string &m : o.modes) {
+        const int id = mode_id(m);
+        if (id < 0) { usage(); return 2; }
+        if (id != SDDMM_B200_FP32) competitors.push_back(std::make_shared<Competitors::GPUB200>(id, 0, "GPU-B200-" + m));
+    }
+    if (o.header) FILE_DUMP(SDDMM::Benchmark<float>::csv_header() << std::endl);
+    const int default_k[6] = {0, 32, 32, 64, 32, 32};
+    int bad = 0;
+    for (int cfg = 1; cfg <= 5; ++cfg) {
+        if (o.config && cfg != o.config) continue;
+        SDDMM::SyntheticDataset d(cfg, o.K ? o.K : default_k[cfg], o.scale, 0, o.variant);
+        SDDMM::Benchmark<float> b(d, competitors, o.num_runs);
+        bad += b.benchmark();
+    }
+    return bad ? 3 : 0;
+}

@@ -17,17 +17,20 @@ inline void canonicalise(std::vector<Triplet<T>> &t) {
 }
 
 // Value comparison used by operator== of the containers.  The reference accepts
-// |rhs - lhs| / rhs <= 1e-3 with a signed denominator (src/matrices/CSR.hpp:91-95),
-// which only works for positive data; here the denominator is |rhs| and exact
-// zeros must match exactly, so signed SDDMM outputs compare sensibly.
+// |rhs - lhs| / rhs <= 1e-3 with a signed denominator (src/matrices/CSR.hpp:91-95), which only
+// works for positive data without cancellation.  Here an entry matches when
+//   |rhs - lhs| <= 1e-3 * |rhs| + 1e-5 * max_i |rhs_i|
+// i.e. the same relative bar, plus an absolute floor scaled by the largest entry so that
+// outputs that cancel to (nearly) zero are not held to an impossible relative error.
 template <typename T>
 inline bool values_match(const std::vector<T> &lhs, const std::vector<T> &rhs) {
     if (lhs.size() != rhs.size()) return false;
     if (std::is_integral<T>::value) return lhs == rhs;
+    double scale = 0.0;
+    for (const T &v : rhs) scale = std::max(scale, std::fabs(static_cast<double>(v)));
     for (size_t i = 0; i < lhs.size(); ++i) {
         const double d = std::fabs(static_cast<double>(rhs[i]) - static_cast<double>(lhs[i]));
-        const double ref = std::fabs(static_cast<double>(rhs[i]));
-        if (ref == 0.0 ? d != 0.0 : d / ref > 1e-3) return false;
+        if (!(d <= 1e-3 * std::fabs(static_cast<double>(rhs[i])) + 1e-5 * scale)) return false;
     }
     return true;
 }

@@ -1,0 +1,66 @@
+"""The C++ host side: containers/dispatcher mirror (CPU), the GPU-B200 competitor behind the reference's
+interface (GPU), and that the competitor header compiles against the reference's own headers."""
+import os
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+PKG = ROOT / "dphpc_b200"
+SRC = PKG / "src"
+OUT = ROOT / "tests" / "cpp" / "_build"
+REFERENCE = Path(os.environ.get("SDDMM_REFERENCE_ROOT", "/root/reference"))
+
+
+def compile_cpp(name, sources, extra=()):
+    OUT.mkdir(exist_ok=True)
+    exe = OUT / name
+    cmd = ["g++", "-O1", "-std=c++17", "-Wall", "-I", str(SRC), "-I", str(ROOT / "include"), "-I", str(ROOT / "tests" / "cpp"),
+           "-o", str(exe), *map(str, sources), "-L", str(PKG), "-lsddmm_datasets", f"-Wl,-rpath,{PKG}", "-pthread", *extra]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-4000:]
+    return exe
+
+
+def test_containers_and_dispatcher_cpp():
+    exe = compile_cpp("container_tests", [ROOT / "tests" / "cpp" / "container_tests.cpp"])
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-4000:]
+    assert "0 failures" in res.stdout
+
+
+def test_benchmark_driver_builds():
+    from dphpc_b200 import build
+
+    exe = build.build_bench()
+    assert exe.exists()
+    res = subprocess.run([str(exe), "--bogus"], capture_output=True, text=True)
+    assert res.returncode == 2 and "usage" in res.stderr
+
+
+@pytest.mark.skipif(not (REFERENCE / "src" / "benchmark" / "competitor.hpp").exists(), reason="reference checkout absent")
+def test_competitor_header_drops_into_the_reference_tree(tmp_path):
+    # compile GPUB200 against the reference's OWN competitor.hpp / matrices (not this repository's mirror)
+    tu = tmp_path / "dropin.cpp"
+    tu.write_text('#include <cmath>\n#include "competitors/gpu/gpu_b200.hpp"\n'
+                  "int main() { Competitors::GPUB200 c; SDDMM::Competitor<float> *p = &c; return p->is_gpu() ? 0 : 1; }\n")
+    cuda_inc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+    cmd = ["g++", "-std=c++17", "-fsyntax-only", "-w", "-include", "cstdint", "-include", "cassert", "-I", str(REFERENCE / "src"),
+           "-I", str(cuda_inc), "-I", str(ROOT / "include"), "-idirafter", str(SRC), str(tu)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-4000:]
+
+
+@pytest.mark.gpu
+def test_competitor_behind_the_reference_interface():
+    oracle_c = ROOT / "oracle" / "sddmm_oracle.c"
+    OUT.mkdir(exist_ok=True)
+    obj = OUT / "sddmm_oracle.o"
+    res = subprocess.run(["gcc", "-O2", "-ffp-contract=off", "-c", "-o", str(obj), str(oracle_c)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    exe = compile_cpp("competitor_tests", [ROOT / "tests" / "cpp" / "competitor_tests.cpp", obj], extra=["-lsddmm_b200"])
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=900)
+    lines = [ln for ln in res.stdout.splitlines() if not ln.startswith(("GPU-B200", "CPU-Basic"))]   # drop the CSV rows
+    assert res.returncode == 0, "\n".join(lines[-60:]) + res.stderr[-2000:]
+    assert "0 failures" in res.stdout

@@ -1,0 +1,93 @@
+"""Row-range sharding used for N > 1 GPUs: host logic on CPU, including a 2-rank gloo run in which every rank
+computes only its shard (with the CPU oracle standing in for the GPU engine) and the gathered result must be
+bit-identical to the unsharded one -- the path bench.py takes under torchrun, minus the device."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from dphpc_b200 import Dataset
+from dphpc_b200.partition import row_cuts, shard
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("cfg,scale", [(2, 0.05), (4, 0.01), (5, 0.01)])
+@pytest.mark.parametrize("parts", [1, 2, 4, 8])
+def test_cuts_cover_and_balance(cfg, scale, parts):
+    d = Dataset(cfg, 4, scale)
+    cuts = row_cuts(d.row_ptr, parts)
+    assert cuts[0] == 0 and cuts[-1] == d.M and len(cuts) == parts + 1
+    assert (np.diff(cuts) >= 0).all()
+    per = np.diff(d.row_ptr[cuts])
+    assert per.sum() == d.nnz
+    longest = int(np.diff(d.row_ptr).max())
+    assert per.max() <= d.nnz / parts + longest  # no shard exceeds its share by more than one row
+
+
+def test_cuts_on_degenerate_patterns():
+    assert row_cuts(np.array([0, 0, 0, 5], np.int32), 2).tolist() == [0, 2, 3]      # all nonzeros in the last row
+    assert row_cuts(np.array([0, 4, 4, 4], np.int32), 4).tolist() == [0, 0, 1, 1, 3]     # one heavy row: it goes to one shard, the others stay (nearly) empty
+    cuts = row_cuts(np.arange(9, dtype=np.int32), 8)                                     # diagonal: one row each
+    assert cuts.tolist() == list(range(9))
+    assert row_cuts(np.zeros(5, np.int32), 2)[[0, -1]].tolist() == [0, 4]                # empty matrix
+
+
+def test_shard_slices_rebase_row_ptr():
+    d = Dataset(5, 8, 0.005)
+    pieces = [shard(d.row_ptr, d.col_idx, d.s_val, d.A, r, 3) for r in range(3)]
+    assert sum(p[3].size for p in pieces) == d.nnz
+    for r0, r1, rp, ci, sv, A in pieces:
+        assert rp[0] == 0 and rp[-1] == ci.size == sv.size and A.shape[0] == r1 - r0 and rp.size == r1 - r0 + 1
+    assert np.array_equal(np.concatenate([p[3] for p in pieces]), d.col_idx)
+
+
+def _rank_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    import oracle_lib
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import torch
+
+    d = Dataset(4, 32, 0.004)
+    orc = oracle_lib.Oracle()
+    # rank 0 owns B and broadcasts it once, like the NCCL broadcast before the timed region
+    B = torch.from_numpy(np.ascontiguousarray(d.B).copy()) if rank == 0 else torch.empty((d.N, d.K), dtype=torch.float32)
+    dist.broadcast(B, src=0)
+    r0, r1, rp, ci, sv, A = shard(d.row_ptr, d.col_idx, d.s_val, d.A, rank, world)
+    p_local = orc.sddmm_csr(r1 - r0, d.K, rp, ci, sv, A, B.numpy())
+    sizes = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(sizes, torch.tensor([p_local.size], dtype=torch.int64))
+    bufs = [torch.empty(int(s.item()), dtype=torch.float32) for s in sizes]
+    dist.all_gather(bufs, torch.from_numpy(p_local)) if len({int(s.item()) for s in sizes}) == 1 else None
+    if len({int(s.item()) for s in sizes}) != 1:  # ragged shards: gather through rank 0 with point-to-point sends
+        if rank == 0:
+            bufs[0] = torch.from_numpy(p_local)
+            for r in range(1, world):
+                dist.recv(bufs[r], src=r)
+        else:
+            dist.send(torch.from_numpy(p_local), dst=0)
+    if rank == 0:
+        full = orc.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        got = np.concatenate([b.numpy() for b in bufs])
+        np.save(Path(out_dir) / "ok.npy", np.array([np.array_equal(full, got), got.size == d.nnz]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gloo_sharded_sddmm(tmp_path):
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    ok = np.load(tmp_path / "ok.npy")
+    assert ok.all()
