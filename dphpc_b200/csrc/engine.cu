@@ -451,7 +451,7 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
 
 int check_dims(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz) {
     if (M < 1 || N < 1 || K < 1 || nnz < 0) return fail(e, SDDMM_B200_ERR_ARG, "need M, N, K >= 1 and nnz >= 0");
-    if (M >= (int64_t(1) << 31) - 1 || N >= (int64_t(1) << 31) - 1 || nnz >= (int64_t(1) << 31) - 64)
+    if (M >= (int64_t(1) << 31) - 1 || N >= (int64_t(1) << 31) - 1 || nnz >= (int64_t(1) << 31) - 8192)
         return fail(e, SDDMM_B200_ERR_ARG, "int32 index range exceeded");
     return SDDMM_B200_OK;
 }

@@ -91,8 +91,11 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
 
     for (int it = blockIdx.x; it < args.n_items; it += gridDim.x) {
         const int item = args.item_ids ? args.item_ids[it] : it;
-        const int64_t j_lo = static_cast<int64_t>(item) * args.item_nnz;
-        const int64_t j_hi = min(args.nnz, j_lo + args.item_nnz);
+        // nonzero indices fit 32 bits (int32 row_ptr; the engine keeps nnz below 2^31 - 8192 so that the
+        // window arithmetic below cannot overflow)
+        const int nnz32 = static_cast<int>(args.nnz);
+        const int j_lo = item * args.item_nnz;
+        const int j_hi = j_lo + min(nnz32 - j_lo, args.item_nnz);
         const int2 rr = args.item_rows[item];
         const int r_lo = rr.x, r_hi = rr.y;
 
@@ -106,10 +109,10 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
             }
             __syncthreads();
 
-            const int64_t s_lo = max(j_lo, static_cast<int64_t>(sRp[0]));
-            const int64_t s_hi = min(j_hi, static_cast<int64_t>(sRp[nr]));
+            const int s_lo = max(j_lo, sRp[0]);
+            const int s_hi = min(j_hi, sRp[nr]);
             int cached_row = -1;      // row whose A chunks sit in areg
-            int64_t cached_end = 0;   // first nonzero index past that row
+            int cached_end = 0;       // first nonzero index past that row
             float4 areg[CPL];
 #pragma unroll
             for (int q = 0; q < CPL; ++q) areg[q] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -117,11 +120,11 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
             // 32-aligned warp windows so every col/val/P access is a full 128-byte line.  The column
             // indices and S values of the NEXT window are requested before the current one is
             // processed, so the gather of B rows never waits behind an index load.
-            int64_t wb = (s_lo & ~int64_t(31)) + warp * 32;
+            int wb = (s_lo & ~31) + warp * 32;
             int4 pc0 = make_int4(0, 0, 0, 0), pc1 = make_int4(0, 0, 0, 0);
             float ps = 0.f;
-            auto request_window = [&](int64_t w) {
-                const int64_t jw = w + lane;
+            auto request_window = [&](int w) {
+                const int jw = w + lane;
                 if ((w >= s_lo) && (w + 32 <= s_hi)) {
                     pc0 = __ldcs(reinterpret_cast<const int4 *>(args.col_idx + w + gbase));
                     pc1 = __ldcs(reinterpret_cast<const int4 *>(args.col_idx + w + gbase + 4));
@@ -142,7 +145,7 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
             }
             phase ^= 1u;
             for (; wb < s_hi; wb += kRowTileWarps * 32) {
-                const int64_t j = wb + lane;
+                const int j = wb + lane;
                 const bool full = (wb >= s_lo) && (wb + 32 <= s_hi);   // warp-uniform
                 bool valid = full || ((j >= s_lo) && (j < s_hi));
 
@@ -167,7 +170,7 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
                     lr = cached_row;
                 } else {
                     // largest t with sRp[t] <= j (out-of-window lanes are clamped so rows stay monotone)
-                    const int jj = static_cast<int>(min(max(j, s_lo), s_hi - 1));
+                    const int jj = min(max(j, s_lo), s_hi - 1);
                     int lo = 0, hi = nr;
                     while (hi - lo > 1) {
                         const int mid = (lo + hi) >> 1;
