@@ -35,7 +35,7 @@ ENGINE_SYMBOLS = [
     "sddmm_b200_sync", "sddmm_b200_download", "sddmm_b200_p_device", "sddmm_b200_last_run_ms", "sddmm_b200_last_kernel_ms",
     "sddmm_b200_get_plan", "sddmm_b200_algorithmic_bytes", "sddmm_b200_flops", "sddmm_b200_last_error",
     "sddmm_b200_stream", "sddmm_b200_device_count", "sddmm_b200_version", "sddmm_b200_host_alloc",
-    "sddmm_b200_host_free",
+    "sddmm_b200_host_free", "sddmm_b200_sddmm_csr_prealloc",
 ]
 DATASET_SYMBOLS = [
     "sddmm_dataset_create", "sddmm_dataset_create_uniform", "sddmm_dataset_destroy", "sddmm_dataset_dims",
@@ -117,6 +117,7 @@ def load_engine_lib() -> C.CDLL:
     lib.sddmm_b200_version.restype = C.c_char_p
     lib.sddmm_b200_host_alloc.argtypes = [C.POINTER(C.c_void_p), C.c_int64]
     lib.sddmm_b200_host_free.argtypes = [C.c_void_p]
+    lib.sddmm_b200_sddmm_csr_prealloc.argtypes = [C.c_int, C.c_void_p] + [C.c_int64] * 4 + [C.c_void_p] * 6
     _engine_lib = lib
     return lib
 

@@ -811,4 +811,76 @@ int sddmm_b200_host_free(void *ptr) {
     return cudaFreeHost(ptr) == cudaSuccess ? SDDMM_B200_OK : SDDMM_B200_ERR_CUDA;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free SDDMM (see sddmm_b200_sddmm_csr_prealloc in the header).
+//
+// The row-tile kernel needs two pieces of scratch besides its operands: the table that says in which
+// rows each nnz-balanced work item begins and ends, and an error word for its bounded waits.  Here
+// both live in a fixed device array that is part of the loaded library image, so the call below never
+// asks the CUDA allocator for anything.  The array name is only a host-side handle: its device address
+// is looked up once per device with cudaGetSymbolAddress (that device current) and cached.
+constexpr int64_t kPreallocMaxNnz = int64_t(1) << 27;                   // 134 217 728 nonzeros
+constexpr int kPreallocItemNnz = 2048;
+constexpr int64_t kPreallocMaxItems = kPreallocMaxNnz / kPreallocItemNnz;  // 65 536 work items
+constexpr size_t kPreallocTableBytes = static_cast<size_t>(kPreallocMaxItems) * sizeof(int2);   // 512 KiB
+constexpr size_t kPreallocScratchBytes = kPreallocTableBytes + 256;      // + the error word, on its own 256-byte line
+static __device__ __align__(256) unsigned char g_prealloc_scratch[kPreallocScratchBytes];
+
+constexpr int kPreallocMaxDevices = 64;
+static unsigned char *g_prealloc_ptr[kPreallocMaxDevices] = {nullptr};   // device address of the array, per device
+
+int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int64_t N, int64_t K, int64_t nnz,
+                                  const int32_t *d_row_ptr, const int32_t *d_col_idx, const float *d_s_val,
+                                  const float *d_A, const float *d_B, float *d_p_val) {
+    if (M < 1 || N < 1 || K < 1 || nnz < 0 || device < 0 || device >= kPreallocMaxDevices) return SDDMM_B200_ERR_ARG;
+    if (!d_row_ptr || !d_A || !d_B || (nnz > 0 && (!d_col_idx || !d_s_val || !d_p_val))) return SDDMM_B200_ERR_ARG;
+    if (M >= (int64_t(1) << 31) - 1 || N >= (int64_t(1) << 31) - 1) return SDDMM_B200_ERR_ARG;
+    if (nnz > kPreallocMaxNnz) return SDDMM_B200_ERR_UNSUPPORTED;        // the work-item table would not fit the fixed scratch
+    const int cpl = round_up_cpl(K);
+    if (K % 4 != 0 || cpl == 0) return SDDMM_B200_ERR_UNSUPPORTED;      // only the row-tile kernel (K % 4 == 0, K <= 256) is offered here
+    if (nnz == 0) return SDDMM_B200_OK;
+    DeviceGuard g(device);
+    if (!g.ok) return SDDMM_B200_ERR_CUDA;
+    if (!g_prealloc_ptr[device]) {   // first call on this device: resolve the array's device address
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_prealloc_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return SDDMM_B200_ERR_CUDA;
+        }
+        g_prealloc_ptr[device] = static_cast<unsigned char *>(p);
+    }
+    int2 *item_rows = reinterpret_cast<int2 *>(g_prealloc_ptr[device]);
+    int32_t *err = reinterpret_cast<int32_t *>(g_prealloc_ptr[device] + kPreallocTableBytes);
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+
+    const int n_items = static_cast<int>((nnz + kPreallocItemNnz - 1) / kPreallocItemNnz);
+    // the array keeps whatever the previous call left: the error word must start at zero, the table is rewritten
+    if (cudaMemsetAsync(err, 0, sizeof(int32_t), st) != cudaSuccess) return SDDMM_B200_ERR_CUDA;
+    k_item_rows<<<grid_for(n_items, kBlock, 1 << 30), kBlock, 0, st>>>(d_row_ptr, static_cast<int32_t>(M), nnz, kPreallocItemNnz, n_items, item_rows);
+
+    int64_t R = kPreallocItemNnz / std::max<int64_t>(1, nnz / M) + 1;
+    R = (R + 7) / 8 * 8;
+    R = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(R, kMaxStageBytes / (K * 4)), M));
+    const int smem = static_cast<int>(((static_cast<size_t>(R) * K * 4 + 15) & ~size_t(15)) + (R + 1) * 4);
+    const bool exact = (K == 32 * cpl);
+    RowTileFn<float> fn = pick_rowtile<float>(cpl, exact);
+    if (cudaFuncSetAttribute(reinterpret_cast<const void *>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return SDDMM_B200_ERR_CUDA;
+    int occ = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, reinterpret_cast<const void *>(fn), kBlock, smem) != cudaSuccess || occ < 1) return SDDMM_B200_ERR_CUDA;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return SDDMM_B200_ERR_CUDA;
+
+    RowTileArgs a;
+    a.row_ptr = d_row_ptr; a.col_idx = d_col_idx; a.s_val = d_s_val; a.p_val = d_p_val; a.A = d_A; a.B = d_B;
+    a.item_rows = item_rows; a.item_ids = nullptr; a.skip_tile_bitmap = nullptr; a.skip_tiles_per_row = 0;
+    a.err = err; a.nnz = nnz; a.M = static_cast<int32_t>(M); a.K = static_cast<int32_t>(K);
+    a.n_items = n_items; a.item_nnz = kPreallocItemNnz; a.rows_per_stage = static_cast<int32_t>(R);
+    fn<<<std::min(n_items, sms * occ), kBlock, smem, st>>>(a);
+    if (cudaGetLastError() != cudaSuccess) return SDDMM_B200_ERR_CUDA;
+    int32_t h_err = 0;   // synchronous by contract: wait, then read the error word back
+    if (cudaMemcpyAsync(&h_err, err, sizeof(int32_t), cudaMemcpyDeviceToHost, st) != cudaSuccess) return SDDMM_B200_ERR_CUDA;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return SDDMM_B200_ERR_CUDA;
+    return h_err == kDevOk ? SDDMM_B200_OK : SDDMM_B200_ERR_DEVICE_WAIT;
+}
+
 }  // extern "C"

@@ -149,6 +149,31 @@ void *sddmm_b200_stream(sddmm_b200_engine *e);
 int sddmm_b200_device_count(void);
 const char *sddmm_b200_version(void);
 
+/* ---- allocation-free call ---------------------------------------------------------
+ * No counterpart in the reference (every competitor there allocates in init_*).
+ *
+ * For callers that must not reach the CUDA allocator when they need an SDDMM: code running
+ * inside a framework that owns all device memory through its own pool and forbids foreign
+ * cudaMalloc calls, a real-time loop that cannot take the allocator's lock or its implicit
+ * device synchronisation, a process whose memory is already fully committed.  Everything is
+ * caller-owned DEVICE memory on `device`; the work-item table and the error word the row-tile
+ * kernel needs live in a fixed 512.25 KiB array inside the library image (every GPU that loads
+ * the library holds it until the process exits), so the call performs no cudaMalloc, cudaFree
+ * or other allocating call.
+ *
+ *   - fp32, CSR, K % 4 == 0 and K <= 256, nnz <= 2^27 (134 217 728); anything else returns
+ *     SDDMM_B200_ERR_UNSUPPORTED and touches nothing.  row_ptr/col_idx are trusted (not validated).
+ *   - synchronous: work is enqueued on `cuda_stream` (a cudaStream_t, may be 0) and the call
+ *     returns after that stream has drained.
+ *   - the first call on a device looks up the array's device address; make that call outside
+ *     any stream capture.
+ *   - all calls on one device share the array and it keeps the last call's contents (the parts
+ *     that must start clean are reset by each call): two calls that overlap on the same GPU
+ *     race on it -- serialise them. */
+int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int64_t N, int64_t K, int64_t nnz,
+                                  const int32_t *d_row_ptr, const int32_t *d_col_idx, const float *d_s_val,
+                                  const float *d_A, const float *d_B, float *d_p_val);
+
 /* pinned host memory helpers (so callers without a CUDA toolchain can stage
  * inputs for full-rate copies) */
 int sddmm_b200_host_alloc(void **ptr, int64_t bytes);
