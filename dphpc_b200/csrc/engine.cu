@@ -45,10 +45,6 @@ struct Carve {
 
 }  // namespace
 
-#ifdef SDDMM_DENSE_TRACE
-unsigned long long *sddmm_trace_ptr = nullptr;
-#endif
-
 struct sddmm_b200_engine {
     int device = 0;
     int mode = SDDMM_B200_FP32;
@@ -523,13 +519,6 @@ int launch_all(sddmm_b200_engine *e) {
         d.k_blocks = static_cast<int32_t>((e->mode == SDDMM_B200_FP32_TC ? 3 * e->K : e->K) / 32);
         d.reserved = 0;
         d.nnz = e->nnz;
-        d.trace = nullptr;
-#ifdef SDDMM_DENSE_TRACE
-        static unsigned long long *trace_buf = nullptr;
-        if (!trace_buf) { cudaMalloc(&trace_buf, 4 * 6 * 16 * 8); sddmm_trace_ptr = trace_buf; }
-        cudaMemsetAsync(trace_buf, 0, 4 * 6 * 16 * 8, e->stream);
-        d.trace = trace_buf;
-#endif
         if ((st = begin_kernel(e, e->stream))) return st;
         sddmm_dense_tile_kernel<<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a, e->map_b);
         if ((st = mark_kernel(e, "sddmm_dense_tile_kernel", e->stream))) return st;
@@ -698,29 +687,6 @@ int sddmm_b200_run(sddmm_b200_engine *e) {
     int st = launch_all(e);
     if (st) return st;
     CU_TRY(e, cudaEventRecord(e->ev_run1, e->stream));
-#ifdef SDDMM_DENSE_TRACE
-    if (e->n_dense > 0 && std::getenv("SDDMM_B200_TRACE_FILE")) {
-        // debugging aid: dump the per-CTA time stamps of the dense-tile kernel
-        static unsigned long long host[4 * 6 * 16];
-        cudaStreamSynchronize(e->stream);
-        void *dev = nullptr;
-        // the buffer address is the static in launch_all; fetch it through a second static
-        dev = sddmm_trace_ptr;
-        if (dev) {
-            cudaMemcpy(host, dev, sizeof(host), cudaMemcpyDeviceToHost);
-            FILE *f = std::fopen(std::getenv("SDDMM_B200_TRACE_FILE"), "w");
-            if (f) {
-                for (int c = 0; c < 4; ++c)
-                    for (int j = 0; j < 6; ++j) {
-                        std::fprintf(f, "cta %d job %d:", c, j);
-                        for (int k = 0; k < 11; ++k) std::fprintf(f, " %llu", host[(c * 6 + j) * 16 + k]);
-                        std::fprintf(f, "\n");
-                    }
-                std::fclose(f);
-            }
-        }
-    }
-#endif
     CU_TRY(e, cudaMemcpyAsync(e->h_err, e->d_err, sizeof(int32_t), cudaMemcpyDeviceToHost, e->stream));
     e->ran = true;
     return SDDMM_B200_OK;

@@ -66,21 +66,7 @@ struct DenseArgs {
     int32_t k_blocks;               // operand row length / 32
     int32_t reserved;
     int64_t nnz;                    // bound of every S.val / P.val position (checked builds only)
-    unsigned long long *trace;      // SDDMM_DENSE_TRACE builds: per-CTA time stamps; nullptr otherwise
 };
-
-#ifdef SDDMM_DENSE_TRACE
-__device__ __forceinline__ unsigned long long dense_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define DENSE_STAMP(slot) do { if (args.trace && blockIdx.x < 4 && jb < 6) args.trace[(blockIdx.x * 6 + jb) * 16 + (slot)] = dense_now(); } while (0)
-#define DENSE_STAMP_E(slot) do { if (tid == 0) DENSE_STAMP(slot); } while (0)
-#else
-#define DENSE_STAMP(slot) do { } while (0)
-#define DENSE_STAMP_E(slot) do { } while (0)
-#endif
 
 // shared memory carve-up (dynamic, 1024-byte aligned by hand)
 struct DenseSmem {
@@ -228,12 +214,10 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                 const int kb = static_cast<int>(it % kbs);
                 if (it + 1 < total && !issue_tma(it + 1)) { ok = false; break; }
                 if (!mbar_wait_bounded(&ops_full[st], ph)) { ok = false; break; }
-                DENSE_STAMP(1);
                 if (kb == 0) {
                     // accumulator drained by the epilogue of the previous job?
                     if (!mbar_wait_bounded(acc_free, (jb & 1u) ^ 1u)) { ok = false; break; }
                 }
-                DENSE_STAMP(2);
                 tcgen05_fence_after();
                 const uint32_t a_s = smem_u32(smem + DenseSmem::kStage0 + st * DenseSmem::kStageBytes);
                 const uint32_t b_s = a_s + kOperandBytes;
@@ -245,7 +229,6 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                 umma_commit(&ops_free[st]);  // arrives once the MMAs above have read their operands
                 if (kb == kbs - 1) {
                     umma_commit(acc_full);   // arrives once the accumulator of this job is complete
-                    DENSE_STAMP(3);
                     ++jb;
                 }
             }
@@ -260,7 +243,6 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
         bool ok = true;
         for (int job = blockIdx.x; job < n_jobs; job += gridDim.x, ++jb) {
             const bool has1 = (2 * job + 1) < args.n_tiles;
-            DENSE_STAMP_E(4);
             // row descriptors of both tiles -> shared memory (threads 0..127: one row each)
             if (tid < 128) {
                 const int which = tid >> 6;
@@ -282,7 +264,6 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                 __syncwarp();
                 ok = __shfl_sync(kFullMask, got, 0) != 0;
             }
-            DENSE_STAMP_E(5);
             if (ok) {
                 tcgen05_fence_after();
                 uint32_t v[32];
@@ -294,10 +275,8 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                 for (int c = 0; c < 32; ++c) row[c] = __uint_as_float(v[c]);
             }
             __syncwarp();
-            DENSE_STAMP_E(6);
             if (lane == 0) mbar_arrive(acc_free);   // tensor memory may be overwritten by the next job
             epi_barrier();                          // accumulator + descriptors visible to all epilogue warps
-            DENSE_STAMP_E(7);
             if (ok) {
                 // stream the 128 tile rows: warp w takes rows w, w+8, ...; 8 rows in flight per warp
 #pragma unroll 1
@@ -326,11 +305,9 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                         if (on0[u]) __stcs(args.p_val + p0[u], arow[lane] * sv0[u]);
                         if (on1[u]) __stcs(args.p_val + p1[u], arow[lane + 32] * sv1[u]);
                     }
-                    DENSE_STAMP_E(rb < 64 ? 8 : 9);
                 }
             }
             epi_barrier();  // all rows streamed before the next job overwrites sAcc / descriptors
-            DENSE_STAMP_E(10);
         }
     }
 
