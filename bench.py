@@ -240,7 +240,8 @@ def main():
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--config", type=int, default=DEFAULT_CONFIG, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--k", type=int, default=0)
-    ap.add_argument("--mode", default="fp32", choices=["fp32", "bf16", "tf32", "fp32_tc"])
+    ap.add_argument("--mode", default="fp32_tc", choices=["fp32", "bf16", "tf32", "fp32_tc"],
+                    help="fp32_tc (default): fp32-grade results, dense tiles on tcgen05; fp32: FMA everywhere")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (profiling captures only)")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-config table and the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true")
@@ -266,7 +267,7 @@ def main():
 
     cfg, K = args.config, args.k or CONFIG_K[args.config]
     d = Dataset(cfg, K, args.scale)
-    cuts = row_cuts(d.row_ptr, world)
+    cuts = row_cuts(d.row_ptr, world, align=64 if d.M >= 64 * 8 * world else 1)   # shards keep the global 64-row tile grid
     r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
     j0, j1 = int(d.row_ptr[r0]), int(d.row_ptr[r1])
     rp_local = (d.row_ptr[r0:r1 + 1].astype(np.int64) - j0).astype(np.int32)

@@ -13,8 +13,12 @@ from __future__ import annotations
 import numpy as np
 
 
-def row_cuts(row_ptr: np.ndarray, parts: int) -> np.ndarray:
-    """parts+1 row indices, cut[0] = 0, cut[parts] = M, non-decreasing."""
+def row_cuts(row_ptr: np.ndarray, parts: int, align: int = 1) -> np.ndarray:
+    """parts+1 row indices, cut[0] = 0, cut[parts] = M, non-decreasing.
+
+    align > 1 moves every inner cut to the nearest multiple of `align` rows: with align = 64 the 64x64
+    tiles of each shard coincide with those of the whole matrix, so a block that is dense globally is
+    still one dense tile locally (the tensor-core path looks at aligned tiles of what it is given)."""
     row_ptr = np.asarray(row_ptr)
     M = row_ptr.size - 1
     nnz = int(row_ptr[M])
@@ -23,13 +27,15 @@ def row_cuts(row_ptr: np.ndarray, parts: int) -> np.ndarray:
     lo = np.maximum(hi - 1, 0)
     rp = row_ptr.astype(np.int64)
     inner = np.where(targets - rp[lo] < rp[hi] - targets, lo, hi)                          # the closer row boundary wins
+    if align > 1:
+        inner = np.minimum((inner + align // 2) // align * align, M)
     cuts = np.concatenate(([0], inner, [M]))
     return np.maximum.accumulate(cuts)
 
 
-def shard(row_ptr, col_idx, s_val, A, rank: int, parts: int):
+def shard(row_ptr, col_idx, s_val, A, rank: int, parts: int, align: int = 1):
     """(row0, row1, rebased row_ptr, col slice, val slice, A slice) of one rank; views where possible."""
-    cuts = row_cuts(row_ptr, parts)
+    cuts = row_cuts(row_ptr, parts, align)
     r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
     a, b = int(row_ptr[r0]), int(row_ptr[r1])
     rp = (np.asarray(row_ptr[r0:r1 + 1], dtype=np.int64) - a).astype(np.int32)

@@ -28,6 +28,15 @@ def test_cuts_cover_and_balance(cfg, scale, parts):
     assert per.max() <= d.nnz / parts + longest  # no shard exceeds its share by more than one row
 
 
+def test_aligned_cuts_stay_on_the_tile_grid():
+    d = Dataset(2, 4, 0.3)
+    cuts = row_cuts(d.row_ptr, 4, align=64)
+    assert cuts[0] == 0 and cuts[-1] == d.M and (np.diff(cuts) >= 0).all()
+    assert all(int(c) % 64 == 0 for c in cuts[1:-1])
+    per = np.diff(d.row_ptr[cuts])
+    assert per.max() <= d.nnz / 4 + 64 * int(np.diff(d.row_ptr).max())
+
+
 def test_cuts_on_degenerate_patterns():
     assert row_cuts(np.array([0, 0, 0, 5], np.int32), 2).tolist() == [0, 2, 3]      # all nonzeros in the last row
     assert row_cuts(np.array([0, 4, 4, 4], np.int32), 4).tolist() == [0, 0, 1, 1, 3]     # one heavy row: it goes to one shard, the others stay (nearly) empty
