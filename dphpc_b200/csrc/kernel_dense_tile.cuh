@@ -22,13 +22,19 @@
 //                     first nonzero in the tile.  S.val is read and P.val is
 //                     written in CSR order in contiguous runs; col_idx is not
 //                     read at all (the mask, built once per upload, replaces it).
+//                     The S.val run of every tile row is staged in shared memory
+//                     by asynchronous 16-byte copies issued most of a job ahead,
+//                     the row records (first position, mask) two jobs ahead: no
+//                     warp waits for global memory inside a job.
 //
 // Modes: plain tf32 operands (rel 1e-2), or fp32-grade results from tf32 tensor cores: the
 // engine stores A' = [A_lo | A_hi | A_hi] and B' = [B_hi | B_lo | B_hi] (hi = tf32(x),
 // lo = tf32(x - hi)), so that A'.B'^T = lo*hi + hi*lo + hi*hi is just a 3x longer K for this
 // kernel -- one code path for both modes.
-// K' must be a multiple of 32; every 32-wide k-block is one 128-byte swizzle atom.  Operand
-// k-blocks go through a two-stage ring so the TMA of one block overlaps the MMA of the other.
+// K' must be a multiple of 32; every 32-wide k-block is one 128-byte swizzle atom.  There is one
+// operand buffer: the next k-block is requested as soon as the MMAs of the current one have read
+// it, which for K' = 32 still overlaps the whole epilogue of the job (shared memory goes to the
+// S.val staging instead, so that two CTAs fit on an SM).
 //
 // Every wait on an mbarrier is bounded; on a timeout the CTA sets the error
 // word, stops issuing work, and still frees its tensor memory.
@@ -44,6 +50,7 @@ constexpr int kDenseTile = 64;               // tile edge
 constexpr int kDenseEpiWarps = 8;
 constexpr int kDenseThreads = (kDenseEpiWarps + 1) * 32;   // + producer/MMA warp
 constexpr int kDenseAccStride = 65;          // floats per accumulator row in smem (odd: conflict-free column writes)
+constexpr int kDenseSvalStride = 72;         // floats per staged S.val row: 64 + up to 3 before + up to 3 after (16-byte granules), 288 bytes
 constexpr uint32_t kOperandBytes = 128 * 128;  // 128 rows x one 128-byte k-block
 constexpr uint32_t kHalfOperandBytes = 64 * 128;
 constexpr int kTmemCols = 128;
@@ -71,13 +78,14 @@ struct DenseArgs {
 // shared memory carve-up (dynamic, 1024-byte aligned by hand)
 struct DenseSmem {
     static constexpr uint32_t kStageBytes = 2 * kOperandBytes;   // A block + B block
-    static constexpr uint32_t kStage0 = 0;                        // stage s: A at s*kStageBytes, B right after it
-    static constexpr uint32_t kAcc = 2 * kStageBytes;
+    static constexpr uint32_t kStage0 = 0;                        // one operand buffer: A block, B block right after it
+    static constexpr uint32_t kAcc = kStageBytes;
     static constexpr uint32_t kAccBytes = 128 * kDenseAccStride * 4;
-    static constexpr uint32_t kStart = kAcc + kAccBytes;          // 128 int32
-    static constexpr uint32_t kMask = kStart + 128 * 4;           // 128 u64 (8-byte aligned: kAccBytes % 8 == 0)
-    static constexpr uint32_t kBars = kMask + 128 * 8;            // 6 mbarriers
-    static constexpr uint32_t kTmemPtr = kBars + 6 * 8;
+    static constexpr uint32_t kSval = kAcc + kAccBytes;           // 128 rows x kDenseSvalStride floats: the S.val run of each tile row, as it lies in memory
+    static constexpr uint32_t kSvalBytes = 128 * kDenseSvalStride * 4;
+    static constexpr uint32_t kRows = kSval + kSvalBytes;         // 3 buffers x 128 row records {first CSR position, 16-byte granules of the run, mask lo, mask hi}
+    static constexpr uint32_t kBars = kRows + 3 * 128 * 16;       // 4 mbarriers
+    static constexpr uint32_t kTmemPtr = kBars + 4 * 8;
     static constexpr uint32_t kTotal = kTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kTotal + 1024;      // slack for the manual 1024-byte alignment
 };
@@ -135,6 +143,23 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
         : "memory");
 }
 
+// Ampere-style asynchronous copies global -> shared (4 or 8 bytes per thread), tracked per thread in groups.
+__device__ __forceinline__ void cp_async_4(void *dst_smem, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_8(void *dst_smem, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void *dst_smem, const void *src) {   // both 16-byte aligned; not kept in L1
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {   // all but the N most recent groups of this thread have landed
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __device__ __forceinline__ void epi_barrier() {  // the 8 epilogue warps only
     asm volatile("bar.sync 1, %0;" ::"n"(kDenseEpiWarps * 32) : "memory");
 }
@@ -145,10 +170,10 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     extern __shared__ unsigned char dense_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(dense_smem_raw) + 1023) & ~uintptr_t(1023));
     float *sAcc = reinterpret_cast<float *>(smem + DenseSmem::kAcc);
-    int32_t *sStart = reinterpret_cast<int32_t *>(smem + DenseSmem::kStart);
-    unsigned long long *sMask = reinterpret_cast<unsigned long long *>(smem + DenseSmem::kMask);
+    float *sSval = reinterpret_cast<float *>(smem + DenseSmem::kSval);
+    uint4 *sRows = reinterpret_cast<uint4 *>(smem + DenseSmem::kRows);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + DenseSmem::kBars);
-    uint64_t *ops_full = &bars[0], *ops_free = &bars[2], *acc_full = &bars[4], *acc_free = &bars[5];   // ops_*: one per stage
+    uint64_t *ops_full = &bars[0], *ops_free = &bars[1], *acc_full = &bars[2], *acc_free = &bars[3];
     uint32_t *tmem_ptr_smem = reinterpret_cast<uint32_t *>(smem + DenseSmem::kTmemPtr);
 
     const int tid = threadIdx.x;
@@ -157,10 +182,8 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     const int n_jobs = (args.n_tiles + 1) >> 1;
 
     if (tid == 0) {
-        mbar_init(&ops_full[0], 1);
-        mbar_init(&ops_full[1], 1);
-        mbar_init(&ops_free[0], 1);
-        mbar_init(&ops_free[1], 1);
+        mbar_init(ops_full, 1);
+        mbar_init(ops_free, 1);
         mbar_init(acc_full, 1);
         mbar_init(acc_free, kDenseEpiWarps);
         fence_mbar_init();
@@ -178,83 +201,162 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
 
     if (warp == kDenseEpiWarps) {
         // ===================== producer + MMA issuer (one thread) =====================
-        // Iterations = (job, k-block) pairs of this CTA in order.  Iteration `it` uses operand stage
-        // it & 1; its TMA is issued one iteration ahead of its MMA.
+        // Iterations = (job, k-block) pairs of this CTA in order.  The TMA of iteration it + 1 is issued
+        // right after the MMAs of iteration it (it waits for them to release the operand buffer).
         if (lane == 0) {
             const int kbs = args.k_blocks;
             const int my_jobs = (n_jobs - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
             const uint32_t total = static_cast<uint32_t>(my_jobs) * static_cast<uint32_t>(kbs);
             bool ok = true;
 
+            // tile ids of a job (the second tile of the last job may be missing: its operands repeat the first)
+            auto load_ids = [&](uint32_t j, int &t0, int &t1) {
+                const int job = static_cast<int>(blockIdx.x) + static_cast<int>(j) * static_cast<int>(gridDim.x);
+                t0 = args.tile_ids[2 * job];
+                t1 = ((2 * job + 1) < args.n_tiles) ? args.tile_ids[2 * job + 1] : t0;
+            };
+            int cur0 = 0, cur1 = 0, nxt0 = 0, nxt1 = 0;   // ids of the job being requested / of the one after (read a job ahead of their use)
+            if (my_jobs > 0) load_ids(0, cur0, cur1);
+            if (my_jobs > 1) load_ids(1, nxt0, nxt1);
+
+            // request operand k-block `it` (called once per it, in order)
             auto issue_tma = [&](uint32_t it) -> bool {
-                const uint32_t st = it & 1u, ph = (it >> 1) & 1u;
-                const int job = static_cast<int>(blockIdx.x) + static_cast<int>(it / kbs) * static_cast<int>(gridDim.x);
+                const uint32_t ph = it & 1u;
+                const uint32_t j = it / kbs;
                 const int kb = static_cast<int>(it % kbs);
-                const int t0 = args.tile_ids[2 * job];
-                const int t1 = ((2 * job + 1) < args.n_tiles) ? args.tile_ids[2 * job + 1] : t0;
-                const int r0 = (t0 / args.tiles_per_row) * kDenseTile, c0 = (t0 % args.tiles_per_row) * kDenseTile;
-                const int r1 = (t1 / args.tiles_per_row) * kDenseTile, c1 = (t1 % args.tiles_per_row) * kDenseTile;
-                // stage free again?  (consumed by the MMAs of iteration it - 2)
-                if (!mbar_wait_bounded(&ops_free[st], ph ^ 1u)) return false;
-                unsigned char *sa = smem + DenseSmem::kStage0 + st * DenseSmem::kStageBytes;
+                if (kb == 0 && it > 0) {
+                    cur0 = nxt0;
+                    cur1 = nxt1;
+                    if (j + 1 < static_cast<uint32_t>(my_jobs)) load_ids(j + 1, nxt0, nxt1);
+                }
+                const int r0 = (cur0 / args.tiles_per_row) * kDenseTile, c0 = (cur0 % args.tiles_per_row) * kDenseTile;
+                const int r1 = (cur1 / args.tiles_per_row) * kDenseTile, c1 = (cur1 % args.tiles_per_row) * kDenseTile;
+                // operand buffer free again?  (read by the MMAs of k-block it - 1)
+                if (!mbar_wait_bounded(ops_free, ph ^ 1u)) return false;
+                unsigned char *sa = smem + DenseSmem::kStage0;
                 unsigned char *sb = sa + kOperandBytes;
-                mbar_expect_tx(&ops_full[st], DenseSmem::kStageBytes);
+                mbar_expect_tx(ops_full, DenseSmem::kStageBytes);
                 const int x = kb * 32;
-                tma_load_2d(sa, &map_a, x, r0, &ops_full[st]);
-                tma_load_2d(sa + kHalfOperandBytes, &map_a, x, r1, &ops_full[st]);
-                tma_load_2d(sb, &map_b, x, c0, &ops_full[st]);
-                tma_load_2d(sb + kHalfOperandBytes, &map_b, x, c1, &ops_full[st]);
+                tma_load_2d(sa, &map_a, x, r0, ops_full);
+                tma_load_2d(sa + kHalfOperandBytes, &map_a, x, r1, ops_full);
+                tma_load_2d(sb, &map_b, x, c0, ops_full);
+                tma_load_2d(sb + kHalfOperandBytes, &map_b, x, c1, ops_full);
                 return true;
             };
 
             if (total > 0) ok = issue_tma(0);
             uint32_t jb = 0;  // jobs whose MMAs have been issued (phase of acc_free / acc_full)
             for (uint32_t it = 0; it < total && ok; ++it) {
-                const uint32_t st = it & 1u, ph = (it >> 1) & 1u;
                 const int kb = static_cast<int>(it % kbs);
-                if (it + 1 < total && !issue_tma(it + 1)) { ok = false; break; }
-                if (!mbar_wait_bounded(&ops_full[st], ph)) { ok = false; break; }
+                if (!mbar_wait_bounded(ops_full, it & 1u)) { ok = false; break; }
                 if (kb == 0) {
                     // accumulator drained by the epilogue of the previous job?
                     if (!mbar_wait_bounded(acc_free, (jb & 1u) ^ 1u)) { ok = false; break; }
                 }
                 tcgen05_fence_after();
-                const uint32_t a_s = smem_u32(smem + DenseSmem::kStage0 + st * DenseSmem::kStageBytes);
+                const uint32_t a_s = smem_u32(smem + DenseSmem::kStage0);
                 const uint32_t b_s = a_s + kOperandBytes;
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {  // 4 k-steps of 8 tf32 = 32 bytes inside the swizzle atom
                     const uint32_t adv = static_cast<uint32_t>(ks) * 32u;
                     umma_tf32(tmem_base, umma_smem_desc(a_s + adv), umma_smem_desc(b_s + adv), (kb > 0 || ks > 0) ? 1u : 0u);
                 }
-                umma_commit(&ops_free[st]);  // arrives once the MMAs above have read their operands
+                umma_commit(ops_free);       // arrives once the MMAs above have read their operands
                 if (kb == kbs - 1) {
                     umma_commit(acc_full);   // arrives once the accumulator of this job is complete
                     ++jb;
                 }
+                if (it + 1 < total && !issue_tma(it + 1)) { ok = false; break; }   // refill the operand buffer
             }
             if (!ok) atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
         }
     } else {
         // ===================== epilogue warps =====================
+        // Tile row r belongs to warp r % 8 for the whole kernel (16 rows per warp, two halves of 8).
+        // S.val: the nonzeros of a tile row are one contiguous CSR run; widened to 16-byte granules it
+        // is at most 18 of them, copied by lanes 0..17 with ONE asynchronous 16-byte copy each into
+        // the row's slot of sSval.  A half is requested for the next job as soon as the warp has
+        // sampled it for this job, so the copies run most of a job ahead and no warp waits for
+        // global memory.  Row records (first position, granules, presence mask) run two jobs ahead.
+        // Sampling: lane l owns tile columns l and l+32; the mask says which are nonzeros and the
+        // popcount below the lane is the offset inside the run -> S.val from shared memory, P.val
+        // written in contiguous CSR runs; col_idx is never read.
+        //
+        // cp.async groups of a thread, oldest first, at the points that wait (always "all but 2"):
+        //   before the mid barrier of job n:  [R(n+1)] [A(n)] [B(n)]      -> records of job n+1 landed
+        //   before sampling half A of job n:  [A(n)] [B(n)] [R(n+2)]      -> A(n) landed
+        //   before sampling half B of job n:  [B(n)] [R(n+2)] [A(n+1)]    -> B(n) landed
         const int q = warp & 3;               // TMEM lane quarter this warp may read: rows 32q .. 32q+31
         const int h = warp >> 2;              // which 32 of the tile's 64 columns this warp moves
         const int tile_of_q = q >> 1;         // rows 0-63: first tile, rows 64-127: second tile
-        uint32_t jb = 0;
-        bool ok = true;
-        for (int job = blockIdx.x; job < n_jobs; job += gridDim.x, ++jb) {
-            const bool has1 = (2 * job + 1) < args.n_tiles;
-            // row descriptors of both tiles -> shared memory (threads 0..127: one row each)
-            if (tid < 128) {
-                const int which = tid >> 6;
-                if (which == 0 || has1) {
-                    const DenseTileDesc *d = args.descs + (2 * job + which);
-                    sStart[tid] = d->start[tid & 63];
-                    sMask[tid] = d->mask[tid & 63];
+        const uint32_t below = (1u << lane) - 1u;
+        const int stride_jobs = static_cast<int>(gridDim.x);
+
+        // raw descriptors of one job -> record buffer `buf` (threads 0..127: one tile row each) ...
+        auto fetch_rows = [&](int job, int buf) {
+            if (tid < 128 && job < n_jobs) {
+                uint4 *dst = sRows + buf * 128 + tid;
+                const int t = 2 * job + (tid >> 6);
+                if (t < args.n_tiles) {
+                    const DenseTileDesc *d = args.descs + t;
+                    cp_async_4(&dst->x, &d->start[tid & 63]);
+                    cp_async_8(&dst->z, &d->mask[tid & 63]);
                 } else {
-                    sStart[tid] = 0;
-                    sMask[tid] = 0ull;
+                    *dst = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
+        };
+        // ... and, once they have landed (same thread), the number of 16-byte granules that cover the run
+        auto finish_rows = [&](int job, int buf) {
+            if (tid < 128 && job < n_jobs) {
+                uint4 *dst = sRows + buf * 128 + tid;
+                const uint4 d = *dst;
+                const uint32_t cnt = __popc(d.z) + __popc(d.w);
+                dst->y = cnt ? ((d.x & 3u) + cnt + 3u) >> 2 : 0u;
+            }
+        };
+        auto request_half = [&](int buf, int half) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int r = (8 * half + u) * kDenseEpiWarps + warp;
+                const uint4 d = sRows[buf * 128 + r];
+                if (lane < static_cast<int>(d.y))
+                    cp_async_16(sSval + r * kDenseSvalStride + 4 * lane, args.s_val + (d.x & ~3u) + 4 * lane);
+            }
+        };
+        auto sample_half = [&](int buf, int half) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int r = (8 * half + u) * kDenseEpiWarps + warp;
+                const uint4 d = sRows[buf * 128 + r];
+                const uint32_t mlo = d.z, mhi = d.w;
+                const int st = static_cast<int>(d.x);
+                const int k0 = __popc(mlo & below), k1 = __popc(mlo) + __popc(mhi & below);   // offsets inside the run
+                const float *arow = sAcc + r * kDenseAccStride;
+                const float *srow = sSval + r * kDenseSvalStride + (st & 3);
+                if ((mlo >> lane) & 1u) __stcs(args.p_val + st + k0, arow[lane] * srow[k0]);
+                if ((mhi >> lane) & 1u) __stcs(args.p_val + st + k1, arow[lane + 32] * srow[k1]);
+            }
+        };
+
+        uint32_t jb = 0;
+        bool ok = true;
+        if (static_cast<int>(blockIdx.x) < n_jobs) {   // first job of the CTA: the only exposed fetches
+            fetch_rows(blockIdx.x, 0);
+            cp_async_commit();
+            cp_async_wait_group<0>();
+            finish_rows(blockIdx.x, 0);
+            epi_barrier();
+            fetch_rows(blockIdx.x + stride_jobs, 1);
+            cp_async_commit();
+            request_half(0, 0);
+            cp_async_commit();
+            request_half(0, 1);
+            cp_async_commit();
+        }
+        for (int job = blockIdx.x; job < n_jobs; job += stride_jobs, ++jb) {
+            const int buf = static_cast<int>(jb % 3u), buf1 = static_cast<int>((jb + 1u) % 3u), buf2 = static_cast<int>((jb + 2u) % 3u);
+            const bool has_next = job + stride_jobs < n_jobs;
             if (ok) {   // one lane polls, then the warp re-converges before the warp-wide tcgen05.ld
                 int got = 1;
                 if (lane == 0) {
@@ -274,41 +376,25 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
 #pragma unroll
                 for (int c = 0; c < 32; ++c) row[c] = __uint_as_float(v[c]);
             }
+            cp_async_wait_group<2>();               // this thread's share of the next job's records
+            finish_rows(job + stride_jobs, buf1);
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_free);   // tensor memory may be overwritten by the next job
-            epi_barrier();                          // accumulator + descriptors visible to all epilogue warps
-            if (ok) {
-                // stream the 128 tile rows: warp w takes rows w, w+8, ...; 8 rows in flight per warp
+            epi_barrier();                          // accumulator + next job's records visible to all epilogue warps
+            fetch_rows(job + 2 * stride_jobs, buf2);
+            cp_async_commit();
 #pragma unroll 1
-                for (int rb = warp; rb < 128; rb += 8 * kDenseEpiWarps) {
-                    float sv0[8], sv1[8];
-                    int p0[8], p1[8];
-                    bool on0[8], on1[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int r = rb + u * kDenseEpiWarps;
-                        const unsigned long long m = sMask[r];
-                        const uint32_t mlo = static_cast<uint32_t>(m), mhi = static_cast<uint32_t>(m >> 32);
-                        const uint32_t below = (1u << lane) - 1u;
-                        const int st = sStart[r];
-                        on0[u] = (mlo >> lane) & 1u;
-                        on1[u] = (mhi >> lane) & 1u;
-                        p0[u] = st + __popc(mlo & below);
-                        p1[u] = st + __popc(mlo) + __popc(mhi & below);
-                        sv0[u] = on0[u] ? __ldcs(args.s_val + p0[u]) : 0.f;
-                        sv1[u] = on1[u] ? __ldcs(args.s_val + p1[u]) : 0.f;
-                    }
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int r = rb + u * kDenseEpiWarps;
-                        const float *arow = sAcc + r * kDenseAccStride;
-                        if (on0[u]) __stcs(args.p_val + p0[u], arow[lane] * sv0[u]);
-                        if (on1[u]) __stcs(args.p_val + p1[u], arow[lane + 32] * sv1[u]);
-                    }
-                }
+            for (int half = 0; half < 2; ++half) {
+                cp_async_wait_group<2>();   // this lane's granules of this half ...
+                __syncwarp();               // ... and every other lane's
+                if (ok) sample_half(buf, half);
+                __syncwarp();               // every lane is done with the slots of this half before they are overwritten
+                if (has_next) request_half(buf1, half);
+                cp_async_commit();
             }
-            epi_barrier();  // all rows streamed before the next job overwrites sAcc / descriptors
+            epi_barrier();  // all rows streamed before the next job overwrites sAcc / the oldest record buffer
         }
+        cp_async_wait_group<0>();
     }
 
     tcgen05_fence_before();
