@@ -408,7 +408,7 @@ def main():
             "wall_s_timed_region": wall,
             "plan": {k: plan[k] for k in ("nnz", "rows_nonempty", "cols_touched", "max_row_nnz", "rowtile_nnz", "rowtile_items",
                                           "rowtile_rows_per_stage", "rowtile_grid", "rowtile_smem_bytes", "dense_nnz", "dense_tiles",
-                                          "rowgroup_nnz", "n_kernels")},
+                                          "rowgroup_nnz", "rowgroup_rows", "n_kernels")},
         }
         line["hbm_gb_per_s_algorithmic"] = eng.algorithmic_bytes() / (float(np.mean(step_ms)) * 1e-3) / 1e9
 

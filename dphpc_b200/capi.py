@@ -58,6 +58,8 @@ class PlanInfo(C.Structure):
         ("dense_grid", C.c_int32), ("dense_block", C.c_int32), ("dense_smem_bytes", C.c_int32),
         ("rowgroup_nnz", C.c_int64),
         ("rowgroup_groups", C.c_int32),
+        ("rowgroup_rows", C.c_int32),
+        ("rowgroup_grid", C.c_int32),
         ("n_kernels", C.c_int32), ("n_devices", C.c_int32),
     ]
 

@@ -17,6 +17,7 @@
 
 #include "../../include/sddmm_b200.h"
 #include "kernel_dense_tile.cuh"
+#include "kernel_rowgroup.cuh"
 #include "kernel_rowtile.cuh"
 #include "plan_kernels.cuh"
 
@@ -94,6 +95,11 @@ struct sddmm_b200_engine {
     CUtensorMap map_a, map_b;
     int32_t n_dense = 0;
     int32_t n_residual_items = 0;
+
+    // row-group path (aligned groups of rows with one column list)
+    uint8_t *d_group_ok = nullptr;
+    int32_t rg_rows = 0;           // rows per group (2, 3, 4) when the row-group kernel runs, else 0
+    int32_t rg_groups = 0;         // ceil(M / rg_rows)
 
     // plan
     sddmm_b200_plan_info plan;
@@ -203,6 +209,7 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     const size_t o_coo = coo ? c.take(nnz * 4 + 16) : 0;
     const size_t o_pc = c.take(sizeof(PlanCounters));
     const size_t o_err = c.take(sizeof(int32_t));
+    const size_t o_gok = c.take(M / 2 + 2);   // one byte per aligned row group (groups of >= 2 rows)
     // dense-tile path: only carved when the mode, K and the size of the 64x64 tile grid allow it
     e->tiles_per_row = static_cast<int32_t>((N + 63) / 64);
     e->tile_grid = static_cast<int64_t>((M + 63) / 64) * e->tiles_per_row;
@@ -232,6 +239,7 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     e->d_Ax = split ? reinterpret_cast<float *>(b + o_ax) : nullptr;
     e->d_Bx = split ? reinterpret_cast<float *>(b + o_bx) : nullptr;
     e->d_rp = reinterpret_cast<int32_t *>(b + o_rp);
+    e->d_group_ok = reinterpret_cast<uint8_t *>(b + o_gok);
     e->d_col = reinterpret_cast<int32_t *>(b + o_col);
     e->d_sval = reinterpret_cast<float *>(b + o_sv);
     e->d_pval = reinterpret_cast<float *>(b + o_pv);
@@ -335,6 +343,7 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     if (!st) st = make_operand_map(e, &e->map_b, split ? e->d_Bx : e->d_B32, e->N, kx);
     if (st) return st;
     CU_TRY(e, cudaFuncSetAttribute(sddmm_dense_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DenseSmem::kDynamicBytes));
+    CU_TRY(e, cudaFuncSetAttribute(sddmm_dense_tile_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     e->n_dense = n_dense;
     e->n_residual_items = pc.residual_items;
     sddmm_b200_plan_info &p = e->plan;
@@ -343,11 +352,81 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     p.dense_tile_rows = p.dense_tile_cols = kDenseTile;
     p.dense_block = kDenseThreads;
     p.dense_smem_bytes = static_cast<int32_t>(DenseSmem::kDynamicBytes);
-    p.dense_grid = std::min((n_dense + 1) / 2, e->sm_count * 2);
+    // Resident CTAs per SM, from the kernel's own resources (the runtime's occupancy query answers 1 for this kernel):
+    // shared memory (+1 KB the driver reserves per CTA), registers (allocated per warp in units of 256), tensor memory columns.
+    cudaFuncAttributes fa;
+    CU_TRY(e, cudaFuncGetAttributes(&fa, sddmm_dense_tile_kernel));
+    cudaDeviceProp prop;
+    CU_TRY(e, cudaGetDeviceProperties(&prop, e->device));
+    const int by_smem = static_cast<int>(prop.sharedMemPerMultiprocessor / (DenseSmem::kDynamicBytes + fa.sharedSizeBytes + 1024));
+    const int regs_per_warp = ((fa.numRegs * 32 + 255) / 256) * 256;
+    const int by_regs = prop.regsPerMultiprocessor / (regs_per_warp * (kDenseThreads / 32));
+    const int by_tmem = 512 / kTmemCols;
+    int dense_ctas_per_sm = std::min(std::min(by_smem, by_regs), std::min(by_tmem, kDenseCtasPerSm));
+    if (dense_ctas_per_sm < 1) return fail(e, SDDMM_B200_ERR_CUDA, "dense-tile kernel does not fit on an SM");
+    if (const char *env = getenv("SDDMM_B200_DENSE_CTAS_PER_SM")) {   // tuning knob: fewer resident CTAs per SM
+        const int v = atoi(env);
+        if (v >= 1 && v < dense_ctas_per_sm) dense_ctas_per_sm = v;
+    }
+    p.dense_grid = std::min((n_dense + 1) / 2, e->sm_count * dense_ctas_per_sm);
     return SDDMM_B200_OK;
 }
 
 // Validation + histogram + plan, after the operands are in the arena.
+using RowGroupFn = void (*)(const RowGroupArgs);
+RowGroupFn pick_rowgroup(int rows, int cpl) {
+    if (cpl == 1) return rows == 2 ? sddmm_rowgroup_kernel<2, 1> : rows == 3 ? sddmm_rowgroup_kernel<3, 1> : sddmm_rowgroup_kernel<4, 1>;
+    return rows == 2 ? sddmm_rowgroup_kernel<2, 2> : rows == 3 ? sddmm_rowgroup_kernel<3, 2> : sddmm_rowgroup_kernel<4, 2>;
+}
+
+// Row groups: aligned groups of 2, 3 or 4 consecutive rows with one column list share each gather of B.
+// The path is taken (for the whole matrix) when it removes at least 30 % of the gathers; fp32 storage, K = 32 or 64.
+int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
+    const bool eligible = e->mode != SDDMM_B200_BF16 && !(e->flags & SDDMM_B200_FLAG_NO_ROW_GROUPS) && (e->K == 32 || e->K == 64) &&
+                          e->M >= 4 && base_pc.max_row_nnz <= 8192;
+    if (!eligible) return SDDMM_B200_OK;
+    cudaStream_t s = e->stream;
+    const int cap = e->sm_count * 8;
+    for (int G = 2; G <= 4; ++G) {
+        const int32_t n_groups = static_cast<int32_t>((e->M + G - 1) / G);
+        k_group_match<<<grid_for(static_cast<int64_t>(n_groups) * 32, kBlock, cap), kBlock, 0, s>>>(
+            e->d_rp, e->d_col, static_cast<int32_t>(e->M), G, n_groups, nullptr, &e->d_pc->group_cover[G - 2], &e->d_pc->group_count[G - 2]);
+    }
+    CU_TRY(e, cudaGetLastError());
+    PlanCounters pc;
+    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
+    CU_TRY(e, cudaStreamSynchronize(s));
+    int best = 0;
+    double best_saved = 0.0;
+    for (int G = 2; G <= 4; ++G) {
+        const double saved = static_cast<double>(pc.group_cover[G - 2]) * (1.0 - 1.0 / G);   // gathers of B that disappear
+        if (saved > best_saved) { best_saved = saved; best = G; }
+    }
+    if (best == 0 || best_saved < 0.3 * static_cast<double>(e->nnz)) return SDDMM_B200_OK;
+    const int32_t n_groups = static_cast<int32_t>((e->M + best - 1) / best);
+    CU_TRY(e, cudaMemsetAsync(&e->d_pc->group_cover[best - 2], 0, sizeof(unsigned long long), s));
+    CU_TRY(e, cudaMemsetAsync(&e->d_pc->group_count[best - 2], 0, sizeof(int), s));
+    k_group_match<<<grid_for(static_cast<int64_t>(n_groups) * 32, kBlock, cap), kBlock, 0, s>>>(
+        e->d_rp, e->d_col, static_cast<int32_t>(e->M), best, n_groups, e->d_group_ok, &e->d_pc->group_cover[best - 2],
+        &e->d_pc->group_count[best - 2]);
+    CU_TRY(e, cudaGetLastError());
+    RowGroupFn fn = pick_rowgroup(best, static_cast<int>(e->K / 32));
+    int occ = 0;
+    CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kRowGroupWarps * 32, 0));
+    if (occ < 1) return fail(e, SDDMM_B200_ERR_CUDA, "row-group kernel does not fit on an SM");
+    e->rg_rows = best;
+    e->rg_groups = n_groups;
+    sddmm_b200_plan_info &p = e->plan;
+    p.rowgroup_nnz = static_cast<int64_t>(pc.group_cover[best - 2]);
+    p.rowgroup_groups = pc.group_count[best - 2];
+    p.rowgroup_rows = best;
+    p.rowgroup_grid = std::min((n_groups + kRowGroupWarps - 1) / kRowGroupWarps, e->sm_count * occ);
+    p.rowtile_nnz = 0;
+    p.rowtile_items = 0;
+    p.n_kernels = 1;
+    return SDDMM_B200_OK;
+}
+
 int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
     const int cap = e->sm_count * 8;
     cudaStream_t s = e->stream;
@@ -410,6 +489,12 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
     if (!e->use_scalar) {
         int st = build_dense_plan(e, pc, item_nnz, n_items);
         if (st) return st;
+    }
+    e->rg_rows = 0;
+    if (!e->use_scalar && e->n_dense == 0) {
+        int st = build_rowgroup_plan(e, pc);
+        if (st) return st;
+        if (e->rg_rows) return SDDMM_B200_OK;
     }
     p.rowtile_nnz = e->nnz - p.dense_nnz;
     p.rowtile_items = e->n_residual_items;
@@ -503,6 +588,14 @@ int launch_all(sddmm_b200_engine *e) {
         sddmm_scalar_kernel<<<p.rowtile_grid, kBlock, 0, e->stream>>>(e->d_rp, e->d_col, e->d_sval, e->d_pval, e->d_A32, e->d_B32,
                                                                       static_cast<int32_t>(e->M), static_cast<int32_t>(e->K), e->nnz);
         return mark_kernel(e, "sddmm_scalar_kernel", e->stream);
+    }
+    if (e->rg_rows) {
+        RowGroupArgs g;
+        g.row_ptr = e->d_rp; g.col_idx = e->d_col; g.s_val = e->d_sval; g.p_val = e->d_pval; g.A = e->d_A32; g.B = e->d_B32;
+        g.group_ok = e->d_group_ok; g.M = static_cast<int32_t>(e->M); g.K = static_cast<int32_t>(e->K); g.n_groups = e->rg_groups;
+        if ((st = begin_kernel(e, e->stream))) return st;
+        pick_rowgroup(e->rg_rows, static_cast<int>(e->K / 32))<<<p.rowgroup_grid, kRowGroupWarps * 32, 0, e->stream>>>(g);
+        return mark_kernel(e, "sddmm_rowgroup_kernel", e->stream);
     }
     // the two kernels write disjoint nonzeros: when both run, the row-tile kernel goes to the side stream
     static const bool no_side = std::getenv("SDDMM_B200_NO_SIDE_STREAM") != nullptr;   // tuning / debugging knob

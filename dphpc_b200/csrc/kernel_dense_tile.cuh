@@ -54,6 +54,7 @@ constexpr int kDenseSvalStride = 72;         // floats per staged S.val row: 64 
 constexpr uint32_t kOperandBytes = 128 * 128;  // 128 rows x one 128-byte k-block
 constexpr uint32_t kHalfOperandBytes = 64 * 128;
 constexpr int kTmemCols = 128;
+constexpr int kDenseCtasPerSm = 2;          // resident CTAs per SM the kernel is sized for (shared memory, registers)
 
 // Per dense tile: first nonzero of each of its 64 rows inside the tile's column
 // range (CSR position), and which of the 64 columns are present.
@@ -164,7 +165,7 @@ __device__ __forceinline__ void epi_barrier() {  // the 8 epilogue warps only
     asm volatile("bar.sync 1, %0;" ::"n"(kDenseEpiWarps * 32) : "memory");
 }
 
-__global__ void __launch_bounds__(kDenseThreads, 2)
+__global__ void __launch_bounds__(kDenseThreads, kDenseCtasPerSm)
 sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b) {
     extern __shared__ unsigned char dense_smem_raw[];

@@ -76,8 +76,10 @@ typedef struct sddmm_b200_plan_info {
     int32_t dense_tile_rows, dense_tile_cols;
     int32_t dense_grid, dense_block, dense_smem_bytes;
     /* row groups (consecutive rows with identical column lists) */
-    int64_t rowgroup_nnz;
-    int32_t rowgroup_groups;
+    int64_t rowgroup_nnz;          /* nonzeros inside matching groups (the row-group kernel, when it runs, handles ALL nonzeros) */
+    int32_t rowgroup_groups;       /* matching groups                                  */
+    int32_t rowgroup_rows;         /* rows per aligned group (2, 3, 4); 0: path not taken */
+    int32_t rowgroup_grid;
     int32_t n_kernels;             /* kernels one run() launches                      */
     int32_t n_devices;
 } sddmm_b200_plan_info;

@@ -259,3 +259,59 @@ def test_full_size_properties(engines, oracle, cfg, K, mode):
     # (d) COO upload gives the same bits
     if cfg in (2, 5):
         assert np.array_equal(e.sddmm_coo(d.M, d.N, d.K, d.row_idx(), d.col_idx, d.s_val, d.A, d.B), p)
+
+
+def _blocked_pattern(rng, n_block_rows, G, N, blocks_per_row, break_every=0):
+    """CSR pattern of G x G dense blocks: the G rows of a block row share one column list.
+    break_every > 0 drops the last entry of the last row of every break_every-th block row, so that group does not match."""
+    rp, ci = [0], []
+    for b in range(n_block_rows):
+        bc = np.sort(rng.choice(N // G, size=min(blocks_per_row, N // G), replace=False))
+        cols = (bc[:, None] * G + np.arange(G)[None, :]).ravel()
+        for t in range(G):
+            c = cols[:-1] if (break_every and b % break_every == 0 and t == G - 1) else cols
+            ci.extend(c.tolist())
+            rp.append(len(ci))
+    return np.array(rp, np.int32), np.array(ci, np.int32)
+
+
+@pytest.mark.parametrize("G,K,extra_rows,break_every", [(3, 64, 0, 0), (3, 32, 2, 5), (2, 32, 1, 0), (4, 64, 3, 7), (4, 32, 0, 3)])
+def test_row_groups_share_the_gather(engines, oracle, G, K, extra_rows, break_every):
+    # rows with identical column lists (block rows of G x G blocks) take the row-group kernel; the result is the same
+    rng = np.random.default_rng(100 * G + K + extra_rows)
+    N = 1200
+    rp, ci = _blocked_pattern(rng, 150, G, N, 20, break_every)
+    for _ in range(extra_rows):   # ragged tail: rows that belong to no complete group
+        extra = np.sort(rng.choice(N, size=17, replace=False)).astype(np.int32)
+        ci = np.concatenate([ci, extra])
+        rp = np.concatenate([rp, [len(ci)]]).astype(np.int32)
+    M = len(rp) - 1
+    sv = rng.random(len(ci), dtype=np.float32)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (N, K)).astype(np.float32)
+    for mode in ("fp32", "fp32_tc"):
+        p = check(engines[mode], mode, oracle, M, N, K, rp, ci, sv, A, B, what=f"row groups G={G} K={K} {mode}")
+        plan = engines[mode].plan()
+        assert plan["rowgroup_rows"] == G and plan["n_kernels"] == 1 and plan["rowtile_nnz"] == 0
+        assert [n for n, _ in engines[mode].kernel_times()] == ["sddmm_rowgroup_kernel"]
+        if not break_every:
+            assert plan["rowgroup_nnz"] == int(rp[150 * G])
+        else:
+            assert 0 < plan["rowgroup_nnz"] < int(rp[150 * G])
+    # the same input with the path switched off goes through the row-tile kernel and agrees
+    e = Engine(0, "fp32", flags=2)
+    try:
+        q = e.sddmm_csr(M, N, K, rp, ci, sv, A, B)
+        assert e.plan()["rowgroup_rows"] == 0
+        bound = oracle_lib.abs_dot_bound(oracle.coo_rows(M, rp), ci, sv, A, B)
+        oracle_lib.assert_values_close(q, p, bound, 2e-5, "row-group kernel vs row-tile kernel")
+    finally:
+        e.close()
+
+
+def test_row_groups_not_taken_without_structure(engines):
+    # uniformly random rows: no aligned group matches, the general kernel runs
+    d = Dataset(5, 32, 0.002)
+    e = engines["fp32"]
+    e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    assert e.plan()["rowgroup_rows"] == 0 and e.plan()["rowtile_nnz"] == d.nnz
