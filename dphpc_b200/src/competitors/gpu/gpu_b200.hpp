@@ -30,9 +30,9 @@ class GPUB200 : public SDDMM::Competitor<float> {
     using T = float;
 
 public:
-    // mode: SDDMM_B200_FP32 / _TF32 / _BF16 / _FP32_TC; device: CUDA ordinal
-    explicit GPUB200(int mode = SDDMM_B200_FP32, int device = 0, const std::string &name = "GPU-B200")
-        : SDDMM::Competitor<T>(name), mode_(mode), device_(device) {}
+    // mode: SDDMM_B200_FP32 / _TF32 / _BF16 / _FP32_TC; device: CUDA ordinal; flags: SDDMM_B200_FLAG_* (paths to switch off)
+    explicit GPUB200(int mode = SDDMM_B200_FP32, int device = 0, const std::string &name = "GPU-B200", uint32_t flags = 0)
+        : SDDMM::Competitor<T>(name), mode_(mode), device_(device), flags_(flags) {}
 
     // (the reference's base class has a non-virtual destructor: hold competitors through make_shared, as its main.cpp does)
     ~GPUB200() { sddmm_b200_destroy(engine_); }
@@ -87,13 +87,14 @@ public:
 
 private:
     int mode_, device_;
+    uint32_t flags_;
     sddmm_b200_engine *engine_ = nullptr;
     bool ready_ = false;
 
     bool ensure_engine() {
         ready_ = false;
         if (engine_) return true;
-        const int st = sddmm_b200_create(&engine_, device_, mode_, 0);
+        const int st = sddmm_b200_create(&engine_, device_, mode_, flags_);
         if (st != SDDMM_B200_OK) {
             std::cerr << "[" << name << "] cannot create the engine (status " << st << "): no usable CUDA device?" << std::endl;
             engine_ = nullptr;
