@@ -99,6 +99,7 @@ struct sddmm_b200_engine {
     // row-group path (aligned groups of rows with one column list)
     uint8_t *d_group_ok = nullptr;
     int32_t rg_rows = 0;           // rows per group (2, 3, 4) when the row-group kernel runs, else 0
+    int32_t rg_first = 0;          // first row of the first full group
     int32_t rg_groups = 0;         // ceil(M / rg_rows)
 
     // plan
@@ -209,7 +210,7 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     const size_t o_coo = coo ? c.take(nnz * 4 + 16) : 0;
     const size_t o_pc = c.take(sizeof(PlanCounters));
     const size_t o_err = c.take(sizeof(int32_t));
-    const size_t o_gok = c.take(M / 2 + 2);   // one byte per aligned row group (groups of >= 2 rows)
+    const size_t o_gok = c.take(M / 2 + 4);   // one byte per row group (groups of >= 2 rows, plus the leading partial group)
     // dense-tile path: only carved when the mode, K and the size of the 64x64 tile grid allow it
     e->tiles_per_row = static_cast<int32_t>((N + 63) / 64);
     e->tile_grid = static_cast<int64_t>((M + 63) / 64) * e->tiles_per_row;
@@ -379,7 +380,7 @@ RowGroupFn pick_rowgroup(int rows, int cpl) {
     return rows == 2 ? sddmm_rowgroup_kernel<2, 2> : rows == 3 ? sddmm_rowgroup_kernel<3, 2> : sddmm_rowgroup_kernel<4, 2>;
 }
 
-// Row groups: aligned groups of 2, 3 or 4 consecutive rows with one column list share each gather of B.
+// Row groups: groups of 2, 3 or 4 consecutive rows with one column list (first full group at row 0 .. G-1) share each gather of B.
 // The path is taken (for the whole matrix) when it removes at least 30 % of the gathers; fp32 storage, K = 32 or 64.
 int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     const bool eligible = e->mode != SDDMM_B200_BF16 && !(e->flags & SDDMM_B200_FLAG_NO_ROW_GROUPS) && (e->K == 32 || e->K == 64) &&
@@ -387,38 +388,44 @@ int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     if (!eligible) return SDDMM_B200_OK;
     cudaStream_t s = e->stream;
     const int cap = e->sm_count * 8;
-    for (int G = 2; G <= 4; ++G) {
-        const int32_t n_groups = static_cast<int32_t>((e->M + G - 1) / G);
-        k_group_match<<<grid_for(static_cast<int64_t>(n_groups) * 32, kBlock, cap), kBlock, 0, s>>>(
-            e->d_rp, e->d_col, static_cast<int32_t>(e->M), G, n_groups, nullptr, &e->d_pc->group_cover[G - 2], &e->d_pc->group_count[G - 2]);
-    }
+    // candidates: G = 2, 3, 4 rows per group, first full group starting at row 0 .. G-1 (9 counting passes, counters slot = G(G-1)/2 - 1 + first)
+    auto slot = [](int G, int first) { return G * (G - 1) / 2 - 1 + first; };
+    auto groups_of = [&](int G, int first) { return static_cast<int32_t>(1 + (e->M - first + G - 1) / G); };
+    for (int G = 2; G <= 4; ++G)
+        for (int first = 0; first < G; ++first)
+            k_group_match<<<grid_for(static_cast<int64_t>(groups_of(G, first)) * 32, kBlock, cap), kBlock, 0, s>>>(
+                e->d_rp, e->d_col, static_cast<int32_t>(e->M), G, first, groups_of(G, first), nullptr, &e->d_pc->group_cover[slot(G, first)],
+                &e->d_pc->group_count[slot(G, first)]);
     CU_TRY(e, cudaGetLastError());
     PlanCounters pc;
     CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
     CU_TRY(e, cudaStreamSynchronize(s));
-    int best = 0;
+    int best = 0, best_first = 0;
     double best_saved = 0.0;
-    for (int G = 2; G <= 4; ++G) {
-        const double saved = static_cast<double>(pc.group_cover[G - 2]) * (1.0 - 1.0 / G);   // gathers of B that disappear
-        if (saved > best_saved) { best_saved = saved; best = G; }
-    }
+    for (int G = 2; G <= 4; ++G)
+        for (int first = 0; first < G; ++first) {
+            const double saved = static_cast<double>(pc.group_cover[slot(G, first)]) * (1.0 - 1.0 / G);   // gathers of B that disappear
+            if (saved > best_saved) { best_saved = saved; best = G; best_first = first; }
+        }
     if (best == 0 || best_saved < 0.3 * static_cast<double>(e->nnz)) return SDDMM_B200_OK;
-    const int32_t n_groups = static_cast<int32_t>((e->M + best - 1) / best);
-    CU_TRY(e, cudaMemsetAsync(&e->d_pc->group_cover[best - 2], 0, sizeof(unsigned long long), s));
-    CU_TRY(e, cudaMemsetAsync(&e->d_pc->group_count[best - 2], 0, sizeof(int), s));
+    const int32_t n_groups = groups_of(best, best_first);
+    const int bs = slot(best, best_first);
+    CU_TRY(e, cudaMemsetAsync(&e->d_pc->group_cover[bs], 0, sizeof(unsigned long long), s));
+    CU_TRY(e, cudaMemsetAsync(&e->d_pc->group_count[bs], 0, sizeof(int), s));
     k_group_match<<<grid_for(static_cast<int64_t>(n_groups) * 32, kBlock, cap), kBlock, 0, s>>>(
-        e->d_rp, e->d_col, static_cast<int32_t>(e->M), best, n_groups, e->d_group_ok, &e->d_pc->group_cover[best - 2],
-        &e->d_pc->group_count[best - 2]);
+        e->d_rp, e->d_col, static_cast<int32_t>(e->M), best, best_first, n_groups, e->d_group_ok, &e->d_pc->group_cover[bs],
+        &e->d_pc->group_count[bs]);
     CU_TRY(e, cudaGetLastError());
     RowGroupFn fn = pick_rowgroup(best, static_cast<int>(e->K / 32));
     int occ = 0;
     CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kRowGroupWarps * 32, 0));
     if (occ < 1) return fail(e, SDDMM_B200_ERR_CUDA, "row-group kernel does not fit on an SM");
     e->rg_rows = best;
+    e->rg_first = best_first;
     e->rg_groups = n_groups;
     sddmm_b200_plan_info &p = e->plan;
-    p.rowgroup_nnz = static_cast<int64_t>(pc.group_cover[best - 2]);
-    p.rowgroup_groups = pc.group_count[best - 2];
+    p.rowgroup_nnz = static_cast<int64_t>(pc.group_cover[bs]);
+    p.rowgroup_groups = pc.group_count[bs];
     p.rowgroup_rows = best;
     p.rowgroup_grid = std::min((n_groups + kRowGroupWarps - 1) / kRowGroupWarps, e->sm_count * occ);
     p.rowtile_nnz = 0;
@@ -592,7 +599,7 @@ int launch_all(sddmm_b200_engine *e) {
     if (e->rg_rows) {
         RowGroupArgs g;
         g.row_ptr = e->d_rp; g.col_idx = e->d_col; g.s_val = e->d_sval; g.p_val = e->d_pval; g.A = e->d_A32; g.B = e->d_B32;
-        g.group_ok = e->d_group_ok; g.M = static_cast<int32_t>(e->M); g.K = static_cast<int32_t>(e->K); g.n_groups = e->rg_groups;
+        g.group_ok = e->d_group_ok; g.M = static_cast<int32_t>(e->M); g.K = static_cast<int32_t>(e->K); g.first = e->rg_first; g.n_groups = e->rg_groups;
         if ((st = begin_kernel(e, e->stream))) return st;
         pick_rowgroup(e->rg_rows, static_cast<int>(e->K / 32))<<<p.rowgroup_grid, kRowGroupWarps * 32, 0, e->stream>>>(g);
         return mark_kernel(e, "sddmm_rowgroup_kernel", e->stream);

@@ -2,7 +2,9 @@
 // (the dense G x G blocks of multi-degree-of-freedom discretisations: every one of
 // the G rows of a block row touches the same columns) share one gather of B.
 //
-// Rows are taken in aligned groups of G (rows G*g .. G*g+G-1).  A group whose rows
+// Rows are taken in groups of G consecutive rows starting at row `first` (0 <= first < G; the
+// rows before it form a leading group that never matches, so that a row shard cut anywhere
+// still lines up with the block rows).  A group whose rows
 // all have the same column list is processed as one unit: each B row is read ONCE
 // into registers and dotted with the G rows of A, so the traffic between L2/L1
 // and the SM -- what bounds the general kernel -- drops by the factor G.  Groups
@@ -32,24 +34,32 @@ struct RowGroupArgs {
     float *p_val;             // nnz
     const float *A;           // M x K
     const float *B;           // N x K
-    const uint8_t *group_ok;  // per aligned group: 1 if its G rows have one column list
+    const uint8_t *group_ok;  // per group: 1 if its G rows have one column list
     int32_t M, K;
-    int32_t n_groups;         // ceil(M / G)
+    int32_t first;            // group 0 = rows [0, first); group g >= 1 = rows [first + (g-1) G, first + g G)
+    int32_t n_groups;         // 1 + ceil((M - first) / G)
 };
+
+// rows of group g
+__device__ __forceinline__ void group_rows(int32_t g, int32_t G, int32_t first, int32_t M, int32_t &r0, int32_t &r1) {
+    r0 = g == 0 ? 0 : first + (g - 1) * G;
+    r1 = g == 0 ? first : min(r0 + G, M);
+}
 
 constexpr int kRowGroupWarps = 8;
 
 // Which aligned groups of G rows share one column list.  One warp per group.
 // cover += nonzeros inside matching groups; groups += matching groups.
-__global__ void k_group_match(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t G,
+__global__ void k_group_match(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t G, int32_t first,
                               int32_t n_groups, uint8_t *__restrict__ group_ok, unsigned long long *__restrict__ cover,
                               int *__restrict__ groups) {
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
     const int64_t n_warps = (gridDim.x * static_cast<int64_t>(blockDim.x)) >> 5;
     for (int64_t g = warp0; g < n_groups; g += n_warps) {
-        const int32_t r0 = static_cast<int32_t>(g) * G;
-        bool ok = r0 + G <= M;
+        int32_t r0, r1;
+        group_rows(static_cast<int32_t>(g), G, first, M, r0, r1);
+        bool ok = g > 0 && r1 - r0 == G;
         int32_t len = 0;
         if (ok) {
             const int32_t s0 = rp[r0];
@@ -131,11 +141,11 @@ __global__ void __launch_bounds__(kRowGroupWarps * 32, 2) sddmm_rowgroup_kernel(
     const int32_t warp0 = blockIdx.x * kRowGroupWarps + (threadIdx.x >> 5);
     const int32_t n_warps = gridDim.x * kRowGroupWarps;
     for (int32_t g = warp0; g < a.n_groups; g += n_warps) {
-        const int32_t r0 = g * G;
+        int32_t r0, r1;
+        group_rows(g, G, a.first, a.M, r0, r1);
         if (a.group_ok[g]) {   // warp-uniform
             rowgroup_unit<G, CPL>(a, r0, lane);
         } else {
-            const int32_t r1 = min(r0 + G, a.M);
             for (int32_t r = r0; r < r1; ++r) rowgroup_unit<1, CPL>(a, r, lane);
         }
     }

@@ -18,7 +18,7 @@ struct PlanCounters {
     unsigned long long cols_touched;
     unsigned long long dense_nnz;
     unsigned long long rowgroup_nnz;
-    unsigned long long group_cover[3];   // nonzeros inside matching aligned row groups of 2, 3, 4 rows
+    unsigned long long group_cover[9];   // nonzeros inside matching row groups: 2, 3, 4 rows per group x first full group at row 0 .. G-1
     int max_row_nnz;
     int bad_row_ptr;   // row_ptr not monotone / wrong ends
     int bad_col;       // column index outside [0, N)
@@ -27,7 +27,7 @@ struct PlanCounters {
     int bad_coo;       // COO row index out of range or decreasing
     int dense_tiles;
     int rowgroups;
-    int group_count[3];                  // matching aligned row groups of 2, 3, 4 rows
+    int group_count[9];                  // matching row groups, same slots
     int residual_items;
 };
 

@@ -275,12 +275,19 @@ def _blocked_pattern(rng, n_block_rows, G, N, blocks_per_row, break_every=0):
     return np.array(rp, np.int32), np.array(ci, np.int32)
 
 
-@pytest.mark.parametrize("G,K,extra_rows,break_every", [(3, 64, 0, 0), (3, 32, 2, 5), (2, 32, 1, 0), (4, 64, 3, 7), (4, 32, 0, 3)])
-def test_row_groups_share_the_gather(engines, oracle, G, K, extra_rows, break_every):
-    # rows with identical column lists (block rows of G x G blocks) take the row-group kernel; the result is the same
-    rng = np.random.default_rng(100 * G + K + extra_rows)
+@pytest.mark.parametrize("G,K,extra_rows,break_every,lead_rows", [(3, 64, 0, 0, 0), (3, 32, 2, 5, 1), (2, 32, 1, 0, 1), (4, 64, 3, 7, 0),
+                                                                  (4, 32, 0, 3, 3), (3, 64, 1, 0, 2)])
+def test_row_groups_share_the_gather(engines, oracle, G, K, extra_rows, break_every, lead_rows):
+    # rows with identical column lists (block rows of G x G blocks) take the row-group kernel; the result is the same.
+    # lead_rows: rows in front of the first block row (a row shard cut in the middle of a block row)
+    rng = np.random.default_rng(100 * G + K + extra_rows + 7 * lead_rows)
     N = 1200
     rp, ci = _blocked_pattern(rng, 150, G, N, 20, break_every)
+    for _ in range(lead_rows):
+        lead = np.sort(rng.choice(N, size=23, replace=False)).astype(np.int32)
+        ci = np.concatenate([lead, ci])
+        rp = np.concatenate([[0], rp + len(lead)]).astype(np.int32)
+    blocked_nnz = int(rp[lead_rows + 150 * G] - rp[lead_rows])
     for _ in range(extra_rows):   # ragged tail: rows that belong to no complete group
         extra = np.sort(rng.choice(N, size=17, replace=False)).astype(np.int32)
         ci = np.concatenate([ci, extra])
@@ -295,9 +302,9 @@ def test_row_groups_share_the_gather(engines, oracle, G, K, extra_rows, break_ev
         assert plan["rowgroup_rows"] == G and plan["n_kernels"] == 1 and plan["rowtile_nnz"] == 0
         assert [n for n, _ in engines[mode].kernel_times()] == ["sddmm_rowgroup_kernel"]
         if not break_every:
-            assert plan["rowgroup_nnz"] == int(rp[150 * G])
+            assert plan["rowgroup_nnz"] == blocked_nnz
         else:
-            assert 0 < plan["rowgroup_nnz"] < int(rp[150 * G])
+            assert 0 < plan["rowgroup_nnz"] < blocked_nnz
     # the same input with the path switched off goes through the row-tile kernel and agrees
     e = Engine(0, "fp32", flags=2)
     try:
