@@ -357,11 +357,12 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     // shared memory (+1 KB the driver reserves per CTA), registers (allocated per warp in units of 256), tensor memory columns.
     cudaFuncAttributes fa;
     CU_TRY(e, cudaFuncGetAttributes(&fa, sddmm_dense_tile_kernel));
-    cudaDeviceProp prop;
-    CU_TRY(e, cudaGetDeviceProperties(&prop, e->device));
-    const int by_smem = static_cast<int>(prop.sharedMemPerMultiprocessor / (DenseSmem::kDynamicBytes + fa.sharedSizeBytes + 1024));
+    int smem_per_sm = 0, regs_per_sm = 0;   // (single attributes: the full property query takes milliseconds)
+    CU_TRY(e, cudaDeviceGetAttribute(&smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, e->device));
+    CU_TRY(e, cudaDeviceGetAttribute(&regs_per_sm, cudaDevAttrMaxRegistersPerMultiprocessor, e->device));
+    const int by_smem = static_cast<int>(static_cast<size_t>(smem_per_sm) / (DenseSmem::kDynamicBytes + fa.sharedSizeBytes + 1024));
     const int regs_per_warp = ((fa.numRegs * 32 + 255) / 256) * 256;
-    const int by_regs = prop.regsPerMultiprocessor / (regs_per_warp * (kDenseThreads / 32));
+    const int by_regs = regs_per_sm / (regs_per_warp * (kDenseThreads / 32));
     const int by_tmem = 512 / kTmemCols;
     int dense_ctas_per_sm = std::min(std::min(by_smem, by_regs), std::min(by_tmem, kDenseCtasPerSm));
     if (dense_ctas_per_sm < 1) return fail(e, SDDMM_B200_ERR_CUDA, "dense-tile kernel does not fit on an SM");
