@@ -23,7 +23,8 @@ HERE = Path(__file__).resolve().parent
 ORACLE_LIB = HERE / "liboracle.so"
 REF_DIR = HERE / "_ref"
 REF_LIB = REF_DIR / "libsddmm_ref.so"
-REFERENCE_ROOT = Path(os.environ.get("SDDMM_REFERENCE_ROOT", "/root/reference"))
+# the reference checkout: SDDMM_REFERENCE_ROOT, else a directory "reference" beside this repository
+REFERENCE_ROOT = Path(os.environ.get("SDDMM_REFERENCE_ROOT", str(HERE.parent.parent / "reference")))
 CUDA_INCLUDE = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
 
 

@@ -10,7 +10,7 @@ ROOT = Path(__file__).resolve().parent.parent
 PKG = ROOT / "dphpc_b200"
 SRC = PKG / "src"
 OUT = ROOT / "tests" / "cpp" / "_build"
-REFERENCE = Path(os.environ.get("SDDMM_REFERENCE_ROOT", "/root/reference"))
+REFERENCE = Path(os.environ.get("SDDMM_REFERENCE_ROOT", str(ROOT.parent / "reference")))   # the reference checkout, beside this repository
 
 
 def compile_cpp(name, sources, extra=()):
