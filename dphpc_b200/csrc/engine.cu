@@ -392,11 +392,12 @@ int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     // candidates: G = 2, 3, 4 rows per group, first full group starting at row 0 .. G-1 (9 counting passes, counters slot = G(G-1)/2 - 1 + first)
     auto slot = [](int G, int first) { return G * (G - 1) / 2 - 1 + first; };
     auto groups_of = [&](int G, int first) { return static_cast<int32_t>(1 + (e->M - first + G - 1) / G); };
+    const int every = e->M > 65536 ? 16 : 1;   // large inputs: choose G and `first` on a 1-in-16 sample of the groups
     for (int G = 2; G <= 4; ++G)
         for (int first = 0; first < G; ++first)
-            k_group_match<<<grid_for(static_cast<int64_t>(groups_of(G, first)) * 32, kBlock, cap), kBlock, 0, s>>>(
-                e->d_rp, e->d_col, static_cast<int32_t>(e->M), G, first, groups_of(G, first), nullptr, &e->d_pc->group_cover[slot(G, first)],
-                &e->d_pc->group_count[slot(G, first)]);
+            k_group_match<<<grid_for(static_cast<int64_t>(groups_of(G, first) / every + 1) * 32, kBlock, cap), kBlock, 0, s>>>(
+                e->d_rp, e->d_col, static_cast<int32_t>(e->M), G, first, groups_of(G, first), every, nullptr,
+                &e->d_pc->group_cover[slot(G, first)], &e->d_pc->group_count[slot(G, first)]);
     CU_TRY(e, cudaGetLastError());
     PlanCounters pc;
     CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
@@ -405,7 +406,7 @@ int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     double best_saved = 0.0;
     for (int G = 2; G <= 4; ++G)
         for (int first = 0; first < G; ++first) {
-            const double saved = static_cast<double>(pc.group_cover[slot(G, first)]) * (1.0 - 1.0 / G);   // gathers of B that disappear
+            const double saved = static_cast<double>(pc.group_cover[slot(G, first)]) * every * (1.0 - 1.0 / G);   // gathers of B that disappear (estimate)
             if (saved > best_saved) { best_saved = saved; best = G; best_first = first; }
         }
     if (best == 0 || best_saved < 0.3 * static_cast<double>(e->nnz)) return SDDMM_B200_OK;
@@ -414,9 +415,12 @@ int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     CU_TRY(e, cudaMemsetAsync(&e->d_pc->group_cover[bs], 0, sizeof(unsigned long long), s));
     CU_TRY(e, cudaMemsetAsync(&e->d_pc->group_count[bs], 0, sizeof(int), s));
     k_group_match<<<grid_for(static_cast<int64_t>(n_groups) * 32, kBlock, cap), kBlock, 0, s>>>(
-        e->d_rp, e->d_col, static_cast<int32_t>(e->M), best, best_first, n_groups, e->d_group_ok, &e->d_pc->group_cover[bs],
+        e->d_rp, e->d_col, static_cast<int32_t>(e->M), best, best_first, n_groups, 1, e->d_group_ok, &e->d_pc->group_cover[bs],
         &e->d_pc->group_count[bs]);
     CU_TRY(e, cudaGetLastError());
+    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));   // exact counts of the chosen grouping
+    CU_TRY(e, cudaStreamSynchronize(s));
+    if (static_cast<double>(pc.group_cover[bs]) * (1.0 - 1.0 / best) < 0.3 * static_cast<double>(e->nnz)) return SDDMM_B200_OK;   // the sample overestimated
     RowGroupFn fn = pick_rowgroup(best, static_cast<int>(e->K / 32));
     int occ = 0;
     CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kRowGroupWarps * 32, 0));

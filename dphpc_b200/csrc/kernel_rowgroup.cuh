@@ -48,15 +48,16 @@ __device__ __forceinline__ void group_rows(int32_t g, int32_t G, int32_t first, 
 
 constexpr int kRowGroupWarps = 8;
 
-// Which aligned groups of G rows share one column list.  One warp per group.
+// Which groups of G rows share one column list.  One warp per group; only every `every`-th group is
+// looked at (every > 1: a sample, to choose G and `first` cheaply; group_ok is then not written).
 // cover += nonzeros inside matching groups; groups += matching groups.
 __global__ void k_group_match(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t G, int32_t first,
-                              int32_t n_groups, uint8_t *__restrict__ group_ok, unsigned long long *__restrict__ cover,
+                              int32_t n_groups, int32_t every, uint8_t *__restrict__ group_ok, unsigned long long *__restrict__ cover,
                               int *__restrict__ groups) {
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
     const int64_t n_warps = (gridDim.x * static_cast<int64_t>(blockDim.x)) >> 5;
-    for (int64_t g = warp0; g < n_groups; g += n_warps) {
+    for (int64_t g = warp0 * every; g < n_groups; g += n_warps * every) {
         int32_t r0, r1;
         group_rows(static_cast<int32_t>(g), G, first, M, r0, r1);
         bool ok = g > 0 && r1 - r0 == G;
