@@ -70,6 +70,23 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
         : "memory");
 }
 
+// ---- asynchronous copies global -> shared, tracked per thread in groups ------------
+__device__ __forceinline__ void cp_async_4(void *dst_smem, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_8(void *dst_smem, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void *dst_smem, const void *src) {   // both 16-byte aligned; not kept in L1
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {   // all but the N most recent groups of this thread have landed
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // ---- element helpers ---------------------------------------------------------
 // A "chunk" is 4 consecutive K elements: a float4 for fp32 storage, 4 bf16
 // (8 bytes) for bf16 storage.  dot4 accumulates one chunk pair in fp32.

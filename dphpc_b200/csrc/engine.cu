@@ -27,7 +27,7 @@ namespace {
 
 constexpr size_t kAlign = 256;
 constexpr int kBlock = 256;
-constexpr int kMaxStageBytes = 64 * 1024;  // A rows staged per CTA
+constexpr int kMaxStageBytes = 32 * 1024;  // A rows per stage buffer (a CTA holds two)
 constexpr int kDenseMinCount = 2048;       // a 64x64 tile is "dense" from half full
 
 struct Arena {
@@ -528,8 +528,7 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
     const int64_t r_max = std::max<int64_t>(1, static_cast<int64_t>(kMaxStageBytes / (static_cast<size_t>(e->K) * eb)));
     R = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(R, r_max), e->M));
     p.rowtile_rows_per_stage = static_cast<int32_t>(R);
-    const size_t a_bytes = (static_cast<size_t>(R) * e->K * eb + 15) & ~size_t(15);
-    p.rowtile_smem_bytes = static_cast<int32_t>(a_bytes + (R + 1) * 4);
+    p.rowtile_smem_bytes = static_cast<int32_t>(rowtile_smem_bytes(static_cast<int>(R), static_cast<uint32_t>(e->K * eb)));
 
     const void *fn = (e->mode == SDDMM_B200_BF16) ? reinterpret_cast<const void *>(pick_rowtile<__nv_bfloat16>(e->cpl, e->K == 32 * e->cpl))
                                                   : reinterpret_cast<const void *>(pick_rowtile<float>(e->cpl, e->K == 32 * e->cpl));
@@ -933,7 +932,7 @@ int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int6
     int64_t R = kPreallocItemNnz / std::max<int64_t>(1, nnz / M) + 1;
     R = (R + 7) / 8 * 8;
     R = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(R, kMaxStageBytes / (K * 4)), M));
-    const int smem = static_cast<int>(((static_cast<size_t>(R) * K * 4 + 15) & ~size_t(15)) + (R + 1) * 4);
+    const int smem = static_cast<int>(rowtile_smem_bytes(static_cast<int>(R), static_cast<uint32_t>(K * 4)));
     const bool exact = (K == 32 * cpl);
     RowTileFn<float> fn = pick_rowtile<float>(cpl, exact);
     if (cudaFuncSetAttribute(reinterpret_cast<const void *>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return SDDMM_B200_ERR_CUDA;

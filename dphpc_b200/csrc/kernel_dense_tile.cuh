@@ -144,23 +144,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
         : "memory");
 }
 
-// Ampere-style asynchronous copies global -> shared (4 or 8 bytes per thread), tracked per thread in groups.
-__device__ __forceinline__ void cp_async_4(void *dst_smem, const void *src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_8(void *dst_smem, const void *src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_16(void *dst_smem, const void *src) {   // both 16-byte aligned; not kept in L1
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait_group() {   // all but the N most recent groups of this thread have landed
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
 __device__ __forceinline__ void epi_barrier() {  // the 8 epilogue warps only
     asm volatile("bar.sync 1, %0;" ::"n"(kDenseEpiWarps * 32) : "memory");
 }

@@ -48,6 +48,16 @@ struct RowTileArgs {
 };
 
 constexpr int kRowTileWarps = 8;
+
+// Dynamic shared memory of the row-tile kernel: two stage buffers, each = R staged rows of A (row_bytes each,
+// rounded up to 16 bytes) + R + 1 row_ptr entries, rounded up to 16 bytes.
+__host__ __device__ inline uint32_t rowtile_buffer_bytes(int rows_per_stage, uint32_t row_bytes) {
+    const uint32_t a_stage_bytes = (static_cast<uint32_t>(rows_per_stage) * row_bytes + 15u) & ~15u;
+    return (a_stage_bytes + (static_cast<uint32_t>(rows_per_stage) + 1u) * 4u + 15u) & ~15u;
+}
+__host__ __device__ inline uint32_t rowtile_smem_bytes(int rows_per_stage, uint32_t row_bytes) {
+    return 2u * rowtile_buffer_bytes(rows_per_stage, row_bytes);
+}
 #ifndef SDDMM_ROWTILE_MINB1
 #define SDDMM_ROWTILE_MINB1 4   // resident CTAs per SM the compiler must allow for, K <= 32
 #endif
@@ -59,17 +69,15 @@ template <int CPL, bool EXACT, typename ET>
 __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE_MINB1 : SDDMM_ROWTILE_MINBN) sddmm_rowtile_kernel(const RowTileArgs args) {
     using chunk_t = typename ChunkOf<ET>::type;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t bar[2];
     __shared__ __align__(16) int32_t sRowOff[kRowTileWarps][32];
 
     const int K = args.K;
     const int R = args.rows_per_stage;
     const int nchunks = EXACT ? 8 * CPL : (K >> 2);
     const uint32_t row_bytes = static_cast<uint32_t>(nchunks) * sizeof(chunk_t);
-    ET *sA = reinterpret_cast<ET *>(smem_raw);
-    const chunk_t *sAc = reinterpret_cast<const chunk_t *>(smem_raw);
     const uint32_t a_stage_bytes = (static_cast<uint32_t>(R) * row_bytes + 15u) & ~15u;
-    int32_t *sRp = reinterpret_cast<int32_t *>(smem_raw + a_stage_bytes);
+    const uint32_t buf_bytes = rowtile_buffer_bytes(R, row_bytes);
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -78,36 +86,76 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
     const int gbase = lane & ~7;      // first lane of the group
 
     if (tid == 0) {
-        mbar_init(&bar, 1);
+        mbar_init(&bar[0], 1);
+        mbar_init(&bar[1], 1);
         fence_mbar_init();
     }
     fence_proxy_async_smem();
     __syncthreads();
-    uint32_t phase = 0;
+    uint32_t phases = 0;   // bit b: parity the next wait on bar[b] uses
 
     // this lane's chunk of every B row
     const unsigned char *Bl = reinterpret_cast<const unsigned char *>(args.B) + gl * sizeof(chunk_t);
     constexpr int QS = (CPL >= 2) ? 2 : 1;  // chunks gathered per nonzero per step
 
-    for (int it = blockIdx.x; it < args.n_items; it += gridDim.x) {
+    // A stage = up to R consecutive rows of one work item.  The stages of a CTA form one sequence (stages of an
+    // item, then the next item of the CTA); the rows and row_ptr entries of stage s+1 are requested (bulk copy +
+    // 4-byte asynchronous copies, into the other buffer) before stage s is processed.
+    const int nnz32 = static_cast<int>(args.nnz);   // nonzero indices fit 32 bits (int32 row_ptr; nnz < 2^31 - 8192)
+    auto load_item = [&](int it, int &j_lo, int &j_hi, int &r_lo, int &r_hi) {
         const int item = args.item_ids ? args.item_ids[it] : it;
-        // nonzero indices fit 32 bits (int32 row_ptr; the engine keeps nnz below 2^31 - 8192 so that the
-        // window arithmetic below cannot overflow)
-        const int nnz32 = static_cast<int>(args.nnz);
-        const int j_lo = item * args.item_nnz;
-        const int j_hi = j_lo + min(nnz32 - j_lo, args.item_nnz);
+        j_lo = item * args.item_nnz;
+        j_hi = j_lo + min(nnz32 - j_lo, args.item_nnz);
         const int2 rr = args.item_rows[item];
-        const int r_lo = rr.x, r_hi = rr.y;
+        r_lo = rr.x;
+        r_hi = rr.y;
+    };
+    auto issue_stage = [&](int b, int r0, int nr) {
+        unsigned char *base = smem_raw + static_cast<uint32_t>(b) * buf_bytes;
+        int32_t *rp_s = reinterpret_cast<int32_t *>(base + a_stage_bytes);
+        for (int t = tid; t <= nr; t += blockDim.x) cp_async_4(&rp_s[t], args.row_ptr + r0 + t);
+        if (tid == 0) {
+            const uint32_t bytes = static_cast<uint32_t>(nr) * row_bytes;
+            fence_proxy_async_smem();   // the buffer was read (generic proxy) in the stage before the previous one
+            mbar_expect_tx(&bar[b], bytes);
+            bulk_g2s(base, reinterpret_cast<const unsigned char *>(args.A) + static_cast<uint64_t>(r0) * row_bytes, bytes, &bar[b]);
+        }
+    };
 
-        for (int r0 = r_lo; r0 <= r_hi; r0 += R) {
-            const int nr = min(R, r_hi - r0 + 1);
-            for (int t = tid; t <= nr; t += blockDim.x) sRp[t] = args.row_ptr[r0 + t];
-            if (tid == 0) {
-                const uint32_t bytes = static_cast<uint32_t>(nr) * row_bytes;
-                mbar_expect_tx(&bar, bytes);
-                bulk_g2s(sA, reinterpret_cast<const unsigned char *>(args.A) + static_cast<uint64_t>(r0) * row_bytes, bytes, &bar);
+    int it = blockIdx.x;
+    if (it >= args.n_items) return;
+    int j_lo, j_hi, r_lo, r_hi;
+    load_item(it, j_lo, j_hi, r_lo, r_hi);
+    int r0 = r_lo;
+    int nr = min(R, r_hi - r0 + 1);
+    int b = 0;
+    issue_stage(0, r0, nr);
+    cp_async_commit();
+
+    while (true) {
+        // ---- request the stage after this one (its parameters are recomputed when the CTA moves on: nothing
+        //      but `has_next` stays live across the window loop) ------------------------------------------
+        bool has_next = true;
+        {
+            int n_r0 = r0 + R, n_r_hi = r_hi;
+            if (n_r0 > r_hi) {
+                const int n_it = it + gridDim.x;
+                if (n_it < args.n_items) {
+                    int n_j_lo, n_j_hi;
+                    load_item(n_it, n_j_lo, n_j_hi, n_r0, n_r_hi);
+                } else {
+                    has_next = false;
+                }
             }
-            __syncthreads();
+            if (has_next) issue_stage(b ^ 1, n_r0, min(R, n_r_hi - n_r0 + 1));
+        }
+        cp_async_commit();   // (an empty group when there is no next stage: the count below stays valid)
+
+        {
+            const chunk_t *sAc = reinterpret_cast<const chunk_t *>(smem_raw + static_cast<uint32_t>(b) * buf_bytes);
+            const int32_t *sRp = reinterpret_cast<const int32_t *>(smem_raw + static_cast<uint32_t>(b) * buf_bytes + a_stage_bytes);
+            cp_async_wait_group<1>();   // this thread's row_ptr entries of the current stage
+            __syncthreads();            // ... and everybody else's
 
             const int s_lo = max(j_lo, sRp[0]);
             const int s_hi = min(j_hi, sRp[nr]);
@@ -139,11 +187,15 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
                 }
             };
             if (wb < s_hi) request_window(wb);   // in flight while the A rows land
-            if (!mbar_wait_bounded(&bar, phase)) {
+            if (!mbar_wait_bounded(&bar[b], (phases >> b) & 1u)) {
                 atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
-                return;  // every thread of the CTA waits on the same phase, so all leave together
+                // every thread of the CTA waits on the same phase, so all leave together -- after the copies
+                // already requested for the next stage have landed (bounded again)
+                cp_async_wait_all();
+                if (has_next) mbar_wait_bounded(&bar[b ^ 1], (phases >> (b ^ 1)) & 1u);
+                return;
             }
-            phase ^= 1u;
+            phases ^= 1u << b;
             for (; wb < s_hi; wb += kRowTileWarps * 32) {
                 const int j = wb + lane;
                 const bool full = (wb >= s_lo) && (wb + 32 <= s_hi);   // warp-uniform
@@ -279,8 +331,18 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
                 const float dot = group8_transpose_reduce(acc, gl);
                 if (valid) __stcs(args.p_val + j, dot * s);
             }
-            __syncthreads();  // all reads of sA / sRp done before the next stage overwrites them
+            __syncthreads();  // all reads of this buffer done before the stage after the next one overwrites it
         }
+        if (!has_next) break;
+        if (r0 + R <= r_hi) {
+            r0 += R;
+        } else {
+            it += gridDim.x;
+            load_item(it, j_lo, j_hi, r_lo, r_hi);
+            r0 = r_lo;
+        }
+        nr = min(R, r_hi - r0 + 1);
+        b ^= 1;
     }
 }
 
