@@ -208,7 +208,7 @@ def run_reference_arm(args, rank, world):
         "impl": "reference", "metric": "SDDMM GFLOP/s (2*nnz*K/t)", "value": val, "unit": "GFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": tm * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(cfg, K, "fp32", 1),
+        "config": workload_config(cfg, K, args.mode, max(1, args.gpus)),   # the same workload description as the GPU arm prints
         "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": 1, "kind": "reference" if ref is not None else "port",
                          "sample": f"each step = CPUBasic::run_csr over rows [0,{r_end}) = {nnz_s} of {d.nnz} nnz",
                          "host_cores_available": os.cpu_count()},
