@@ -66,6 +66,17 @@ def hbm_peak():
     return FALLBACK_HBM_GBS, "fallback 6650 GB/s (MEASURED_PEAKS.json absent)"
 
 
+def tensor_peak():
+    """Measured dense bf16 tensor throughput (TFLOP/s, burst) the tensor-path figure is compared with."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops)"
+        except Exception:
+            pass
+    return 1590.0, "fallback 1590 TFLOP/s (MEASURED_PEAKS.json absent)"
+
+
 def measured_traffic(kernel, workload_key):
     """DRAM bytes per launch from the committed ncu capture, if one covers this kernel and workload."""
     p = ROOT / "profiles" / "dram_traffic.json"
@@ -135,33 +146,82 @@ def pinned_copy(lib, arr):
 
 
 def cpu_reference(M, N, K, row_ptr, col_idx, s_val, A, B, max_nnz, reps):
-    """Time the reference's CPU SDDMM on a row-prefix sample of the workload (1 thread: it has no threading)."""
-    import oracle_lib
+    """Time the reference's CPU SDDMM on a row-prefix sample of the workload: on all host threads (row ranges running
+    concurrently, see CpuRowShards) and, for the record, on one thread (what the reference itself does)."""
     r_end = int(np.searchsorted(row_ptr, max_nnz, side="right") - 1) if row_ptr[M] > max_nnz else M
     r_end = max(1, min(M, r_end))
-    nnz_s = int(row_ptr[r_end])
-    rp = np.ascontiguousarray(row_ptr[:r_end + 1])
-    ref = oracle_lib.Reference.try_load()
-    times = []
-    if ref is not None:
-        kind = "reference"
-        run, result, destroy = ref.problem(r_end, N, K, rp, col_idx[:nnz_s], s_val[:nnz_s], A[:r_end], B)
-        for _ in range(reps):
-            times.append(run() * 1e-9)
-        destroy()
-    else:
-        kind = "port"
-        orc = oracle_lib.Oracle()
-        Ac, Bc = np.ascontiguousarray(A[:r_end]), np.ascontiguousarray(B)
-        out = np.empty(nnz_s, np.float32)
-        for _ in range(reps):
-            t0 = time.perf_counter()
-            orc.sddmm_csr_rows(0, r_end, K, rp, np.ascontiguousarray(col_idx[:nnz_s]), np.ascontiguousarray(s_val[:nnz_s]), Ac, Bc, out)
-            times.append(time.perf_counter() - t0)
-    t = float(np.median(times))
-    return {"value": 2.0 * nnz_s * K / t / 1e9, "unit": "GFLOP/s", "cores": 1, "kind": kind,
-            "sample": f"rows [0,{r_end}) of the workload = {nnz_s} nnz, median of {reps} runs of CPUBasic::run_csr, {t * 1e3:.1f} ms each",
+    out = {}
+    for label, threads in (("all", host_threads()), ("one", 1)):
+        shards = CpuRowShards(M, N, K, row_ptr, col_idx, s_val, A, B, r_end, threads)
+        shards.step()   # warm-up
+        t = float(np.median([shards.step() for _ in range(reps)]))
+        out[label] = (shards.threads, shards.kind, shards.nnz, t)
+        shards.close()
+    threads, kind, nnz_s, t = out["all"]
+    _, _, _, t1 = out["one"]
+    return {"value": 2.0 * nnz_s * K / t / 1e9, "unit": "GFLOP/s", "cores": threads, "kind": kind,
+            "sample": f"rows [0,{r_end}) of the workload = {nnz_s} nnz cut into {threads} nnz-balanced row ranges, each running "
+                      f"CPUBasic::run_csr on its own host thread; median of {reps} runs, {t * 1e3:.1f} ms each",
+            "single_thread": {"value": 2.0 * nnz_s * K / t1 / 1e9, "unit": "GFLOP/s", "ms": t1 * 1e3,
+                              "what": "the same sample in one call of CPUBasic::run_csr (the reference has no threading)"},
             "host_cores_available": os.cpu_count()}, t, nnz_s
+
+
+def host_threads():
+    """Host threads the CPU legs may use (the cores this process is allowed to run on, at most 64)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, min(64, n))
+
+
+class CpuRowShards:
+    """The reference's CPU SDDMM on all host threads: the rows [0, r_end) are cut into nnz-balanced contiguous ranges
+    (the way the GPU arm shards rows), every range is its own problem object of the UNMODIFIED reference code
+    (CPUBasic::run_csr), and the ranges run concurrently, one host thread each (ctypes drops the GIL during the call).
+    A step takes as long as its slowest range.  Falls back to the C restatement when the reference library is absent."""
+
+    def __init__(self, M, N, K, row_ptr, col_idx, s_val, A, B, r_end, threads):
+        import oracle_lib
+        from dphpc_b200.partition import row_cuts
+        self.ref = oracle_lib.Reference.try_load()
+        self.kind = "reference" if self.ref is not None else "port"
+        self.nnz = int(row_ptr[r_end])
+        rp = np.ascontiguousarray(row_ptr[:r_end + 1])
+        threads = max(1, min(threads, r_end))
+        cuts = row_cuts(rp, threads) if threads > 1 else [0, r_end]
+        self.parts = []
+        orc = None if self.ref is not None else oracle_lib.Oracle()
+        for a, b in zip(cuts[:-1], cuts[1:]):
+            if b <= a:
+                continue
+            lo, hi = int(rp[a]), int(rp[b])
+            sub_rp = np.ascontiguousarray(rp[a:b + 1] - lo)
+            ci, sv = np.ascontiguousarray(col_idx[lo:hi]), np.ascontiguousarray(s_val[lo:hi])
+            Aa = np.ascontiguousarray(A[a:b])
+            if self.ref is not None:
+                run, _, destroy = self.ref.problem(b - a, N, K, sub_rp, ci, sv, Aa, B)
+                self.parts.append((run, destroy))
+            else:
+                out = np.empty(hi - lo, np.float32)
+                Bc = np.ascontiguousarray(B)
+                self.parts.append(((lambda sub_rp=sub_rp, ci=ci, sv=sv, Aa=Aa, out=out, n=b - a:
+                                    orc.sddmm_csr_rows(0, n, K, sub_rp, ci, sv, Aa, Bc, out)), (lambda: None)))
+        self.threads = len(self.parts)
+        from concurrent.futures import ThreadPoolExecutor
+        self.pool = ThreadPoolExecutor(max_workers=self.threads)
+
+    def step(self):
+        """One pass over the sample on all threads; wall seconds."""
+        t0 = time.perf_counter()
+        list(self.pool.map(lambda p: p[0](), self.parts))
+        return time.perf_counter() - t0
+
+    def close(self):
+        self.pool.shutdown()
+        for _, destroy in self.parts:
+            destroy()
 
 
 def workload_config(cfg, K, mode, world):
@@ -178,26 +238,13 @@ def run_reference_arm(args, rank, world):
     total = args.steps + args.warmup
     # bound each step so the whole run stays within a few minutes (CPUBasic does ~1-2 GFLOP/s)
     budget_nnz = int(max(2e5, min(d.nnz, 150.0 / max(total, 1) * 1.0e9 / (2 * K))))
-    import oracle_lib
-    ref = oracle_lib.Reference.try_load()
+    threads = host_threads()
+    budget_nnz = min(d.nnz, budget_nnz * threads)   # the sample grows with the threads that share it
     r_end = int(np.searchsorted(d.row_ptr, budget_nnz, side="right") - 1) if d.nnz > budget_nnz else d.M
     r_end = max(1, min(d.M, r_end))
-    nnz_s = int(d.row_ptr[r_end])
-    rp = np.ascontiguousarray(d.row_ptr[:r_end + 1])
-    if ref is not None:
-        run, _, destroy = ref.problem(r_end, d.N, K, rp, d.col_idx[:nnz_s], d.s_val[:nnz_s], d.A[:r_end], d.B)
-        step = lambda: run() * 1e-9  # noqa: E731
-    else:
-        orc = oracle_lib.Oracle()
-        Ac, Bc = np.ascontiguousarray(d.A[:r_end]), np.ascontiguousarray(d.B)
-        ci, sv = np.ascontiguousarray(d.col_idx[:nnz_s]), np.ascontiguousarray(d.s_val[:nnz_s])
-        out = np.empty(nnz_s, np.float32)
-
-        def step():
-            t0 = time.perf_counter()
-            orc.sddmm_csr_rows(0, r_end, K, rp, ci, sv, Ac, Bc, out)
-            return time.perf_counter() - t0
-        destroy = lambda: None  # noqa: E731
+    shards = CpuRowShards(d.M, d.N, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, r_end, threads)
+    nnz_s = shards.nnz
+    step, destroy = shards.step, shards.close
     for _ in range(args.warmup):
         step()
     ts = [step() for _ in range(args.steps)]
@@ -209,8 +256,9 @@ def run_reference_arm(args, rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": tm * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(cfg, K, args.mode, max(1, args.gpus)),   # the same workload description as the GPU arm prints
-        "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": 1, "kind": "reference" if ref is not None else "port",
-                         "sample": f"each step = CPUBasic::run_csr over rows [0,{r_end}) = {nnz_s} of {d.nnz} nnz",
+        "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": shards.threads, "kind": shards.kind,
+                         "sample": f"each step = CPUBasic::run_csr over rows [0,{r_end}) = {nnz_s} of {d.nnz} nnz, cut into "
+                                   f"{shards.threads} nnz-balanced row ranges that run concurrently (one host thread each)",
                          "host_cores_available": os.cpu_count()},
         "e2e": {"value": val, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -396,6 +444,16 @@ def main():
                     "traffic": measured_traffic(dom, f"config{cfg}_k{K}_{args.mode}"), "algorithmic_bytes_per_launch": int(alg),
                     "launch_ms": dom_ms, "peak_source": peak_src,
                     "kernels_ms": {k: float(np.mean(v)) for k, v in kern.items()}}
+        # what the same nonzeros would move if no gathered B row were ever reused (every nonzero fetches its own B row)
+        eb = 2 if args.mode == "bf16" else 4
+        roofline["gather_model_bytes"] = int(eb * K * (plan["rows_nonempty"] + plan["nnz"]) + 12 * plan["nnz"] + 4 * (plan["rows"] + 1))
+        if "dense" in dom:
+            # the dense contraction the tensor cores execute: 64x64xK' per tile (K' = 3K for the 3-term tf32 split)
+            kp = 3 * K if args.mode == "fp32_tc" else K
+            tpeak, tsrc = tensor_peak()
+            tfl = 2.0 * 64 * 64 * kp * plan["dense_tiles"] / (dom_ms * 1e-3) / 1e12
+            roofline["tensor"] = {"dense_tile_tflops": tfl, "peak_tflops": tpeak, "frac": tfl / tpeak, "peak_source": tsrc,
+                                  "note": "tensor throughput is not what bounds this path (8 B per nonzero of HBM traffic is)"}
 
     line = None
     if rank == 0:
