@@ -2,8 +2,17 @@
 // Dataset<T> keeps the public getters of the reference's SDDMM::Dataset<T>
 // (src/benchmark/dataset.hpp:79-119).  SyntheticDataset wraps the seeded generators of
 // include/sddmm_datasets.h (the reference's RandomWithDensityDataset, :331-356, is unseeded);
-// DummyDataset is the reference's built-in known-answer case (:183-204).
+// DummyDataset is the reference's built-in known-answer case (:183-204).  MatrixMarketDataset and
+// EdgeListDataset read the two file formats the reference loads (:122-181 and :270-313) with its
+// semantics: 1-based MatrixMarket coordinates, no mirroring of symmetric files, entries with
+// |value| < 1e-7 dropped; SNAP edge lists take the ids as they are and the value 1.  Unlike the
+// reference they fill A and B from a seed, accept pattern files, and report bad input by exception
+// instead of assert.
 #pragma once
+#include <cmath>
+#include <cstdint>
+#include <fstream>
+#include <sstream>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -85,6 +94,91 @@ private:
                                       std::vector<float>(v, v + nnz)));
         sddmm_dataset_destroy(ds);
         return out;
+    }
+};
+
+// A and B for inputs that come without dense operands: uniform [-1, 1), reproducible from the seed
+inline Dense<float> seeded_dense(unsigned rows, unsigned cols, uint64_t seed) {
+    std::vector<float> v(static_cast<size_t>(rows) * cols);
+    uint64_t x = seed;
+    for (float &f : v) {
+        x += 0x9E3779B97F4A7C15ull;   // splitmix64 step
+        uint64_t z = x;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        f = static_cast<float>(static_cast<double>(z >> 40) * (2.0 / 16777216.0) - 1.0);
+    }
+    return Dense<float>(rows, cols, std::move(v));
+}
+
+// MatrixMarket coordinate file (https://math.nist.gov/MatrixMarket/formats.html), real, integer or pattern.
+class MatrixMarketDataset : public Dataset<float> {
+public:
+    MatrixMarketDataset(const std::string &name, const std::string &path, int K, uint64_t seed = 0x5DD0)
+        : Dataset<float>(load(name, path, K, seed)) {}
+
+private:
+    static Dataset<float> load(const std::string &name, const std::string &path, int K, uint64_t seed) {
+        std::ifstream in(path);
+        if (!in) throw std::runtime_error("cannot open " + path);
+        std::string line;
+        bool pattern = false;
+        long long M = -1, N = -1, declared = -1;
+        while (std::getline(in, line)) {
+            if (line.empty()) continue;
+            if (line[0] == '%') {
+                if (line.rfind("%%MatrixMarket", 0) == 0 && line.find("pattern") != std::string::npos) pattern = true;
+                continue;
+            }
+            std::istringstream size_line(line);
+            if (!(size_line >> M >> N >> declared) || M < 1 || N < 1 || declared < 0) throw std::runtime_error("bad size line in " + path);
+            break;
+        }
+        if (M < 0) throw std::runtime_error("no size line in " + path);
+        std::vector<Triplet<float>> triplets;
+        triplets.reserve(static_cast<size_t>(declared));
+        long long seen = 0;
+        while (std::getline(in, line)) {
+            if (line.empty() || line[0] == '%') continue;
+            std::istringstream entry(line);
+            long long r, c;
+            double v = 1.0;
+            if (!(entry >> r >> c) || (!pattern && !(entry >> v))) throw std::runtime_error("bad entry in " + path + ": " + line);
+            if (r < 1 || r > M || c < 1 || c > N) throw std::runtime_error("coordinate out of range in " + path + ": " + line);
+            ++seen;
+            if (std::fabs(v) < 1e-7) continue;   // the reference drops (numerically) zero entries
+            triplets.push_back({static_cast<int>(r - 1), static_cast<int>(c - 1), static_cast<float>(v)});
+        }
+        if (seen != declared) throw std::runtime_error(path + ": " + std::to_string(seen) + " entries, size line says " + std::to_string(declared));
+        return Dataset<float>(name, seeded_dense(static_cast<unsigned>(M), static_cast<unsigned>(K), seed),
+                              seeded_dense(static_cast<unsigned>(N), static_cast<unsigned>(K), seed + 1),
+                              CSR<float>(static_cast<int>(M), static_cast<int>(N), triplets));
+    }
+};
+
+// SNAP-style edge list: '#' comment lines, then "row<TAB or space>col" pairs used as they are (0-based), value 1.
+class EdgeListDataset : public Dataset<float> {
+public:
+    EdgeListDataset(const std::string &name, const std::string &path, int M, int N, int K, uint64_t seed = 0x5DD0)
+        : Dataset<float>(load(name, path, M, N, K, seed)) {}
+
+private:
+    static Dataset<float> load(const std::string &name, const std::string &path, int M, int N, int K, uint64_t seed) {
+        std::ifstream in(path);
+        if (!in) throw std::runtime_error("cannot open " + path);
+        std::vector<Triplet<float>> triplets;
+        std::string line;
+        while (std::getline(in, line)) {
+            if (line.empty() || line[0] == '#') continue;
+            std::istringstream entry(line);
+            long long r, c;
+            if (!(entry >> r >> c)) throw std::runtime_error("bad edge in " + path + ": " + line);
+            if (r < 0 || r >= M || c < 0 || c >= N) throw std::runtime_error("edge out of range in " + path + ": " + line);
+            triplets.push_back({static_cast<int>(r), static_cast<int>(c), 1.0f});
+        }
+        return Dataset<float>(name, seeded_dense(static_cast<unsigned>(M), static_cast<unsigned>(K), seed),
+                              seeded_dense(static_cast<unsigned>(N), static_cast<unsigned>(K), seed + 1), CSR<float>(M, N, triplets));
     }
 };
 

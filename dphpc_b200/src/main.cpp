@@ -1,6 +1,7 @@
-// sddmm_bench: benchmark driver for the GPU-B200 competitor on the seeded synthetic configurations.
+// sddmm_bench: benchmark driver for the GPU-B200 competitor on the seeded synthetic configurations or on a matrix file.
 // Command line of the reference's driver (src/main.cpp:285-349: --K/-k, --no_csv_header, --num_runs;
-// --data_folder is accepted and ignored: no matrix files are read) plus --config, --scale, --mode.
+// --data_folder is accepted and ignored) plus --config, --scale, --mode, and --mtx FILE (MatrixMarket coordinate file) or
+// --edges FILE --rows M --cols N (SNAP edge list), read with the reference's rules (src/benchmark/dataset.hpp:122-181, 270-313).
 // The first competitor is the correctness baseline of the harness; here that is GPU-B200 in fp32
 // mode (the independent CPU check lives in the test-suite, not in this binary).
 #include <cstdlib>
@@ -15,7 +16,8 @@
 namespace {
 
 struct Options {
-    int K = 0, num_runs = 3, config = 0, variant = 0;
+    int K = 0, num_runs = 3, config = 0, variant = 0, rows = 0, cols = 0;
+    std::string mtx, edges;
     double scale = 1.0;
     bool header = true;
     std::vector<std::string> modes{"fp32", "fp32_tc"};   // tf32 / bf16 on request: their 1e-2 error fails the 1e-3 check
@@ -30,7 +32,8 @@ int mode_id(const std::string &m) {
 }
 
 void usage() {
-    std::cerr << "usage: sddmm_bench [--config 1..5 (default: all)] [-k K] [--num_runs R] [--scale s] [--mode fp32,tf32,...] [--no_csv_header]\n";
+    std::cerr << "usage: sddmm_bench [--config 1..5 (default: all) | --mtx FILE | --edges FILE --rows M --cols N] [-k K] [--num_runs R] [--scale s]"
+                 " [--mode fp32,tf32,...] [--no_csv_header]\n";
 }
 
 }  // namespace
@@ -44,6 +47,10 @@ int main(int argc, char **argv) {
         else if (a == "--num_runs") o.num_runs = std::atoi(next());
         else if (a == "--config") o.config = std::atoi(next());
         else if (a == "--variant") o.variant = std::atoi(next());
+        else if (a == "--mtx") o.mtx = next();
+        else if (a == "--edges") o.edges = next();
+        else if (a == "--rows") o.rows = std::atoi(next());
+        else if (a == "--cols") o.cols = std::atoi(next());
         else if (a == "--scale") o.scale = std::atof(next());
         else if (a == "--no_csv_header") o.header = false;
         else if (a == "-d" || a == "--data_folder") next();
@@ -70,6 +77,23 @@ int main(int argc, char **argv) {
     if (o.header) FILE_DUMP(SDDMM::Benchmark<float>::csv_header() << std::endl);
     const int default_k[6] = {0, 32, 32, 64, 32, 32};
     int bad = 0;
+    if (!o.mtx.empty() || !o.edges.empty()) {   // one matrix file instead of the synthetic configurations
+        try {
+            const int K = o.K ? o.K : 32;
+            if (!o.mtx.empty()) {
+                SDDMM::MatrixMarketDataset d(o.mtx, o.mtx, K);
+                bad = SDDMM::Benchmark<float>(d, competitors, o.num_runs).benchmark();
+            } else {
+                if (o.rows < 1 || o.cols < 1) { usage(); return 2; }
+                SDDMM::EdgeListDataset d(o.edges, o.edges, o.rows, o.cols, K);
+                bad = SDDMM::Benchmark<float>(d, competitors, o.num_runs).benchmark();
+            }
+        } catch (const std::exception &e) {
+            std::cerr << "sddmm_bench: " << e.what() << std::endl;
+            return 2;
+        }
+        return bad ? 3 : 0;
+    }
     for (int cfg = 1; cfg <= 5; ++cfg) {
         if (o.config && cfg != o.config) continue;
         SDDMM::SyntheticDataset d(cfg, o.K ? o.K : default_k[cfg], o.scale, 0, o.variant);

@@ -1,6 +1,9 @@
 // Host containers and dispatcher: the cases of the reference's tests/matrix_test.cc that need no GPU
 // (BasicTest.COO :84-91, RepresentationConversion :93-106, BiggerConversion :108-122, dispatcher_* :354-425,
 // test_dispatch_tensor :460-477, DummyDataset known answer), run against this repository's interface mirror.
+#include <algorithm>
+#include <cstdlib>
+#include <fstream>
 #include <numeric>
 
 #include "benchmark/dataset.hpp"
@@ -82,6 +85,68 @@ TEST_CASE(density_does_not_overflow) {
     CHECK(big.getDensity() == 0.0);
     SDDMM::SyntheticDataset d(1, 4);
     CHECK(d.getS_CSR().getDensity() > 0.04 && d.getS_CSR().getDensity() < 0.05);
+}
+
+namespace {
+std::string write_temp(const char *name, const char *text) {
+    const char *dir = std::getenv("TMPDIR");
+    const std::string path = std::string(dir ? dir : "/tmp") + "/sddmm_b200_" + name;
+    std::ofstream(path) << text;
+    return path;
+}
+template <typename F>
+bool throws(F f) {
+    try { f(); } catch (const std::runtime_error &) { return true; }
+    return false;
+}
+}  // namespace
+
+TEST_CASE(matrix_market_reader_follows_the_reference_rules) {
+    // comments, 1-based coordinates, a numerically zero entry (dropped), unsorted input, a duplicate coordinate,
+    // a symmetric header that is NOT mirrored (src/benchmark/dataset.hpp:150-180 of the reference)
+    const std::string path = write_temp("a.mtx",
+        "%%MatrixMarket matrix coordinate real symmetric\n% a comment\n4 5 6\n3 2 1.5\n1 1 2.0\n4 5 -3.0\n2 3 1e-9\n1 4 0.5\n3 2 7.0\n");
+    SDDMM::MatrixMarketDataset d("tiny", path, 8);
+    CSR<float> &S = d.getS_CSR();
+    CHECK_EQ(S.getRows(), 4);
+    CHECK_EQ(S.getCols(), 5);
+    CHECK(S.getRowPositions() == std::vector<int>({0, 2, 2, 3, 4}));      // row 2 lost its only (zero) entry
+    CHECK(S.getColPositions() == std::vector<int>({0, 3, 1, 4}));
+    CHECK_EQ(S.getValues()[0], 2.0f);
+    CHECK_EQ(S.getValues()[3], -3.0f);
+    CHECK_EQ(static_cast<int>(d.getA().getRows()), 4);
+    CHECK_EQ(static_cast<int>(d.getB().getRows()), 5);
+    CHECK_EQ(static_cast<int>(d.getA().getCols()), 8);
+    CHECK(d.getS_COO() == COO<float>(S));
+    // the dense operands depend on the seed only
+    SDDMM::MatrixMarketDataset again("tiny", path, 8);
+    const size_t na = static_cast<size_t>(d.getA().getRows()) * d.getA().getCols();
+    CHECK(std::equal(d.getA().get_pointer(), d.getA().get_pointer() + na, again.getA().get_pointer()));
+    float lo = 1.f, hi = -1.f;
+    const size_t nb = static_cast<size_t>(d.getB().getRows()) * d.getB().getCols();
+    for (size_t i = 0; i < nb; ++i) { lo = std::min(lo, d.getB().get_pointer()[i]); hi = std::max(hi, d.getB().get_pointer()[i]); }
+    CHECK(lo >= -1.f && hi < 1.f && lo < 0.f && hi > 0.f);
+}
+
+TEST_CASE(matrix_market_pattern_files_and_bad_input) {
+    const std::string pat = write_temp("p.mtx", "%%MatrixMarket matrix coordinate pattern general\n3 3 2\n1 3\n3 1\n");
+    SDDMM::MatrixMarketDataset d("pattern", pat, 4);
+    CHECK(d.getS_CSR().getColPositions() == std::vector<int>({2, 0}));
+    CHECK(d.getS_CSR().getValues() == std::vector<float>({1.0f, 1.0f}));
+    CHECK(throws([] { SDDMM::MatrixMarketDataset x("missing", "/nonexistent/file.mtx", 4); }));
+    const std::string short_file = write_temp("s.mtx", "3 3 4\n1 1 1.0\n");
+    CHECK(throws([&] { SDDMM::MatrixMarketDataset x("short", short_file, 4); }));
+    const std::string range = write_temp("r.mtx", "3 3 1\n4 1 1.0\n");
+    CHECK(throws([&] { SDDMM::MatrixMarketDataset x("range", range, 4); }));
+}
+
+TEST_CASE(edge_list_reader) {
+    const std::string path = write_temp("e.txt", "# Directed graph\n# Nodes: 4 Edges: 4\n# FromNodeId\tToNodeId\n0\t1\n2\t3\n2\t0\n0\t1\n");
+    SDDMM::EdgeListDataset d("edges", path, 4, 4, 4);
+    CHECK(d.getS_CSR().getRowPositions() == std::vector<int>({0, 1, 1, 3, 3}));
+    CHECK(d.getS_CSR().getColPositions() == std::vector<int>({1, 0, 3}));
+    CHECK(d.getS_CSR().getValues() == std::vector<float>({1.0f, 1.0f, 1.0f}));
+    CHECK(throws([&] { SDDMM::EdgeListDataset x("small", path, 2, 2, 4); }));
 }
 
 int main(int argc, char **argv) { return tiny_test::run_all(argc > 1 ? argv[1] : nullptr); }

@@ -64,3 +64,33 @@ def test_competitor_behind_the_reference_interface():
     lines = [ln for ln in res.stdout.splitlines() if not ln.startswith(("GPU-B200", "CPU-Basic"))]   # drop the CSV rows
     assert res.returncode == 0, "\n".join(lines[-60:]) + res.stderr[-2000:]
     assert "0 failures" in res.stdout
+
+
+@pytest.mark.gpu
+def test_benchmark_driver_reads_matrix_files(tmp_path):
+    # sddmm_bench on a MatrixMarket file and on an edge list: CSV rows with correctness = 1 for both competitors
+    import numpy as np
+    from dphpc_b200 import build
+
+    exe = build.build_bench()
+    rng = np.random.default_rng(5)
+    M, N, nnz = 300, 200, 4000
+    flat = rng.choice(M * N, size=nnz, replace=False)
+    mtx = tmp_path / "m.mtx"
+    with open(mtx, "w") as f:
+        f.write("%%MatrixMarket matrix coordinate real general\n% generated\n")
+        f.write(f"{M} {N} {nnz}\n")
+        for p in flat:
+            f.write(f"{p // N + 1} {p % N + 1} {rng.uniform(0.1, 1.0):.6f}\n")
+    edges = tmp_path / "e.txt"
+    with open(edges, "w") as f:
+        f.write("# edge list\n")
+        for p in flat[:1500]:
+            f.write(f"{p // N}\t{p % N}\n")
+    for args in (["--mtx", str(mtx)], ["--edges", str(edges), "--rows", str(M), "--cols", str(N)]):
+        res = subprocess.run([str(exe), *args, "-k", "32", "--num_runs", "2"], capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+        rows = [ln.split(",") for ln in res.stdout.splitlines() if ln.startswith("GPU-B200")]
+        header = next(ln.split(",") for ln in res.stdout.splitlines() if ln.startswith("competitor"))
+        ci = header.index("correctness")
+        assert len(rows) >= 2 and all(r[ci].strip() == "1" for r in rows), res.stdout[-2000:]
