@@ -192,10 +192,12 @@ class CpuRowShards:
         threads = max(1, min(threads, r_end))
         cuts = row_cuts(rp, threads) if threads > 1 else [0, r_end]
         self.parts = []
+        self.ranges = []   # row range of every part
         orc = None if self.ref is not None else oracle_lib.Oracle()
         for a, b in zip(cuts[:-1], cuts[1:]):
             if b <= a:
                 continue
+            self.ranges.append((int(a), int(b)))
             lo, hi = int(rp[a]), int(rp[b])
             sub_rp = np.ascontiguousarray(rp[a:b + 1] - lo)
             ci, sv = np.ascontiguousarray(col_idx[lo:hi]), np.ascontiguousarray(s_val[lo:hi])
