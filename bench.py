@@ -393,6 +393,16 @@ def main():
     else:
         t_total = t_local
     ms_per_step = t_total / args.steps
+    # per-rank shard size and time (how well the nnz-balanced row cuts balance the device time)
+    per_rank = None
+    if dist is not None:
+        mine = torch.tensor([float(nnz_loc), t_local / args.steps], dtype=torch.float64, device="cuda")
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)   # (every rank takes part; only rank 0 prints)
+        nnzs = [int(t[0].item()) for t in allr]
+        mss = [float(t[1].item()) for t in allr]
+        per_rank = {"nnz": nnzs, "ms_per_step": mss, "nnz_imbalance_max_over_mean": max(nnzs) / max(1e-30, sum(nnzs) / world),
+                    "time_imbalance_max_over_mean": max(mss) / max(1e-30, sum(mss) / world)}
     flops = 2.0 * d.nnz * K
     value = flops / (ms_per_step * 1e-3) / 1e9
 
@@ -465,7 +475,7 @@ def main():
             "dtype": {"fp32": "f32", "fp32_tc": "f32 (tf32x3 on dense tiles)", "tf32": "tf32", "bf16": "bf16"}[args.mode],
             "data": "synthetic", "config": workload_config(cfg, K, args.mode, world),
             "e2e": e2e, "gpu_launches": int(args.steps * plan["n_kernels"]), "roofline": roofline, "clocks": clocks,
-            "wall_s_timed_region": wall,
+            "wall_s_timed_region": wall, "per_rank": per_rank,
             "plan": {k: plan[k] for k in ("nnz", "rows_nonempty", "cols_touched", "max_row_nnz", "rowtile_nnz", "rowtile_items",
                                           "rowtile_rows_per_stage", "rowtile_grid", "rowtile_smem_bytes", "dense_nnz", "dense_tiles",
                                           "rowgroup_nnz", "rowgroup_rows", "n_kernels")},

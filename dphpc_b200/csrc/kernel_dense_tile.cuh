@@ -258,8 +258,8 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
         // ===================== epilogue warps =====================
         // Tile row r belongs to warp r % 8 for the whole kernel (16 rows per warp, two halves of 8).
         // S.val: the nonzeros of a tile row are one contiguous CSR run; widened to 16-byte granules it
-        // is at most 18 of them, copied by lanes 0..17 with ONE asynchronous 16-byte copy each into
-        // the row's slot of sSval.  A half is requested for the next job as soon as the warp has
+        // is at most 18 of them, copied with asynchronous 16-byte copies (one per lane, two rows per
+        // instruction) into the row's slot of sSval.  A half is requested for the next job as soon as the warp has
         // sampled it for this job, so the copies run most of a job ahead and no warp waits for
         // global memory.  Row records (first position, granules, presence mask) run two jobs ahead.
         // Sampling: lane l owns tile columns l and l+32; the mask says which are nonzeros and the
@@ -299,13 +299,21 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                 dst->y = cnt ? ((d.x & 3u) + cnt + 3u) >> 2 : 0u;
             }
         };
+        // two rows per instruction: lanes 0..15 copy granules 0..15 of one row, lanes 16..31 those of the next;
+        // a run of 64 that does not start on a granule boundary needs granules 16 (and 17): a second, rarely taken, step
         auto request_half = [&](int buf, int half) {
+            const int side = lane >> 4, g = lane & 15;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int r = (8 * half + u) * kDenseEpiWarps + warp;
+            for (int u = 0; u < 8; u += 2) {
+                const int r = (8 * half + u + side) * kDenseEpiWarps + warp;
                 const uint4 d = sRows[buf * 128 + r];
-                if (lane < static_cast<int>(d.y))
-                    cp_async_16(sSval + r * kDenseSvalStride + 4 * lane, args.s_val + (d.x & ~3u) + 4 * lane);
+                const int n = static_cast<int>(d.y);
+                float *dst = sSval + r * kDenseSvalStride;
+                const float *src = args.s_val + (d.x & ~3u);
+                if (g < n) cp_async_16(dst + 4 * g, src + 4 * g);
+                if (__any_sync(kFullMask, n > 16)) {
+                    if (g + 16 < n) cp_async_16(dst + 4 * (g + 16), src + 4 * (g + 16));
+                }
             }
         };
         auto sample_half = [&](int buf, int half) {
