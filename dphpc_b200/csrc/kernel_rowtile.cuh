@@ -299,23 +299,6 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
                                                 : zero_chunk(chunk_t());
                             }
                         }
-#ifdef SDDMM_ROWTILE_COND_RELOAD
-                        int cur = -1;
-                        float4 a[QS];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            if (ro[i] != cur) {   // group-uniform: reload the A chunks only when the row changes
-                                cur = ro[i];
-#pragma unroll
-                                for (int qq = 0; qq < QS; ++qq) {
-                                    const int ch = gl + 8 * (q0 + qq);
-                                    a[qq] = (EXACT || ch < nchunks) ? chunk_to_f4(sAc[cur + ch]) : make_float4(0.f, 0.f, 0.f, 0.f);
-                                }
-                            }
-#pragma unroll
-                            for (int qq = 0; qq < QS; ++qq) acc[i] = dot4(a[qq], chunk_to_f4(bq[i][qq]), acc[i]);
-                        }
-#else
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
 #pragma unroll
@@ -325,7 +308,6 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
                                 acc[i] = dot4(a, chunk_to_f4(bq[i][qq]), acc[i]);
                             }
                         }
-#endif
                     }
                 }
                 const float dot = group8_transpose_reduce(acc, gl);
