@@ -16,7 +16,7 @@
 //                     k-steps and tcgen05.commit
 //   8 epilogue warps  tcgen05.ld the accumulator (thread = row), park it in
 //                     shared memory, then one warp per tile row streams that
-//                     row: lane l owns columns l and l+32, a 64-bit presence
+//                     row: lane l owns columns 2l and 2l+1, a 64-bit presence
 //                     mask says which of them are nonzeros of S, the rank of
 //                     the column inside the mask is the offset from the row's
 //                     first nonzero in the tile.  S.val is read and P.val is
@@ -49,7 +49,7 @@ namespace sddmm {
 constexpr int kDenseTile = 64;               // tile edge
 constexpr int kDenseEpiWarps = 8;
 constexpr int kDenseThreads = (kDenseEpiWarps + 1) * 32;   // + producer/MMA warp
-constexpr int kDenseAccStride = 65;          // floats per accumulator row in smem (odd: conflict-free column writes)
+constexpr int kDenseAccStride = 66;          // floats per accumulator row in smem (even: rows are read and written as 8-byte column pairs)
 constexpr int kDenseSvalStride = 72;         // floats per staged S.val row: 64 + up to 3 before + up to 3 after (16-byte granules), 288 bytes
 constexpr uint32_t kOperandBytes = 128 * 128;  // 128 rows x one 128-byte k-block
 constexpr uint32_t kHalfOperandBytes = 64 * 128;
@@ -262,9 +262,10 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
         // instruction) into the row's slot of sSval.  A half is requested for the next job as soon as the warp has
         // sampled it for this job, so the copies run most of a job ahead and no warp waits for
         // global memory.  Row records (first position, granules, presence mask) run two jobs ahead.
-        // Sampling: lane l owns tile columns l and l+32; the mask says which are nonzeros and the
-        // popcount below the lane is the offset inside the run -> S.val from shared memory, P.val
-        // written in contiguous CSR runs; col_idx is never read.
+        // Sampling: lane l owns the adjacent tile columns 2l and 2l+1 (one 8-byte read of the parked
+        // accumulator); the mask says which are nonzeros and the popcount below column 2l is the offset
+        // inside the run -> S.val from shared memory, P.val written in contiguous CSR runs; col_idx is
+        // never read.
         //
         // cp.async groups of a thread, oldest first, at the points that wait (always "all but 2"):
         //   before the mid barrier of job n:  [R(n+1)] [A(n)] [B(n)]      -> records of job n+1 landed
@@ -273,7 +274,9 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
         const int q = warp & 3;               // TMEM lane quarter this warp may read: rows 32q .. 32q+31
         const int h = warp >> 2;              // which 32 of the tile's 64 columns this warp moves
         const int tile_of_q = q >> 1;         // rows 0-63: first tile, rows 64-127: second tile
-        const uint32_t below = (1u << lane) - 1u;
+        const bool upper = lane >= 16;                        // columns 2l, 2l+1 sit in the upper mask word
+        const uint32_t pshift = (2u * lane) & 31u;            // bit of column 2l inside its mask word
+        const uint32_t pbelow = (1u << pshift) - 1u;
         const int stride_jobs = static_cast<int>(gridDim.x);
 
         // raw descriptors of one job -> record buffer `buf` (threads 0..127: one tile row each) ...
@@ -321,13 +324,17 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
             for (int u = 0; u < 8; ++u) {
                 const int r = (8 * half + u) * kDenseEpiWarps + warp;
                 const uint4 d = sRows[buf * 128 + r];
-                const uint32_t mlo = d.z, mhi = d.w;
+                // lane l owns the adjacent columns 2l and 2l+1: one 8-byte read of the accumulator pair; the second
+                // column's nonzero (if any) directly follows the first one's in the run
                 const int st = static_cast<int>(d.x);
-                const int k0 = __popc(mlo & below), k1 = __popc(mlo) + __popc(mhi & below);   // offsets inside the run
-                const float *arow = sAcc + r * kDenseAccStride;
-                const float *srow = sSval + r * kDenseSvalStride + (st & 3);
-                if ((mlo >> lane) & 1u) __stcs(args.p_val + st + k0, arow[lane] * srow[k0]);
-                if ((mhi >> lane) & 1u) __stcs(args.p_val + st + k1, arow[lane + 32] * srow[k1]);
+                const uint32_t w = upper ? d.w : d.z;                       // the mask word that holds this lane's two bits
+                const uint32_t pair = (w >> pshift) & 3u;
+                const int k0 = (upper ? __popc(d.z) : 0) + __popc(w & pbelow);   // offset of column 2l inside the run
+                const float2 a = *reinterpret_cast<const float2 *>(sAcc + r * kDenseAccStride + 2 * lane);
+                const float *srow = sSval + r * kDenseSvalStride + (st & 3) + k0;
+                float *prow = args.p_val + st + k0;
+                if (pair & 1u) __stcs(prow, a.x * srow[0]);
+                if (pair & 2u) __stcs(prow + (pair & 1u), a.y * srow[pair & 1u]);
             }
         };
 
@@ -366,7 +373,8 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                 tcgen05_fence_before();
                 float *row = sAcc + (32 * q + lane) * kDenseAccStride + 32 * h;
 #pragma unroll
-                for (int c = 0; c < 32; ++c) row[c] = __uint_as_float(v[c]);
+                for (int c = 0; c < 32; c += 2)
+                    *reinterpret_cast<float2 *>(row + c) = make_float2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
             }
             cp_async_wait_group<2>();               // this thread's share of the next job's records
             finish_rows(job + stride_jobs, buf1);
