@@ -234,6 +234,13 @@ class Engine:
     def update_values(self, s_val):
         self._check(self.lib.sddmm_b200_update_values(self.h, _ptr(_as(s_val, np.float32))), "update_values")
 
+    def update_raw(self, A=None, B=None, s_val=None):
+        """update_dense / update_values with host pointers given as integers (e.g. pinned buffers)."""
+        if A is not None or B is not None:
+            self._check(self.lib.sddmm_b200_update_dense(self.h, _ptr(A), _ptr(B)), "update_dense")
+        if s_val is not None:
+            self._check(self.lib.sddmm_b200_update_values(self.h, _ptr(s_val)), "update_values")
+
     def run(self):
         self._check(self.lib.sddmm_b200_run(self.h), "run")
 
