@@ -273,12 +273,17 @@ def kernel_only_stats(eng, steps, warmup, flush):
     for _ in range(warmup):
         eng.run(); eng.sync()
     tot, per = [], {}
-    for _ in range(steps):
+    for _ in range(steps):   # step time: no instrumentation between the kernels
         flush()
         eng.run(); eng.sync()
         tot.append(eng.last_run_ms())
+    eng.set_kernel_timing(True)
+    for _ in range(max(3, steps // 2)):   # per-kernel times: separate, instrumented steps
+        flush()
+        eng.run(); eng.sync()
         for name, ms in eng.kernel_times():
             per.setdefault(name, []).append(ms)
+    eng.set_kernel_timing(False)
     return float(np.mean(tot)), {k: float(np.mean(v)) for k, v in per.items()}
 
 
@@ -372,14 +377,20 @@ def main():
     sampler = ClockSampler(local) if rank == 0 else None
     wall0 = time.perf_counter()
     step_ms, kern = [], {}
-    for _ in range(args.steps):
+    for _ in range(args.steps):   # the timed steps: no instrumentation between the kernels
         flush()
         eng.run(); eng.sync()
         step_ms.append(eng.last_run_ms())
-        for name, ms in eng.kernel_times():
-            kern.setdefault(name, []).append(ms)
     barrier()
     wall = time.perf_counter() - wall0
+    # a few more steps with an event pair around every kernel, for the roofline of the dominant kernel (not part of `value`)
+    eng.set_kernel_timing(True)
+    for _ in range(max(3, min(args.steps, 10))):
+        flush()
+        eng.run(); eng.sync()
+        for name, ms in eng.kernel_times():
+            kern.setdefault(name, []).append(ms)
+    eng.set_kernel_timing(False)
     # keep the GPU busy a little longer so the clock sampler sees it under load even for short runs
     t_end = time.perf_counter() + (0.6 if rank == 0 else 0.0)
     while time.perf_counter() < t_end:

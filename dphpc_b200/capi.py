@@ -35,7 +35,7 @@ ENGINE_SYMBOLS = [
     "sddmm_b200_sync", "sddmm_b200_download", "sddmm_b200_p_device", "sddmm_b200_last_run_ms", "sddmm_b200_last_kernel_ms",
     "sddmm_b200_get_plan", "sddmm_b200_algorithmic_bytes", "sddmm_b200_flops", "sddmm_b200_last_error",
     "sddmm_b200_stream", "sddmm_b200_device_count", "sddmm_b200_version", "sddmm_b200_host_alloc",
-    "sddmm_b200_host_free", "sddmm_b200_sddmm_csr_prealloc",
+    "sddmm_b200_host_free", "sddmm_b200_sddmm_csr_prealloc", "sddmm_b200_set_kernel_timing",
 ]
 DATASET_SYMBOLS = [
     "sddmm_dataset_create", "sddmm_dataset_create_uniform", "sddmm_dataset_destroy", "sddmm_dataset_dims",
@@ -106,6 +106,7 @@ def load_engine_lib() -> C.CDLL:
     lib.sddmm_b200_p_device.argtypes = [H, C.POINTER(C.c_void_p)]
     lib.sddmm_b200_last_run_ms.argtypes = [H, C.POINTER(C.c_float)]
     lib.sddmm_b200_last_kernel_ms.argtypes = [H, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_char_p)]
+    lib.sddmm_b200_set_kernel_timing.argtypes = [H, C.c_int]
     lib.sddmm_b200_get_plan.argtypes = [H, C.POINTER(PlanInfo)]
     lib.sddmm_b200_algorithmic_bytes.argtypes = [H]
     lib.sddmm_b200_algorithmic_bytes.restype = C.c_int64
@@ -266,8 +267,12 @@ class Engine:
         self._check(self.lib.sddmm_b200_last_run_ms(self.h, C.byref(ms)), "last_run_ms")
         return float(ms.value)
 
+    def set_kernel_timing(self, enabled: bool = True):
+        """Record an event pair around every kernel of the following run() calls (costs microseconds per launch)."""
+        self._check(self.lib.sddmm_b200_set_kernel_timing(self.h, 1 if enabled else 0), "set_kernel_timing")
+
     def kernel_times(self) -> list:
-        """[(kernel name, device ms)] of the last run()."""
+        """[(kernel name, device ms)] of the last run(); ms is -1 unless set_kernel_timing(True) was in effect."""
         out = []
         for i in range(self.plan()["n_kernels"]):
             ms, name = C.c_float(), C.c_char_p()

@@ -56,9 +56,11 @@ struct sddmm_b200_engine {
     cudaEvent_t ev_begin[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};  // per kernel, on the stream it runs on
     cudaEvent_t ev_end[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};
     cudaEvent_t ev_run0 = nullptr, ev_run1 = nullptr;   // whole run(), on the main stream
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_join = nullptr;
     const char *kernel_name[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};
     int kernels_launched = 0;
+    bool kernel_timing = false;    // record an event pair around every kernel (sddmm_b200_set_kernel_timing)
+    bool last_run_timed = false;   // ... and whether the last run() did
     int sm_count = 148;
     char err[512] = {0};
 
@@ -577,6 +579,7 @@ int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t
 
 // events right before / right after kernel number `kernels_launched`, on the stream it is launched on
 int begin_kernel(sddmm_b200_engine *e, cudaStream_t st) {
+    if (!e->kernel_timing) return SDDMM_B200_OK;   // a timing event between two launches costs microseconds: only on request
     CU_TRY(e, cudaEventRecord(e->ev_begin[e->kernels_launched], st));
     return SDDMM_B200_OK;
 }
@@ -584,7 +587,7 @@ int mark_kernel(sddmm_b200_engine *e, const char *name, cudaStream_t st) {
     CU_TRY(e, cudaGetLastError());
     const int idx = e->kernels_launched;
     e->kernel_name[idx] = name;
-    CU_TRY(e, cudaEventRecord(e->ev_end[idx], st));
+    if (e->kernel_timing) CU_TRY(e, cudaEventRecord(e->ev_end[idx], st));
     e->kernels_launched = idx + 1;
     return SDDMM_B200_OK;
 }
@@ -612,10 +615,7 @@ int launch_all(sddmm_b200_engine *e) {
     static const bool no_side = std::getenv("SDDMM_B200_NO_SIDE_STREAM") != nullptr;   // tuning / debugging knob
     const bool both = e->n_dense > 0 && e->n_residual_items > 0 && !no_side;
     cudaStream_t rt_stream = both ? e->side_stream : e->stream;
-    if (both) {
-        CU_TRY(e, cudaEventRecord(e->ev_fork, e->stream));
-        CU_TRY(e, cudaStreamWaitEvent(e->side_stream, e->ev_fork, 0));
-    }
+    if (both) CU_TRY(e, cudaStreamWaitEvent(e->side_stream, e->ev_run0, 0));   // (run() has just recorded it on the main stream)
     if (e->n_dense > 0) {
         DenseArgs d;
         d.tile_ids = e->d_dense_ids; d.descs = e->d_dense_descs; d.s_val = e->d_sval; d.p_val = e->d_pval; d.err = e->d_err;
@@ -686,7 +686,6 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     for (int i = 0; i < sddmm_b200_engine::kMaxKernels; ++i)
         ok = ok && cudaEventCreate(&e->ev_begin[i]) == cudaSuccess && cudaEventCreate(&e->ev_end[i]) == cudaSuccess;
     ok = ok && cudaEventCreate(&e->ev_run0) == cudaSuccess && cudaEventCreate(&e->ev_run1) == cudaSuccess;
-    ok = ok && cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess;
     ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&e->h_err), sizeof(int32_t), cudaHostAllocDefault) == cudaSuccess;
@@ -712,7 +711,7 @@ int sddmm_b200_destroy(sddmm_b200_engine *e) {
             if (e->ev_begin[i]) cudaEventDestroy(e->ev_begin[i]);
             if (e->ev_end[i]) cudaEventDestroy(e->ev_end[i]);
         }
-        for (cudaEvent_t ev : {e->ev_run0, e->ev_run1, e->ev_fork, e->ev_join})
+        for (cudaEvent_t ev : {e->ev_run0, e->ev_run1, e->ev_join})
             if (ev) cudaEventDestroy(ev);
         if (e->side_stream) cudaStreamDestroy(e->side_stream);
         if (e->stream) cudaStreamDestroy(e->stream);
@@ -788,6 +787,7 @@ int sddmm_b200_run(sddmm_b200_engine *e) {
     if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "run before upload");
     DeviceGuard g(e->device);
     CU_TRY(e, cudaEventRecord(e->ev_run0, e->stream));
+    e->last_run_timed = e->kernel_timing;
     int st = launch_all(e);
     if (st) return st;
     CU_TRY(e, cudaEventRecord(e->ev_run1, e->stream));
@@ -836,10 +836,20 @@ int sddmm_b200_last_kernel_ms(sddmm_b200_engine *e, int index, float *ms, const 
     if (!e || !ms) return SDDMM_B200_ERR_ARG;
     if (!e->ran) return fail(e, SDDMM_B200_ERR_STATE, "last_kernel_ms before run");
     if (index < 0 || index >= e->kernels_launched) return fail(e, SDDMM_B200_ERR_ARG, "kernel index %d of %d", index, e->kernels_launched);
+    if (name) *name = e->kernel_name[index];
+    if (!e->last_run_timed) {   // names are always known, times only when the run was asked to record them
+        *ms = -1.f;
+        return SDDMM_B200_OK;
+    }
     DeviceGuard g(e->device);
     CU_TRY(e, cudaEventSynchronize(e->ev_end[index]));
     CU_TRY(e, cudaEventElapsedTime(ms, e->ev_begin[index], e->ev_end[index]));
-    if (name) *name = e->kernel_name[index];
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_set_kernel_timing(sddmm_b200_engine *e, int enabled) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    e->kernel_timing = enabled != 0;
     return SDDMM_B200_OK;
 }
 

@@ -138,8 +138,11 @@ int sddmm_b200_p_device(sddmm_b200_engine *e, float **p_val_device);
  * Device time of the last run() (CUDA events on the engine's stream), standing
  * in for the cudaEvent pair of Benchmark<T>::timing (src/benchmark/benchmark.hpp:160-164). */
 int sddmm_b200_last_run_ms(sddmm_b200_engine *e, float *ms);
-/* Device time and name of kernel `index` (0 .. plan.n_kernels-1) of the last run(). */
+/* Device time and name of kernel `index` (0 .. plan.n_kernels-1) of the last run().  The name is always
+ * returned; the time only if per-kernel timing was on for that run (else *ms = -1): an event pair around
+ * every kernel costs several microseconds per launch, so it is off unless asked for. */
 int sddmm_b200_last_kernel_ms(sddmm_b200_engine *e, int index, float *ms, const char **name);
+int sddmm_b200_set_kernel_timing(sddmm_b200_engine *e, int enabled);
 int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info);
 /* compulsory traffic e*K*(M+ + N+) + 12*nnz + 4*(M+1) with e = bytes per stored
  * element of A/B; extends the read-only model of plots/plot_roofline.py:30 */

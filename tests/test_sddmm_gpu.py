@@ -322,3 +322,23 @@ def test_row_groups_not_taken_without_structure(engines):
     e = engines["fp32"]
     e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
     assert e.plan()["rowgroup_rows"] == 0 and e.plan()["rowtile_nnz"] == d.nnz
+
+
+def test_kernel_timing_is_opt_in():
+    # kernel names are always reported; an event pair around every kernel is recorded only on request
+    d = Dataset(2, 32, 0.12)
+    e = Engine(0, "fp32_tc")
+    try:
+        e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        names = [n for n, _ in e.kernel_times()]
+        assert names == ["sddmm_dense_tile_kernel", "sddmm_rowtile_kernel"]
+        assert all(ms == -1.0 for _, ms in e.kernel_times())
+        e.set_kernel_timing(True)
+        e.run(); e.sync()
+        assert [n for n, _ in e.kernel_times()] == names and all(ms > 0 for _, ms in e.kernel_times())
+        assert e.last_run_ms() > 0
+        e.set_kernel_timing(False)
+        e.run(); e.sync()
+        assert all(ms == -1.0 for _, ms in e.kernel_times()) and e.last_run_ms() > 0
+    finally:
+        e.close()
