@@ -227,7 +227,7 @@ def test_update_values_and_dense_keep_the_plan(engines, oracle):
 
 # ---- full BASELINE sizes: size-independent properties + sampled comparison --------------------------
 @pytest.mark.parametrize("cfg,K,mode", [(2, 32, "fp32"), (2, 32, "fp32_tc"), (2, 32, "tf32"), (3, 64, "fp32"), (4, 32, "fp32"),
-                                        (5, 32, "fp32"), (5, 32, "bf16")])
+                                        (5, 32, "fp32"), (5, 32, "bf16"), (2, 64, "fp32_tc"), (3, 32, "fp32_tc"), (5, 128, "bf16")])
 def test_full_size_properties(engines, oracle, cfg, K, mode):
     d = Dataset(cfg, K, 1.0)
     e = engines[mode]
