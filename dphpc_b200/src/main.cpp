@@ -1,7 +1,8 @@
 // sddmm_bench: benchmark driver for the GPU-B200 competitor on the seeded synthetic configurations or on a matrix file.
 // Command line of the reference's driver (src/main.cpp:285-349: --K/-k, --no_csv_header, --num_runs;
 // --data_folder is accepted and ignored) plus --config, --scale, --mode, and --mtx FILE (MatrixMarket coordinate file) or
-// --edges FILE --rows M --cols N (SNAP edge list), read with the reference's rules (src/benchmark/dataset.hpp:122-181, 270-313).
+// --edges FILE --rows M --cols N (SNAP edge list), read with the reference's rules (src/benchmark/dataset.hpp:122-181, 270-313);
+// --multi adds the row-sharded competitor that uses every visible GPU from this one process.
 // The first competitor is the correctness baseline of the harness; here that is GPU-B200 in fp32
 // mode (the independent CPU check lives in the test-suite, not in this binary).
 #include <cstdlib>
@@ -20,6 +21,7 @@ struct Options {
     std::string mtx, edges;
     double scale = 1.0;
     bool header = true;
+    bool multi = false;   // also run the row-sharded competitor on every visible GPU
     std::vector<std::string> modes{"fp32", "fp32_tc"};   // tf32 / bf16 on request: their 1e-2 error fails the 1e-3 check
 };
 
@@ -33,7 +35,7 @@ int mode_id(const std::string &m) {
 
 void usage() {
     std::cerr << "usage: sddmm_bench [--config 1..5 (default: all) | --mtx FILE | --edges FILE --rows M --cols N] [-k K] [--num_runs R] [--scale s]"
-                 " [--mode fp32,tf32,...] [--no_csv_header]\n";
+                 " [--mode fp32,tf32,...] [--multi] [--no_csv_header]\n";
 }
 
 }  // namespace
@@ -53,6 +55,7 @@ int main(int argc, char **argv) {
         else if (a == "--cols") o.cols = std::atoi(next());
         else if (a == "--scale") o.scale = std::atof(next());
         else if (a == "--no_csv_header") o.header = false;
+        else if (a == "--multi") o.multi = true;
         else if (a == "-d" || a == "--data_folder") next();
         else if (a == "--mode") {
             o.modes.clear();
@@ -73,6 +76,11 @@ int main(int argc, char **argv) {
         const int id = mode_id(m);
         if (id < 0) { usage(); return 2; }
         if (id != SDDMM_B200_FP32) competitors.push_back(std::make_shared<Competitors::GPUB200>(id, 0, "GPU-B200-" + m));
+    }
+    if (o.multi) {
+        const int n = sddmm_b200_device_count();
+        for (const std::string &m : o.modes)
+            competitors.push_back(std::make_shared<Competitors::GPUB200Multi>(std::vector<int>{}, mode_id(m), "GPU-B200-" + m + "-x" + std::to_string(n)));
     }
     if (o.header) FILE_DUMP(SDDMM::Benchmark<float>::csv_header() << std::endl);
     const int default_k[6] = {0, 32, 32, 64, 32, 32};

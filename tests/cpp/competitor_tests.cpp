@@ -3,6 +3,7 @@
 // CPU-Basic).  CPU-Basic here is the C oracle (oracle/sddmm_oracle.c), linked into this test binary only.
 // Cases: sddmm_coo1..4 (:124-182), random suites (:184-246), DummyDataset, csr-vs-coo agreement, and
 // reuse of one competitor object across datasets (the harness does that, src/benchmark/benchmark.hpp:64-137).
+#include <algorithm>
 #include <cmath>
 #include <memory>
 
@@ -39,7 +40,12 @@ public:
 std::vector<std::shared_ptr<SDDMM::Competitor<float>>> &competitors() {
     static std::vector<std::shared_ptr<SDDMM::Competitor<float>>> c{
         std::make_shared<CPUOracle>(), std::make_shared<Competitors::GPUB200>(SDDMM_B200_FP32, 0, "GPU-B200"),
-        std::make_shared<Competitors::GPUB200>(SDDMM_B200_FP32_TC, 0, "GPU-B200-fp32_tc")};
+        std::make_shared<Competitors::GPUB200>(SDDMM_B200_FP32_TC, 0, "GPU-B200-fp32_tc"),
+        // row shards over several engines: every visible device; two and three engines on device 0 (the sharding
+        // logic is the same, so it is also covered on a single-GPU machine)
+        std::make_shared<Competitors::GPUB200Multi>(std::vector<int>{}, SDDMM_B200_FP32, "GPU-B200-all"),
+        std::make_shared<Competitors::GPUB200Multi>(std::vector<int>{0, 0}, SDDMM_B200_FP32, "GPU-B200-2shards"),
+        std::make_shared<Competitors::GPUB200Multi>(std::vector<int>{0, 0, 0}, SDDMM_B200_FP32_TC, "GPU-B200-3shards-fp32_tc")};
     return c;
 }
 
@@ -136,6 +142,41 @@ TEST_CASE(harness_dummy_and_synthetic) {
     SDDMM::Benchmark<float> b3(power, competitors(), 1);
     CHECK_EQ(b3.benchmark(), 0);
 }
+TEST_CASE(row_cuts_balance_nonzeros) {
+    // 6 rows with 0, 10, 0, 10, 30, 10 nonzeros: halves cut after row 4 would be 20 | 40, after row 5 50 | 10 -> the closer
+    // boundary to 30 is row_ptr = 20 (cut at row 4)
+    const std::vector<int> rp{0, 0, 10, 10, 20, 50, 60};
+    CHECK(Competitors::GPUB200Multi::row_cuts(rp, 2) == std::vector<int64_t>({0, 4, 6}));
+    CHECK(Competitors::GPUB200Multi::row_cuts(rp, 1) == std::vector<int64_t>({0, 6}));
+    const std::vector<int64_t> c3 = Competitors::GPUB200Multi::row_cuts(rp, 3);
+    CHECK(c3.front() == 0 && c3.back() == 6 && std::is_sorted(c3.begin(), c3.end()));
+    // more shards than rows: cuts stay monotone, some shards are empty
+    const std::vector<int64_t> c8 = Competitors::GPUB200Multi::row_cuts(rp, 8);
+    CHECK(c8.size() == 9 && c8.front() == 0 && c8.back() == 6 && std::is_sorted(c8.begin(), c8.end()));
+    // aligned cuts land on multiples of 64
+    std::vector<int> big(1025);
+    for (int i = 0; i <= 1024; ++i) big[static_cast<size_t>(i)] = 7 * i;
+    for (int64_t c : Competitors::GPUB200Multi::row_cuts(big, 4, 64)) CHECK(c % 64 == 0);
+}
+
+TEST_CASE(multi_device_shards_and_reuse) {
+    // a matrix big enough for aligned cuts and dense tiles, run twice through the same object with different inputs
+    auto multi = std::make_shared<Competitors::GPUB200Multi>(std::vector<int>{0, 0, 0}, SDDMM_B200_FP32_TC, "GPU-B200-3shards");
+    for (int round = 0; round < 2; ++round) {
+        SDDMM::SyntheticDataset d(round == 0 ? 2 : 3, round == 0 ? 32 : 64, round == 0 ? 0.15 : 0.01);
+        CSR<float> ref(d.getS_CSR()), P(d.getS_CSR());
+        competitors()[0]->run_csr(d.getA(), d.getB(), d.getS_CSR(), ref);
+        multi->init_csr(d.getA(), d.getB(), d.getS_CSR(), P);
+        multi->run_csr(d.getA(), d.getB(), d.getS_CSR(), P);
+        multi->cleanup_csr(d.getA(), d.getB(), d.getS_CSR(), P);
+        CHECK(multi->shards() == 3 && multi->cuts().size() == 4 && multi->last_kernel_ms() > 0.f);
+        std::vector<int> rows;
+        for (int i = 0; i < d.getS_CSR().getRows(); ++i)
+            rows.insert(rows.end(), static_cast<size_t>(d.getS_CSR().getRowPositions()[static_cast<size_t>(i) + 1] - d.getS_CSR().getRowPositions()[static_cast<size_t>(i)]), i);
+        CHECK(close_enough(d.getA(), d.getB(), d.getS_CSR(), rows, P, ref, 1e-5));
+    }
+}
+
 TEST_CASE(launch_shape_is_reported) {
     auto d = SDDMM::SyntheticDataset::uniform(300, 300, 32, 9000, 5);
     auto &gpu = *competitors()[1];

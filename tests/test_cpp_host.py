@@ -43,8 +43,9 @@ def test_benchmark_driver_builds():
 def test_competitor_header_drops_into_the_reference_tree(tmp_path):
     # compile GPUB200 against the reference's OWN competitor.hpp / matrices (not this repository's mirror)
     tu = tmp_path / "dropin.cpp"
-    tu.write_text('#include <cmath>\n#include "competitors/gpu/gpu_b200.hpp"\n'
-                  "int main() { Competitors::GPUB200 c; SDDMM::Competitor<float> *p = &c; return p->is_gpu() ? 0 : 1; }\n")
+    tu.write_text('#include <cmath>\n#include "competitors/gpu/gpu_b200.hpp"\n#include "competitors/gpu/gpu_b200_multi.hpp"\n'
+                  "int main() { Competitors::GPUB200 c; Competitors::GPUB200Multi m; SDDMM::Competitor<float> *p = &c, *q = &m;\n"
+                  "             return p->is_gpu() && q->is_gpu() ? 0 : 1; }\n")
     cuda_inc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
     cmd = ["g++", "-std=c++17", "-fsyntax-only", "-w", "-include", "cstdint", "-include", "cassert", "-I", str(REFERENCE / "src"),
            "-I", str(cuda_inc), "-I", str(ROOT / "include"), "-idirafter", str(SRC), str(tu)]
