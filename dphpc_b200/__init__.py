@@ -5,5 +5,5 @@ competitor in dphpc_b200/src; this package holds their sources, the in-tree
 build and thin ctypes bindings used by the tests and bench.py.
 """
 from .capi import (  # noqa: F401
-    BF16, FP32, FP32_TC, TF32, Dataset, Engine, SddmmError, device_count, load_dataset_lib, load_engine_lib,
+    BF16, FP32, FP32_TC, TF32, Dataset, Engine, Pipeline, SddmmError, device_count, load_dataset_lib, load_engine_lib,
 )

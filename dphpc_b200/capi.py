@@ -36,6 +36,8 @@ ENGINE_SYMBOLS = [
     "sddmm_b200_get_plan", "sddmm_b200_algorithmic_bytes", "sddmm_b200_flops", "sddmm_b200_last_error",
     "sddmm_b200_stream", "sddmm_b200_device_count", "sddmm_b200_version", "sddmm_b200_host_alloc",
     "sddmm_b200_host_free", "sddmm_b200_sddmm_csr_prealloc", "sddmm_b200_set_kernel_timing",
+    "sddmm_b200_pipeline_create", "sddmm_b200_pipeline_destroy", "sddmm_b200_pipeline_sddmm_csr",
+    "sddmm_b200_pipeline_last_chunks", "sddmm_b200_pipeline_last_error", "sddmm_b200_pipeline_set_min_chunk_bytes",
 ]
 DATASET_SYMBOLS = [
     "sddmm_dataset_create", "sddmm_dataset_create_uniform", "sddmm_dataset_destroy", "sddmm_dataset_dims",
@@ -121,6 +123,13 @@ def load_engine_lib() -> C.CDLL:
     lib.sddmm_b200_host_alloc.argtypes = [C.POINTER(C.c_void_p), C.c_int64]
     lib.sddmm_b200_host_free.argtypes = [C.c_void_p]
     lib.sddmm_b200_sddmm_csr_prealloc.argtypes = [C.c_int, C.c_void_p] + [C.c_int64] * 4 + [C.c_void_p] * 6
+    lib.sddmm_b200_pipeline_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_uint32, C.c_int]
+    lib.sddmm_b200_pipeline_destroy.argtypes = [H]
+    lib.sddmm_b200_pipeline_sddmm_csr.argtypes = [H, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 6
+    lib.sddmm_b200_pipeline_last_chunks.argtypes = [H]
+    lib.sddmm_b200_pipeline_set_min_chunk_bytes.argtypes = [H, C.c_int64]
+    lib.sddmm_b200_pipeline_last_error.argtypes = [H]
+    lib.sddmm_b200_pipeline_last_error.restype = C.c_char_p
     _engine_lib = lib
     return lib
 
@@ -304,6 +313,57 @@ class Engine:
         self.upload_coo(M, N, K, row_idx, col_idx, s_val, A, B)
         self.run()
         return self.download()
+
+
+class Pipeline:
+    """Chunked host-to-host SDDMM on one device (sddmm_b200_pipeline_* in include/sddmm_b200.h): upload, run and
+    download of consecutive row chunks overlapped."""
+
+    def __init__(self, device: int = 0, mode="fp32", flags: int = 0, chunks: int = 4, min_chunk_bytes: int | None = None):
+        self.lib = load_engine_lib()
+        self.h = C.c_void_p()
+        m = MODES[mode] if isinstance(mode, str) else int(mode)
+        st = self.lib.sddmm_b200_pipeline_create(C.byref(self.h), int(device), m, int(flags), int(chunks))
+        if st:
+            self.h = C.c_void_p()
+            raise SddmmError(st, "sddmm_b200_pipeline_create", "(no usable CUDA device?)" if st == 4 else "")
+        if min_chunk_bytes is not None and self.lib.sddmm_b200_pipeline_set_min_chunk_bytes(self.h, int(min_chunk_bytes)):
+            raise SddmmError(1, "sddmm_b200_pipeline_set_min_chunk_bytes")
+
+    def close(self):
+        if getattr(self, "h", None) and self.h.value:
+            self.lib.sddmm_b200_pipeline_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def sddmm_csr_raw(self, M, N, K, row_ptr, col_idx, s_val, A, B, p_val):
+        """Host pointers given as integers (e.g. pinned buffers); no conversion, no size check."""
+        st = self.lib.sddmm_b200_pipeline_sddmm_csr(self.h, M, N, K, _ptr(row_ptr), _ptr(col_idx), _ptr(s_val), _ptr(A), _ptr(B),
+                                                    _ptr(p_val))
+        if st:
+            raise SddmmError(st, "pipeline_sddmm_csr", self.lib.sddmm_b200_pipeline_last_error(self.h).decode())
+
+    def sddmm_csr(self, M, N, K, row_ptr, col_idx, s_val, A, B) -> np.ndarray:
+        row_ptr, col_idx = _as(row_ptr, np.int32), _as(col_idx, np.int32)
+        s_val, A, B = _as(s_val, np.float32), _as(A, np.float32), _as(B, np.float32)
+        assert row_ptr.size == M + 1 and A.size == M * K and B.size == N * K
+        out = np.empty(int(row_ptr[M]) if row_ptr[M] > 0 else 0, dtype=np.float32)
+        self.sddmm_csr_raw(M, N, K, row_ptr, col_idx, s_val, A, B, out)
+        return out
+
+    def last_chunks(self) -> int:
+        return int(self.lib.sddmm_b200_pipeline_last_chunks(self.h))
 
 
 def device_count() -> int:

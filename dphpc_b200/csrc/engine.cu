@@ -57,6 +57,12 @@ struct sddmm_b200_engine {
     cudaEvent_t ev_end[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};
     cudaEvent_t ev_run0 = nullptr, ev_run1 = nullptr;   // whole run(), on the main stream
     cudaEvent_t ev_join = nullptr;
+    // chunked host-to-host calls (pipeline.cuh): copies of consecutive row chunks are chained through these
+    cudaEvent_t ev_h2d = nullptr;                 // recorded after the upload's copies are enqueued
+    cudaEvent_t h2d_after = nullptr;              // another engine's ev_h2d: this upload's copies start after it
+    const float *B_on_device = nullptr;           // B already in this GPU's memory (another engine's copy): taken from there
+    void (*on_copies_enqueued)(void *) = nullptr; // called once ev_h2d is recorded
+    void *on_copies_user = nullptr;
     const char *kernel_name[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};
     int kernels_launched = 0;
     bool kernel_timing = false;    // record an event pair around every kernel (sddmm_b200_set_kernel_timing)
@@ -81,6 +87,7 @@ struct sddmm_b200_engine {
     PlanCounters *d_pc = nullptr;
     int32_t *d_err = nullptr;
     int32_t *h_err = nullptr;  // pinned mirror of the device error word
+    PlanCounters *h_pc = nullptr;  // pinned landing place of the plan counters (a pageable target would make the copy a staged, blocking one)
 
     // dense-tile (tensor-core) path
     bool dense_possible = false;   // buffers carved for this upload
@@ -312,6 +319,14 @@ int make_operand_map(sddmm_b200_engine *e, CUtensorMap *map, const float *base, 
 
 // Find the 64x64 tiles that are at least half full, build their row descriptors and the list
 // of work items the row-tile kernel still has to visit.
+// the plan counters as they are when the stream has drained
+int read_counters(sddmm_b200_engine *e, PlanCounters *out) {
+    CU_TRY(e, cudaMemcpyAsync(e->h_pc, e->d_pc, sizeof(PlanCounters), cudaMemcpyDeviceToHost, e->stream));
+    CU_TRY(e, cudaStreamSynchronize(e->stream));
+    *out = *e->h_pc;
+    return SDDMM_B200_OK;
+}
+
 int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item_nnz, int n_items) {
     e->n_dense = 0;
     e->n_residual_items = n_items;
@@ -328,8 +343,7 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
                                                                          e->d_dense_ids, e->dense_cap, e->d_pc);
     CU_TRY(e, cudaGetLastError());
     PlanCounters pc;
-    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
-    CU_TRY(e, cudaStreamSynchronize(s));
+    if (int rc = read_counters(e, &pc)) return rc;
     const int n_dense = std::min(pc.dense_tiles, e->dense_cap);
     if (n_dense <= 0) return SDDMM_B200_OK;
     k_tile_rows<DenseTileDesc><<<grid_for(static_cast<int64_t>(n_dense) * 64, kBlock, 1 << 30), kBlock, 0, s>>>(
@@ -338,8 +352,7 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     k_residual_items<<<grid_for(n_items, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_item_covered, n_items, item_nnz, e->nnz, e->d_item_ids,
                                                                           e->d_pc);
     CU_TRY(e, cudaGetLastError());
-    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
-    CU_TRY(e, cudaStreamSynchronize(s));
+    if (int rc = read_counters(e, &pc)) return rc;
     const bool split = e->mode == SDDMM_B200_FP32_TC;
     const int64_t kx = split ? 3 * e->K : e->K;
     int st = make_operand_map(e, &e->map_a, split ? e->d_Ax : e->d_A32, e->M, kx);
@@ -402,8 +415,7 @@ int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
                 &e->d_pc->group_cover[slot(G, first)], &e->d_pc->group_count[slot(G, first)]);
     CU_TRY(e, cudaGetLastError());
     PlanCounters pc;
-    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
-    CU_TRY(e, cudaStreamSynchronize(s));
+    if (int rc = read_counters(e, &pc)) return rc;
     int best = 0, best_first = 0;
     double best_saved = 0.0;
     for (int G = 2; G <= 4; ++G)
@@ -420,8 +432,7 @@ int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
         e->d_rp, e->d_col, static_cast<int32_t>(e->M), best, best_first, n_groups, 1, e->d_group_ok, &e->d_pc->group_cover[bs],
         &e->d_pc->group_count[bs]);
     CU_TRY(e, cudaGetLastError());
-    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));   // exact counts of the chosen grouping
-    CU_TRY(e, cudaStreamSynchronize(s));
+    if (int rc = read_counters(e, &pc)) return rc;   // exact counts of the chosen grouping
     if (static_cast<double>(pc.group_cover[bs]) * (1.0 - 1.0 / best) < 0.3 * static_cast<double>(e->nnz)) return SDDMM_B200_OK;   // the sample overestimated
     RowGroupFn fn = pick_rowgroup(best, static_cast<int>(e->K / 32));
     int occ = 0;
@@ -453,15 +464,13 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
                                                                               e->d_rp, e->d_pc);
         // refuse to interpret a row_ptr built from unsorted rows
         PlanCounters pc0;
-        CU_TRY(e, cudaMemcpyAsync(&pc0, e->d_pc, sizeof(pc0), cudaMemcpyDeviceToHost, s));
-        CU_TRY(e, cudaStreamSynchronize(s));
+        if (int rc = read_counters(e, &pc0)) return rc;
         if (pc0.bad_coo) return fail(e, SDDMM_B200_ERR_INDEX, "COO row indices must be sorted and inside [0, M)");
     }
     k_row_stats<<<grid_for(e->M, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_rp, static_cast<int32_t>(e->M), e->nnz, e->d_rowstart, e->d_pc);
     CU_TRY(e, cudaGetLastError());
     PlanCounters pc;
-    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
-    CU_TRY(e, cudaStreamSynchronize(s));
+    if (int rc = read_counters(e, &pc)) return rc;
     if (pc.bad_row_ptr) return fail(e, SDDMM_B200_ERR_INDEX, "row_ptr must start at 0, end at nnz and be non-decreasing");
     if (e->nnz > 0) {
         k_col_scan<<<grid_for(e->nnz, kBlock, cap), kBlock, 0, s>>>(e->d_col, e->nnz, static_cast<int32_t>(e->N), e->d_rowstart,
@@ -471,8 +480,7 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
                                                                           e->d_item_rows);
         CU_TRY(e, cudaGetLastError());
     }
-    CU_TRY(e, cudaMemcpyAsync(&pc, e->d_pc, sizeof(pc), cudaMemcpyDeviceToHost, s));
-    CU_TRY(e, cudaStreamSynchronize(s));
+    if (int rc = read_counters(e, &pc)) return rc;
     if (pc.bad_col) return fail(e, SDDMM_B200_ERR_INDEX, "column index outside [0, N)");
 
     sddmm_b200_plan_info &p = e->plan;
@@ -561,6 +569,7 @@ int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t
     int st = carve_arena(e, coo_rows != nullptr, n_items);
     if (st) return st;
     cudaStream_t s = e->stream;
+    if (e->h2d_after) CU_TRY(e, cudaStreamWaitEvent(s, e->h2d_after, 0));
     if (row_ptr) CU_TRY(e, cudaMemcpyAsync(e->d_rp, row_ptr, static_cast<size_t>(M + 1) * 4, kind, s));
     if (coo_rows && nnz) CU_TRY(e, cudaMemcpyAsync(e->d_coo_rows, coo_rows, static_cast<size_t>(nnz) * 4, kind, s));
     if (nnz) {
@@ -568,7 +577,10 @@ int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t
         CU_TRY(e, cudaMemcpyAsync(e->d_sval, s_val, static_cast<size_t>(nnz) * 4, kind, s));
     }
     CU_TRY(e, cudaMemcpyAsync(e->d_A32, A, static_cast<size_t>(M * K) * 4, kind, s));
-    CU_TRY(e, cudaMemcpyAsync(e->d_B32, B, static_cast<size_t>(N * K) * 4, kind, s));
+    if (e->B_on_device) CU_TRY(e, cudaMemcpyAsync(e->d_B32, e->B_on_device, static_cast<size_t>(N * K) * 4, cudaMemcpyDeviceToDevice, s));
+    else CU_TRY(e, cudaMemcpyAsync(e->d_B32, B, static_cast<size_t>(N * K) * 4, kind, s));
+    CU_TRY(e, cudaEventRecord(e->ev_h2d, s));
+    if (e->on_copies_enqueued) e->on_copies_enqueued(e->on_copies_user);
     st = convert_storage(e);
     if (st) return st;
     st = build_plan(e, item_nnz, n_items);
@@ -687,8 +699,10 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
         ok = ok && cudaEventCreate(&e->ev_begin[i]) == cudaSuccess && cudaEventCreate(&e->ev_end[i]) == cudaSuccess;
     ok = ok && cudaEventCreate(&e->ev_run0) == cudaSuccess && cudaEventCreate(&e->ev_run1) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&e->ev_h2d, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess;
     ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&e->h_err), sizeof(int32_t), cudaHostAllocDefault) == cudaSuccess;
+    ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&e->h_pc), sizeof(PlanCounters), cudaHostAllocDefault) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
         sddmm_b200_destroy(e);
@@ -706,12 +720,13 @@ int sddmm_b200_destroy(sddmm_b200_engine *e) {
         if (e->stream) cudaStreamSynchronize(e->stream);
         if (e->arena.base) cudaFree(e->arena.base);
         if (e->h_err) cudaFreeHost(e->h_err);
+        if (e->h_pc) cudaFreeHost(e->h_pc);
         if (e->side_stream) cudaStreamSynchronize(e->side_stream);
         for (int i = 0; i < sddmm_b200_engine::kMaxKernels; ++i) {
             if (e->ev_begin[i]) cudaEventDestroy(e->ev_begin[i]);
             if (e->ev_end[i]) cudaEventDestroy(e->ev_end[i]);
         }
-        for (cudaEvent_t ev : {e->ev_run0, e->ev_run1, e->ev_join})
+        for (cudaEvent_t ev : {e->ev_run0, e->ev_run1, e->ev_join, e->ev_h2d})
             if (ev) cudaEventDestroy(ev);
         if (e->side_stream) cudaStreamDestroy(e->side_stream);
         if (e->stream) cudaStreamDestroy(e->stream);
@@ -964,3 +979,5 @@ int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int6
 }
 
 }  // extern "C"
+
+#include "pipeline.cuh"

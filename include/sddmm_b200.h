@@ -179,6 +179,29 @@ int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int6
                                   const int32_t *d_row_ptr, const int32_t *d_col_idx, const float *d_s_val,
                                   const float *d_A, const float *d_B, float *d_p_val);
 
+/* ---- chunked host-to-host call ------------------------------------------------------
+ * The one-shot sequence of the reference's harness -- init_csr, run_csr, cleanup_csr
+ * (src/benchmark/benchmark.hpp:81-83) -- as ONE call on host buffers, with the three phases
+ * of consecutive row chunks overlapped: the rows of S are cut into up to `chunks` contiguous
+ * ranges with equal shares of the nonzeros; while one range is planned, computed and copied
+ * back, the next one's inputs are already crossing the (full-duplex) host link.  B crosses
+ * the link once.  The result is the same as upload_csr + run + download on one engine
+ * (every nonzero is computed by the same kernels; which rows reach the tensor-core tiles is
+ * decided per range).  A range is not made smaller than 64 MB of host-link traffic (12 bytes
+ * per nonzero + A + B; sddmm_b200_pipeline_set_min_chunk_bytes changes that), so small inputs
+ * run as one range.  For full overlap the host buffers should be pinned
+ * (sddmm_b200_host_alloc); pageable buffers work, with less overlap.
+ * Errors: the status codes above; sddmm_b200_pipeline_last_error names the row range. */
+typedef struct sddmm_b200_pipeline sddmm_b200_pipeline;
+int sddmm_b200_pipeline_create(sddmm_b200_pipeline **out, int device, int mode, uint32_t flags, int chunks /* 1..64 */);
+int sddmm_b200_pipeline_destroy(sddmm_b200_pipeline *p);
+int sddmm_b200_pipeline_sddmm_csr(sddmm_b200_pipeline *p, int64_t M, int64_t N, int64_t K, const int32_t *row_ptr,
+                                  const int32_t *col_idx, const float *s_val, const float *A, const float *B,
+                                  float *p_val /* nnz, out */);
+int sddmm_b200_pipeline_last_chunks(sddmm_b200_pipeline *p); /* ranges the last call used */
+int sddmm_b200_pipeline_set_min_chunk_bytes(sddmm_b200_pipeline *p, int64_t bytes);
+const char *sddmm_b200_pipeline_last_error(sddmm_b200_pipeline *p);
+
 /* pinned host memory helpers (so callers without a CUDA toolchain can stage
  * inputs for full-rate copies) */
 int sddmm_b200_host_alloc(void **ptr, int64_t bytes);

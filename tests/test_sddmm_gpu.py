@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 import oracle_lib
-from dphpc_b200 import Dataset, Engine, SddmmError
+from dphpc_b200 import Dataset, Engine, Pipeline, SddmmError
 
 pytestmark = pytest.mark.gpu
 
@@ -342,3 +342,59 @@ def test_kernel_timing_is_opt_in():
         assert all(ms == -1.0 for _, ms in e.kernel_times()) and e.last_run_ms() > 0
     finally:
         e.close()
+
+
+@pytest.mark.parametrize("cfg,scale,K,mode,chunks", [(2, 0.3, 32, "fp32_tc", 4), (2, 0.3, 32, "fp32", 3), (2, 0.25, 32, "tf32", 8),
+                                                      (3, 0.02, 64, "fp32", 4), (5, 0.02, 32, "fp32", 5), (5, 0.01, 128, "bf16", 2)])
+def test_pipeline_matches_oracle_and_engine(engines, oracle, cfg, scale, K, mode, chunks):
+    # chunked host-to-host call: same values as one engine (same kernels per nonzero), pattern order kept across the cuts
+    d = Dataset(cfg, K, scale)
+    with Pipeline(0, mode, chunks=chunks, min_chunk_bytes=1 << 20) as pl:
+        p = pl.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        assert 1 < pl.last_chunks() <= chunks
+        p_again = pl.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)   # the object is reusable
+    np.testing.assert_array_equal(p, p_again)
+    p_ref = oracle.sddmm_csr(d.M, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    rows = oracle.coo_rows(d.M, d.row_ptr)
+    bound = oracle_lib.abs_dot_bound(rows, d.col_idx, d.s_val, d.A, d.B)
+    oracle_lib.assert_values_close(p, p_ref, bound, TOL[mode], f"pipeline {mode} cfg{cfg}")
+    p_one = engines[mode].sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    oracle_lib.assert_values_close(p, p_one, bound, 2 * TOL[mode], f"pipeline vs one engine {mode} cfg{cfg}")
+
+
+def test_pipeline_edges(oracle):
+    rng = np.random.default_rng(7)
+    with Pipeline(0, "fp32", chunks=4, min_chunk_bytes=4 << 20) as pl:
+        # small input: one range; golden-sized case exact
+        A = np.ones((3, 4), np.float32)
+        assert pl.sddmm_csr(3, 3, 4, [0, 1, 2, 3], [0, 1, 2], [1, 1, 1], A, A).tolist() == [4.0, 4.0, 4.0]
+        assert pl.last_chunks() == 1
+        # no nonzeros at all
+        assert pl.sddmm_csr(3, 3, 4, [0, 0, 0, 0], [], [], A, A).size == 0
+        # all nonzeros in few rows between long runs of empty rows: some ranges hold no rows or no nonzeros
+        M, N, K = 40, 300000, 32
+        lens = np.zeros(M, np.int64)
+        lens[[5, 6, 30]] = [200000, 150000, 100000]
+        rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        ci = np.concatenate([np.sort(rng.choice(N, n, replace=False)) for n in lens if n]).astype(np.int32)
+        sv = rng.uniform(-1, 1, ci.size).astype(np.float32)
+        A, B = rng.uniform(-1, 1, (M, K)).astype(np.float32), rng.uniform(-1, 1, (N, K)).astype(np.float32)
+        p = pl.sddmm_csr(M, N, K, rp, ci, sv, A, B)
+        assert pl.last_chunks() == 4
+        p_ref = oracle.sddmm_csr(M, K, rp, ci, sv, A, B)
+        bound = oracle_lib.abs_dot_bound(oracle.coo_rows(M, rp), ci, sv, A, B)
+        oracle_lib.assert_values_close(p, p_ref, bound, 1e-5, "pipeline ragged")
+        # errors name the status of the engine; the object stays usable
+        bad = rp.copy()
+        bad[7] = bad[6] - 5
+        with pytest.raises(SddmmError) as ei:
+            pl.sddmm_csr(M, N, K, bad, ci, sv, A, B)
+        assert ei.value.code == 2
+        ci_bad = ci.copy()
+        ci_bad[-1] = N
+        with pytest.raises(SddmmError) as ei:
+            pl.sddmm_csr(M, N, K, rp, ci_bad, sv, A, B)
+        assert ei.value.code == 2
+        np.testing.assert_array_equal(pl.sddmm_csr(M, N, K, rp, ci, sv, A, B), p)
+    with pytest.raises(SddmmError):
+        Pipeline(0, "fp32", chunks=0)
