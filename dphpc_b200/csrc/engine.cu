@@ -558,6 +558,30 @@ int check_dims(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nn
     return SDDMM_B200_OK;
 }
 
+int cuda_status(sddmm_b200_engine *e, cudaError_t err) {
+    CU_TRY(e, err);
+    return SDDMM_B200_OK;
+}
+
+// all copies of an upload: pattern on the main stream, then values and dense operands on the side stream; ev_h2d after the last
+int enqueue_copies(sddmm_b200_engine *e, const int32_t *row_ptr, const int32_t *coo_rows, const int32_t *col_idx, const float *s_val,
+                   const float *A, const float *B, cudaMemcpyKind kind) {
+    cudaStream_t s = e->stream, s2 = e->side_stream;
+    const int64_t M = e->M, N = e->N, K = e->K, nnz = e->nnz;
+    if (row_ptr) CU_TRY(e, cudaMemcpyAsync(e->d_rp, row_ptr, static_cast<size_t>(M + 1) * 4, kind, s));
+    if (coo_rows && nnz) CU_TRY(e, cudaMemcpyAsync(e->d_coo_rows, coo_rows, static_cast<size_t>(nnz) * 4, kind, s));
+    if (nnz) CU_TRY(e, cudaMemcpyAsync(e->d_col, col_idx, static_cast<size_t>(nnz) * 4, kind, s));
+    CU_TRY(e, cudaEventRecord(e->ev_join, s));
+    CU_TRY(e, cudaStreamWaitEvent(s2, e->ev_join, 0));   // keeps the link order: pattern first
+    if (nnz) CU_TRY(e, cudaMemcpyAsync(e->d_sval, s_val, static_cast<size_t>(nnz) * 4, kind, s2));
+    CU_TRY(e, cudaMemcpyAsync(e->d_A32, A, static_cast<size_t>(M * K) * 4, kind, s2));
+    if (e->B_on_device) CU_TRY(e, cudaMemcpyAsync(e->d_B32, e->B_on_device, static_cast<size_t>(N * K) * 4, cudaMemcpyDeviceToDevice, s2));
+    else CU_TRY(e, cudaMemcpyAsync(e->d_B32, B, static_cast<size_t>(N * K) * 4, kind, s2));
+    CU_TRY(e, cudaEventRecord(e->ev_h2d, s2));
+    if (e->on_copies_enqueued) e->on_copies_enqueued(e->on_copies_user);
+    return SDDMM_B200_OK;
+}
+
 int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz, const int32_t *row_ptr,
                   const int32_t *coo_rows, const int32_t *col_idx, const float *s_val, const float *A, const float *B,
                   cudaMemcpyKind kind) {
@@ -568,23 +592,20 @@ int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t
     const int n_items = static_cast<int>((nnz + item_nnz - 1) / item_nnz);
     int st = carve_arena(e, coo_rows != nullptr, n_items);
     if (st) return st;
-    cudaStream_t s = e->stream;
+    // The pattern goes first on the main stream and is planned there while S.val, A and B -- which the plan does not
+    // read -- still cross the host link on the side stream.
+    cudaStream_t s = e->stream, s2 = e->side_stream;
     if (e->h2d_after) CU_TRY(e, cudaStreamWaitEvent(s, e->h2d_after, 0));
-    if (row_ptr) CU_TRY(e, cudaMemcpyAsync(e->d_rp, row_ptr, static_cast<size_t>(M + 1) * 4, kind, s));
-    if (coo_rows && nnz) CU_TRY(e, cudaMemcpyAsync(e->d_coo_rows, coo_rows, static_cast<size_t>(nnz) * 4, kind, s));
-    if (nnz) {
-        CU_TRY(e, cudaMemcpyAsync(e->d_col, col_idx, static_cast<size_t>(nnz) * 4, kind, s));
-        CU_TRY(e, cudaMemcpyAsync(e->d_sval, s_val, static_cast<size_t>(nnz) * 4, kind, s));
+    st = enqueue_copies(e, row_ptr, coo_rows, col_idx, s_val, A, B, kind);
+    if (!st) st = build_plan(e, item_nnz, n_items);
+    if (!st) st = cuda_status(e, cudaStreamWaitEvent(s, e->ev_h2d, 0));
+    if (!st) st = convert_storage(e);
+    if (!st) st = cuda_status(e, cudaStreamSynchronize(s));   // the caller's buffers are free again when this returns
+    if (st) {   // nothing of a failed upload may still be reading the caller's buffers
+        cudaStreamSynchronize(s2);
+        cudaStreamSynchronize(s);
+        return st;
     }
-    CU_TRY(e, cudaMemcpyAsync(e->d_A32, A, static_cast<size_t>(M * K) * 4, kind, s));
-    if (e->B_on_device) CU_TRY(e, cudaMemcpyAsync(e->d_B32, e->B_on_device, static_cast<size_t>(N * K) * 4, cudaMemcpyDeviceToDevice, s));
-    else CU_TRY(e, cudaMemcpyAsync(e->d_B32, B, static_cast<size_t>(N * K) * 4, kind, s));
-    CU_TRY(e, cudaEventRecord(e->ev_h2d, s));
-    if (e->on_copies_enqueued) e->on_copies_enqueued(e->on_copies_user);
-    st = convert_storage(e);
-    if (st) return st;
-    st = build_plan(e, item_nnz, n_items);
-    if (st) return st;
     e->uploaded = true;
     return SDDMM_B200_OK;
 }
