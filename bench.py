@@ -471,7 +471,22 @@ def main():
             tp.append(time.perf_counter() - t0)
         t_pipe = float(np.mean(tp))
         pipe_chunks = pipe.last_chunks()
+        # ... and when the pattern stays: only the numbers travel, chunk by chunk
+        def pipe_reuse_step():
+            pipe.update_csr_raw(h_sv, h_A, h_B, h_P)
+        pipe_reuse_step()
+        barrier()
+        tpr = []
+        for _ in range(n_e2e):
+            t0 = time.perf_counter()
+            pipe_reuse_step()
+            tpr.append(time.perf_counter() - t0)
+        t_pipe_reuse = float(np.mean(tpr))
         pipe.close()
+        if dist is not None:
+            tt = torch.tensor([t_pipe_reuse], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t_pipe_reuse = float(tt.item())
         if dist is not None:
             tt = torch.tensor([t_pipe], dtype=torch.float64, device="cuda")
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -483,9 +498,12 @@ def main():
                        "in nnz-balanced row chunks whose three phases overlap; per rank bytes",
                "single_engine": {"value": flops / t_e2e / 1e9, "unit": "GFLOP/s", "ms_per_step": t_e2e * 1e3,
                                  "what": "upload_csr + run + download on one engine, one phase after the other"},
-               "pattern_reuse": {"value": flops / t_reuse / 1e9, "unit": "GFLOP/s", "ms_per_step": t_reuse * 1e3,
+               "pattern_reuse": {"value": flops / t_pipe_reuse / 1e9, "unit": "GFLOP/s", "ms_per_step": t_pipe_reuse * 1e3,
                                  "h2d_bytes_per_step": int(4 * nnz_loc + 4 * K * (Mloc + d.N)), "d2h_bytes_per_step": int(4 * nnz_loc),
-                                 "what": "update_dense + update_values (pinned host A, B, S.val -> HBM; pattern and plan kept) + run + download"}}
+                                 "what": "sddmm_b200_pipeline_update_csr (pinned host A, B, S.val -> HBM; pattern and plans kept; run; "
+                                         "P.val -> pinned host; row chunks overlapped)",
+                                 "single_engine": {"value": flops / t_reuse / 1e9, "unit": "GFLOP/s", "ms_per_step": t_reuse * 1e3,
+                                                   "what": "update_dense + update_values + run + download on one engine"}}}
         eng.nnz = nnz_loc
 
     # ---- roofline of the dominant kernel (this rank's shard) -------------------------------------

@@ -38,6 +38,7 @@ ENGINE_SYMBOLS = [
     "sddmm_b200_host_free", "sddmm_b200_sddmm_csr_prealloc", "sddmm_b200_set_kernel_timing",
     "sddmm_b200_pipeline_create", "sddmm_b200_pipeline_destroy", "sddmm_b200_pipeline_sddmm_csr",
     "sddmm_b200_pipeline_last_chunks", "sddmm_b200_pipeline_last_error", "sddmm_b200_pipeline_set_min_chunk_bytes",
+    "sddmm_b200_pipeline_update_csr",
 ]
 DATASET_SYMBOLS = [
     "sddmm_dataset_create", "sddmm_dataset_create_uniform", "sddmm_dataset_destroy", "sddmm_dataset_dims",
@@ -126,6 +127,7 @@ def load_engine_lib() -> C.CDLL:
     lib.sddmm_b200_pipeline_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_uint32, C.c_int]
     lib.sddmm_b200_pipeline_destroy.argtypes = [H]
     lib.sddmm_b200_pipeline_sddmm_csr.argtypes = [H, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 6
+    lib.sddmm_b200_pipeline_update_csr.argtypes = [H] + [C.c_void_p] * 4
     lib.sddmm_b200_pipeline_last_chunks.argtypes = [H]
     lib.sddmm_b200_pipeline_set_min_chunk_bytes.argtypes = [H, C.c_int64]
     lib.sddmm_b200_pipeline_last_error.argtypes = [H]
@@ -361,6 +363,12 @@ class Pipeline:
         out = np.empty(int(row_ptr[M]) if row_ptr[M] > 0 else 0, dtype=np.float32)
         self.sddmm_csr_raw(M, N, K, row_ptr, col_idx, s_val, A, B, out)
         return out
+
+    def update_csr_raw(self, s_val, A, B, p_val):
+        """New S.val, A, B for the pattern of the last sddmm_csr call; host arrays or addresses, result into p_val."""
+        st = self.lib.sddmm_b200_pipeline_update_csr(self.h, _ptr(s_val), _ptr(A), _ptr(B), _ptr(p_val))
+        if st:
+            raise SddmmError(st, "pipeline_update_csr", self.lib.sddmm_b200_pipeline_last_error(self.h).decode())
 
     def last_chunks(self) -> int:
         return int(self.lib.sddmm_b200_pipeline_last_chunks(self.h))

@@ -25,6 +25,9 @@ struct sddmm_b200_pipeline {
     std::vector<int32_t *> h_rp;        // pinned staging of every chunk's rebased row_ptr
     std::vector<int64_t> h_rp_cap;      // ... and its capacity in elements
     std::vector<int64_t> cuts;          // first row of every chunk of the last call (chunks + 1)
+    std::vector<int64_t> offsets;       // ... and its first nonzero
+    int64_t K = 0;
+    bool ready = false;                 // the last sddmm_csr call succeeded: its pattern and plans are in the engines
     int last_chunks = 0;
     int64_t min_chunk_bytes = int64_t(64) << 20;   // a chunk costs a plan (a handful of stream round trips): not below this much traffic each
     std::string err;
@@ -122,6 +125,7 @@ int sddmm_b200_pipeline_sddmm_csr(sddmm_b200_pipeline *p, int64_t M, int64_t N, 
     if (!p) return SDDMM_B200_ERR_ARG;
     p->err.clear();
     p->last_chunks = 0;
+    p->ready = false;
     auto bad = [&](int code, const char *msg) {
         p->err = msg;
         return code;
@@ -216,7 +220,67 @@ int sddmm_b200_pipeline_sddmm_csr(sddmm_b200_pipeline *p, int64_t M, int64_t N, 
                  "): " + sddmm_b200_last_error(p->engines[static_cast<size_t>(c)]);
         return status[static_cast<size_t>(c)];
     }
+    p->offsets.assign(static_cast<size_t>(chunks) + 1, 0);
+    for (int c = 0; c <= chunks; ++c) p->offsets[static_cast<size_t>(c)] = row_ptr[p->cuts[static_cast<size_t>(c)]];
+    p->K = K;
+    p->ready = true;
     return SDDMM_B200_OK;
+}
+
+// Same pattern, new numbers: nothing here blocks, so one host thread enqueues every chunk (copies chained as above,
+// conversion, kernels, copy-back) and then waits for all of them.
+int sddmm_b200_pipeline_update_csr(sddmm_b200_pipeline *p, const float *s_val, const float *A, const float *B, float *p_val) {
+    if (!p) return SDDMM_B200_ERR_ARG;
+    p->err.clear();
+    auto bad = [&](int code, const std::string &msg) {
+        p->err = msg;
+        return code;
+    };
+    if (!p->ready) return bad(SDDMM_B200_ERR_STATE, "update before a successful sddmm_csr call");
+    if (!A || !B) return bad(SDDMM_B200_ERR_ARG, "null pointer argument");
+    const int chunks = p->last_chunks;
+    if (p->offsets[static_cast<size_t>(chunks)] > 0 && (!s_val || !p_val)) return bad(SDDMM_B200_ERR_ARG, "null pointer argument");
+    DeviceGuard g(p->device);
+    if (!g.ok) return bad(SDDMM_B200_ERR_CUDA, "cannot select the device");
+    const int64_t K = p->K;
+    cudaEvent_t prev = nullptr;
+    const float *b_src = nullptr;
+    int st = SDDMM_B200_OK;
+    for (int c = 0; c < chunks && st == SDDMM_B200_OK; ++c) {
+        const int64_t r0 = p->cuts[static_cast<size_t>(c)], r1 = p->cuts[static_cast<size_t>(c) + 1], off = p->offsets[static_cast<size_t>(c)];
+        if (r1 == r0) continue;
+        sddmm_b200_engine *e = p->engines[static_cast<size_t>(c)];
+        cudaStream_t s = e->stream;
+        bool ok = true;
+        if (prev) ok = ok && cudaStreamWaitEvent(s, prev, 0) == cudaSuccess;
+        if (e->nnz) ok = ok && cudaMemcpyAsync(e->d_sval, s_val + off, static_cast<size_t>(e->nnz) * 4, cudaMemcpyHostToDevice, s) == cudaSuccess;
+        ok = ok && cudaMemcpyAsync(e->d_A32, A + r0 * K, static_cast<size_t>((r1 - r0) * K) * 4, cudaMemcpyHostToDevice, s) == cudaSuccess;
+        ok = ok && cudaMemcpyAsync(e->d_B32, b_src ? b_src : B, static_cast<size_t>(e->N * K) * 4,
+                                   b_src ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, s) == cudaSuccess;
+        ok = ok && cudaEventRecord(e->ev_h2d, s) == cudaSuccess;
+        prev = e->ev_h2d;
+        if (!b_src) b_src = e->d_B32;
+        if (!ok) {
+            st = bad(SDDMM_B200_ERR_CUDA, std::string("copy failed: ") + cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        st = convert_storage(e);
+        if (st == SDDMM_B200_OK) st = sddmm_b200_run(e);
+        if (st == SDDMM_B200_OK && e->nnz &&
+            cudaMemcpyAsync(p_val + off, e->d_pval, static_cast<size_t>(e->nnz) * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+            st = SDDMM_B200_ERR_CUDA;
+        if (st != SDDMM_B200_OK) p->err = sddmm_b200_last_error(e);
+    }
+    for (int c = 0; c < chunks; ++c) {   // always drain every chunk: the caller's buffers are free again when this returns
+        if (p->cuts[static_cast<size_t>(c) + 1] == p->cuts[static_cast<size_t>(c)]) continue;
+        sddmm_b200_engine *e = p->engines[static_cast<size_t>(c)];
+        const int sc = sddmm_b200_sync(e);
+        if (sc != SDDMM_B200_OK && st == SDDMM_B200_OK) {
+            st = sc;
+            p->err = sddmm_b200_last_error(e);
+        }
+    }
+    return st;
 }
 
 }  // extern "C"

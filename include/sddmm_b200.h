@@ -198,6 +198,11 @@ int sddmm_b200_pipeline_destroy(sddmm_b200_pipeline *p);
 int sddmm_b200_pipeline_sddmm_csr(sddmm_b200_pipeline *p, int64_t M, int64_t N, int64_t K, const int32_t *row_ptr,
                                   const int32_t *col_idx, const float *s_val, const float *A, const float *B,
                                   float *p_val /* nnz, out */);
+/* The pattern of the last successful sddmm_b200_pipeline_sddmm_csr call with new S.val, A and B (iterative
+ * callers: no counterpart in the reference, which re-uploads everything): only the numbers cross the link,
+ * plans are kept, ranges overlap in the same way.  SDDMM_B200_ERR_STATE without such a call. */
+int sddmm_b200_pipeline_update_csr(sddmm_b200_pipeline *p, const float *s_val, const float *A, const float *B,
+                                   float *p_val /* nnz, out */);
 int sddmm_b200_pipeline_last_chunks(sddmm_b200_pipeline *p); /* ranges the last call used */
 int sddmm_b200_pipeline_set_min_chunk_bytes(sddmm_b200_pipeline *p, int64_t bytes);
 const char *sddmm_b200_pipeline_last_error(sddmm_b200_pipeline *p);

@@ -353,6 +353,12 @@ def test_pipeline_matches_oracle_and_engine(engines, oracle, cfg, scale, K, mode
         p = pl.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
         assert 1 < pl.last_chunks() <= chunks
         p_again = pl.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)   # the object is reusable
+        # same pattern, new numbers: only S.val, A, B travel, the plans stay
+        rng = np.random.default_rng(11)
+        sv2 = rng.uniform(-1, 1, d.s_val.size).astype(np.float32)
+        A2, B2 = rng.uniform(-1, 1, (d.M, K)).astype(np.float32), rng.uniform(-1, 1, (d.N, K)).astype(np.float32)
+        p2 = np.full(d.s_val.size, np.nan, np.float32)
+        pl.update_csr_raw(sv2, A2, B2, p2)
     np.testing.assert_array_equal(p, p_again)
     p_ref = oracle.sddmm_csr(d.M, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
     rows = oracle.coo_rows(d.M, d.row_ptr)
@@ -360,11 +366,16 @@ def test_pipeline_matches_oracle_and_engine(engines, oracle, cfg, scale, K, mode
     oracle_lib.assert_values_close(p, p_ref, bound, TOL[mode], f"pipeline {mode} cfg{cfg}")
     p_one = engines[mode].sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
     oracle_lib.assert_values_close(p, p_one, bound, 2 * TOL[mode], f"pipeline vs one engine {mode} cfg{cfg}")
+    p2_ref = oracle.sddmm_csr(d.M, K, d.row_ptr, d.col_idx, sv2, A2, B2)
+    oracle_lib.assert_values_close(p2, p2_ref, oracle_lib.abs_dot_bound(rows, d.col_idx, sv2, A2, B2), TOL[mode], f"pipeline update {mode} cfg{cfg}")
 
 
 def test_pipeline_edges(oracle):
     rng = np.random.default_rng(7)
     with Pipeline(0, "fp32", chunks=4, min_chunk_bytes=4 << 20) as pl:
+        with pytest.raises(SddmmError) as ei:   # no pattern yet
+            pl.update_csr_raw(np.ones(3, np.float32), np.ones((3, 4), np.float32), np.ones((3, 4), np.float32), np.zeros(3, np.float32))
+        assert ei.value.code == 5
         # small input: one range; golden-sized case exact
         A = np.ones((3, 4), np.float32)
         assert pl.sddmm_csr(3, 3, 4, [0, 1, 2, 3], [0, 1, 2], [1, 1, 1], A, A).tolist() == [4.0, 4.0, 4.0]
@@ -395,6 +406,12 @@ def test_pipeline_edges(oracle):
         with pytest.raises(SddmmError) as ei:
             pl.sddmm_csr(M, N, K, rp, ci_bad, sv, A, B)
         assert ei.value.code == 2
+        with pytest.raises(SddmmError) as ei:   # the failed call left no usable pattern
+            pl.update_csr_raw(sv, A, B, np.zeros(ci.size, np.float32))
+        assert ei.value.code == 5
         np.testing.assert_array_equal(pl.sddmm_csr(M, N, K, rp, ci, sv, A, B), p)
+        p_up = np.zeros(ci.size, np.float32)
+        pl.update_csr_raw(sv, 2 * A, B, p_up)   # ranges without rows or nonzeros are skipped here too
+        oracle_lib.assert_values_close(p_up, 2 * p_ref, 2 * bound, 1e-5, "pipeline ragged update")
     with pytest.raises(SddmmError):
         Pipeline(0, "fp32", chunks=0)
