@@ -38,7 +38,7 @@ ENGINE_SYMBOLS = [
     "sddmm_b200_host_free", "sddmm_b200_sddmm_csr_prealloc", "sddmm_b200_set_kernel_timing",
     "sddmm_b200_pipeline_create", "sddmm_b200_pipeline_destroy", "sddmm_b200_pipeline_sddmm_csr",
     "sddmm_b200_pipeline_last_chunks", "sddmm_b200_pipeline_last_error", "sddmm_b200_pipeline_set_min_chunk_bytes",
-    "sddmm_b200_pipeline_update_csr",
+    "sddmm_b200_pipeline_update_csr", "sddmm_b200_pipeline_sddmm_coo",
 ]
 DATASET_SYMBOLS = [
     "sddmm_dataset_create", "sddmm_dataset_create_uniform", "sddmm_dataset_destroy", "sddmm_dataset_dims",
@@ -127,6 +127,7 @@ def load_engine_lib() -> C.CDLL:
     lib.sddmm_b200_pipeline_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_uint32, C.c_int]
     lib.sddmm_b200_pipeline_destroy.argtypes = [H]
     lib.sddmm_b200_pipeline_sddmm_csr.argtypes = [H, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 6
+    lib.sddmm_b200_pipeline_sddmm_coo.argtypes = [H, C.c_int64, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 6
     lib.sddmm_b200_pipeline_update_csr.argtypes = [H] + [C.c_void_p] * 4
     lib.sddmm_b200_pipeline_last_chunks.argtypes = [H]
     lib.sddmm_b200_pipeline_set_min_chunk_bytes.argtypes = [H, C.c_int64]
@@ -362,6 +363,17 @@ class Pipeline:
         assert row_ptr.size == M + 1 and A.size == M * K and B.size == N * K
         out = np.empty(int(row_ptr[M]) if row_ptr[M] > 0 else 0, dtype=np.float32)
         self.sddmm_csr_raw(M, N, K, row_ptr, col_idx, s_val, A, B, out)
+        return out
+
+    def sddmm_coo(self, M, N, K, row_idx, col_idx, s_val, A, B) -> np.ndarray:
+        row_idx, col_idx = _as(row_idx, np.int32), _as(col_idx, np.int32)
+        s_val, A, B = _as(s_val, np.float32), _as(A, np.float32), _as(B, np.float32)
+        assert row_idx.size == col_idx.size == s_val.size and A.size == M * K and B.size == N * K
+        out = np.empty(row_idx.size, dtype=np.float32)
+        st = self.lib.sddmm_b200_pipeline_sddmm_coo(self.h, M, N, K, row_idx.size, _ptr(row_idx), _ptr(col_idx), _ptr(s_val), _ptr(A),
+                                                    _ptr(B), _ptr(out))
+        if st:
+            raise SddmmError(st, "pipeline_sddmm_coo", self.lib.sddmm_b200_pipeline_last_error(self.h).decode())
         return out
 
     def update_csr_raw(self, s_val, A, B, p_val):

@@ -63,6 +63,7 @@ struct sddmm_b200_engine {
     const float *B_on_device = nullptr;           // B already in this GPU's memory (another engine's copy): taken from there
     void (*on_copies_enqueued)(void *) = nullptr; // called once ev_h2d is recorded
     void *on_copies_user = nullptr;
+    int32_t coo_row_base = 0;                     // COO upload of a row slice of a larger matrix: first row of the slice
     const char *kernel_name[kMaxKernels] = {nullptr, nullptr, nullptr, nullptr};
     int kernels_launched = 0;
     bool kernel_timing = false;    // record an event pair around every kernel (sddmm_b200_set_kernel_timing)
@@ -461,7 +462,7 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
     CU_TRY(e, cudaMemsetAsync(e->d_rowstart, 0, (static_cast<size_t>(e->nnz) / 32 + 2) * 4, s));
     if (e->d_coo_rows) {
         k_coo_to_row_ptr<<<grid_for(e->nnz + 1, kBlock, cap), kBlock, 0, s>>>(e->d_coo_rows, e->nnz, static_cast<int32_t>(e->M),
-                                                                              e->d_rp, e->d_pc);
+                                                                              e->coo_row_base, e->d_rp, e->d_pc);
         // refuse to interpret a row_ptr built from unsorted rows
         PlanCounters pc0;
         if (int rc = read_counters(e, &pc0)) return rc;

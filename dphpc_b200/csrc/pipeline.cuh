@@ -74,6 +74,81 @@ std::vector<int64_t> chunk_cuts(const int32_t *row_ptr, int64_t M, int chunks) {
 
 }  // namespace
 
+namespace {
+
+// Chunks of the current call are in p->cuts (rows) and p->offsets (nonzeros): run them, one host thread each.
+// CSR: row_ptr given (rebased per chunk into pinned staging); COO: row_idx given (rebased on the device).
+int run_chunks(sddmm_b200_pipeline *p, int chunks, int64_t N, int64_t K, const int32_t *row_ptr, const int32_t *row_idx,
+               const int32_t *col_idx, const float *s_val, const float *A, const float *B, float *p_val) {
+    std::atomic<int> enqueued{0};
+    std::atomic<const float *> b_src{nullptr};
+    std::atomic<cudaEvent_t> last_copy{nullptr};
+    std::vector<int> status(static_cast<size_t>(chunks), SDDMM_B200_OK);
+    std::vector<ChunkSignal> signals(static_cast<size_t>(chunks));
+    static const bool trace = std::getenv("SDDMM_B200_PIPELINE_TRACE") != nullptr;   // debugging knob: host times of every phase
+    const auto t_start = std::chrono::steady_clock::now();
+    auto since = [&]() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_start).count(); };
+    auto work = [&](int c) {
+        sddmm_b200_engine *e = p->engines[static_cast<size_t>(c)];
+        double t_go = 0, t_up = 0, t_run = 0;
+        ChunkSignal &sig = signals[static_cast<size_t>(c)];
+        sig = ChunkSignal{&enqueued, &b_src, &last_copy, e, c, false};
+        const int64_t r0 = p->cuts[static_cast<size_t>(c)], r1 = p->cuts[static_cast<size_t>(c) + 1];
+        const int64_t off = p->offsets[static_cast<size_t>(c)], n = p->offsets[static_cast<size_t>(c) + 1] - off;
+        int32_t *local = row_ptr ? p->h_rp[static_cast<size_t>(c)] : nullptr;
+        if (row_ptr)
+            for (int64_t i = r0; i <= r1; ++i) local[i - r0] = static_cast<int32_t>(row_ptr[i] - off);
+        while (enqueued.load(std::memory_order_acquire) < c) std::this_thread::yield();   // every earlier chunk signals, also when it fails
+        int st = SDDMM_B200_OK;
+        t_go = since();
+        if (r1 > r0) {
+            e->h2d_after = last_copy.load();   // null for the first chunk that copies
+            e->B_on_device = b_src.load();
+            e->on_copies_enqueued = chunk_copies_enqueued;
+            e->on_copies_user = &sig;
+            if (row_ptr) {
+                st = sddmm_b200_upload_csr(e, r1 - r0, N, K, local, col_idx + off, s_val + off, A + r0 * K, B);
+            } else {
+                e->coo_row_base = static_cast<int32_t>(r0);
+                st = sddmm_b200_upload_coo(e, r1 - r0, N, K, n, row_idx + off, col_idx + off, s_val + off, A + r0 * K, B);
+                e->coo_row_base = 0;
+            }
+            e->h2d_after = nullptr;
+            e->B_on_device = nullptr;
+            e->on_copies_enqueued = nullptr;
+        }
+        if (!sig.fired) {   // empty chunk, or the upload gave up before its copies: let the next chunk go
+            sig.fired = true;
+            enqueued.store(c + 1, std::memory_order_release);
+        }
+        t_up = since();
+        if (r1 > r0 && st == SDDMM_B200_OK) st = sddmm_b200_run(e);
+        t_run = since();
+        if (r1 > r0 && st == SDDMM_B200_OK) st = sddmm_b200_download(e, p_val + off);
+        status[static_cast<size_t>(c)] = st;
+        if (trace) std::fprintf(stderr, "[pipeline] chunk %d rows [%lld, %lld): go %.3f  uploaded+planned %.3f  launched %.3f  downloaded %.3f ms\n", c,
+                                static_cast<long long>(r0), static_cast<long long>(r1), t_go, t_up, t_run, since());
+    };
+    {
+        std::vector<std::thread> threads;
+        for (int c = 1; c < chunks; ++c) threads.emplace_back(work, c);
+        work(0);
+        for (std::thread &t : threads) t.join();
+    }
+    p->last_chunks = chunks;
+    for (int c = 0; c < chunks; ++c) {
+        if (status[static_cast<size_t>(c)] == SDDMM_B200_OK) continue;
+        p->err = "rows [" + std::to_string(p->cuts[static_cast<size_t>(c)]) + ", " + std::to_string(p->cuts[static_cast<size_t>(c) + 1]) +
+                 "): " + sddmm_b200_last_error(p->engines[static_cast<size_t>(c)]);
+        return status[static_cast<size_t>(c)];
+    }
+    p->K = K;
+    p->ready = true;
+    return SDDMM_B200_OK;
+}
+
+}  // namespace
+
 extern "C" {
 
 int sddmm_b200_pipeline_create(sddmm_b200_pipeline **out, int device, int mode, uint32_t flags, int chunks) {
@@ -146,6 +221,8 @@ int sddmm_b200_pipeline_sddmm_csr(sddmm_b200_pipeline *p, int64_t M, int64_t N, 
         const int64_t prev = c ? row_ptr[p->cuts[static_cast<size_t>(c) - 1]] : 0;
         if (at < prev || at > nnz || (c == 0 && at != 0)) return bad(SDDMM_B200_ERR_INDEX, "row_ptr is not monotone from 0");
     }
+    p->offsets.assign(static_cast<size_t>(chunks) + 1, 0);
+    for (int c = 0; c <= chunks; ++c) p->offsets[static_cast<size_t>(c)] = row_ptr[p->cuts[static_cast<size_t>(c)]];
     {   // pinned staging for the rebased row_ptr of every chunk (grows, never shrinks)
         DeviceGuard g(p->device);
         if (!g.ok) return bad(SDDMM_B200_ERR_CUDA, "cannot select the device");
@@ -164,67 +241,45 @@ int sddmm_b200_pipeline_sddmm_csr(sddmm_b200_pipeline *p, int64_t M, int64_t N, 
             p->h_rp_cap[static_cast<size_t>(c)] = need;
         }
     }
+    return run_chunks(p, chunks, N, K, row_ptr, nullptr, col_idx, s_val, A, B, p_val);
+}
 
-    std::atomic<int> enqueued{0};
-    std::atomic<const float *> b_src{nullptr};
-    std::atomic<cudaEvent_t> last_copy{nullptr};
-    std::vector<int> status(static_cast<size_t>(chunks), SDDMM_B200_OK);
-    std::vector<ChunkSignal> signals(static_cast<size_t>(chunks));
-    static const bool trace = std::getenv("SDDMM_B200_PIPELINE_TRACE") != nullptr;   // debugging knob: host times of every phase
-    const auto t_start = std::chrono::steady_clock::now();
-    auto since = [&]() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_start).count(); };
-    auto work = [&](int c) {
-        sddmm_b200_engine *e = p->engines[static_cast<size_t>(c)];
-        double t_go = 0, t_up = 0, t_run = 0;
-        ChunkSignal &sig = signals[static_cast<size_t>(c)];
-        sig = ChunkSignal{&enqueued, &b_src, &last_copy, e, c, false};
-        const int64_t r0 = p->cuts[static_cast<size_t>(c)], r1 = p->cuts[static_cast<size_t>(c) + 1];
-        const int64_t off = row_ptr[r0];
-        int32_t *local = p->h_rp[static_cast<size_t>(c)];
-        for (int64_t i = r0; i <= r1; ++i) local[i - r0] = static_cast<int32_t>(row_ptr[i] - off);
-        while (enqueued.load(std::memory_order_acquire) < c) std::this_thread::yield();   // every earlier chunk signals, also when it fails
-        int st = SDDMM_B200_OK;
-        t_go = since();
-        if (r1 > r0) {
-            e->h2d_after = last_copy.load();   // null for the first chunk that copies
-            e->B_on_device = b_src.load();
-            e->on_copies_enqueued = chunk_copies_enqueued;
-            e->on_copies_user = &sig;
-            st = sddmm_b200_upload_csr(e, r1 - r0, N, K, local, col_idx + off, s_val + off, A + r0 * K, B);
-            e->h2d_after = nullptr;
-            e->B_on_device = nullptr;
-            e->on_copies_enqueued = nullptr;
-        }
-        if (!sig.fired) {   // empty chunk, or the upload gave up before its copies: let the next chunk go
-            sig.fired = true;
-            enqueued.store(c + 1, std::memory_order_release);
-        }
-        t_up = since();
-        if (r1 > r0 && st == SDDMM_B200_OK) st = sddmm_b200_run(e);
-        t_run = since();
-        if (r1 > r0 && st == SDDMM_B200_OK) st = sddmm_b200_download(e, p_val + off);
-        status[static_cast<size_t>(c)] = st;
-        if (trace) std::fprintf(stderr, "[pipeline] chunk %d rows [%lld, %lld): go %.3f  uploaded+planned %.3f  launched %.3f  downloaded %.3f ms\n", c,
-                                static_cast<long long>(r0), static_cast<long long>(r1), t_go, t_up, t_run, since());
+// COO, rows sorted as the reference's COO<T> keeps them (src/matrices/COO.hpp:39).  The cuts are found by binary search in
+// row_idx; every chunk's slice is validated on the device against its own row range, which together proves the global order.
+int sddmm_b200_pipeline_sddmm_coo(sddmm_b200_pipeline *p, int64_t M, int64_t N, int64_t K, int64_t nnz, const int32_t *row_idx,
+                                  const int32_t *col_idx, const float *s_val, const float *A, const float *B, float *p_val) {
+    if (!p) return SDDMM_B200_ERR_ARG;
+    p->err.clear();
+    p->last_chunks = 0;
+    p->ready = false;
+    auto bad = [&](int code, const char *msg) {
+        p->err = msg;
+        return code;
     };
-    {
-        std::vector<std::thread> threads;
-        for (int c = 1; c < chunks; ++c) threads.emplace_back(work, c);
-        work(0);
-        for (std::thread &t : threads) t.join();
-    }
-    p->last_chunks = chunks;
-    for (int c = 0; c < chunks; ++c) {
-        if (status[static_cast<size_t>(c)] == SDDMM_B200_OK) continue;
-        p->err = "rows [" + std::to_string(p->cuts[static_cast<size_t>(c)]) + ", " + std::to_string(p->cuts[static_cast<size_t>(c) + 1]) +
-                 "): " + sddmm_b200_last_error(p->engines[static_cast<size_t>(c)]);
-        return status[static_cast<size_t>(c)];
-    }
+    if (!A || !B) return bad(SDDMM_B200_ERR_ARG, "null pointer argument");
+    if (M < 1 || N < 1 || K < 1 || nnz < 0) return bad(SDDMM_B200_ERR_ARG, "need M, N, K >= 1 and nnz >= 0");
+    if (M >= (int64_t(1) << 31) - 1) return bad(SDDMM_B200_ERR_ARG, "int32 index range exceeded");
+    if (nnz > 0 && (!row_idx || !col_idx || !s_val || !p_val)) return bad(SDDMM_B200_ERR_ARG, "null pointer argument");
+    const int64_t bytes = nnz * 16 + (M + N) * K * 4;
+    const int chunks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(p->engines.size()), bytes / p->min_chunk_bytes)));
+    const int64_t align = M >= int64_t(64) * 8 * chunks ? 64 : 1;
+    p->cuts.assign(static_cast<size_t>(chunks) + 1, 0);
     p->offsets.assign(static_cast<size_t>(chunks) + 1, 0);
-    for (int c = 0; c <= chunks; ++c) p->offsets[static_cast<size_t>(c)] = row_ptr[p->cuts[static_cast<size_t>(c)]];
-    p->K = K;
-    p->ready = true;
-    return SDDMM_B200_OK;
+    p->cuts[static_cast<size_t>(chunks)] = M;
+    p->offsets[static_cast<size_t>(chunks)] = nnz;
+    for (int c = 1; c < chunks; ++c) {
+        int64_t r = nnz ? row_idx[std::min<int64_t>(nnz - 1, nnz * c / chunks)] : 0;   // the row holding the chunk's first nonzero ...
+        if (r < 0 || r >= M) return bad(SDDMM_B200_ERR_INDEX, "COO row indices must be sorted and inside [0, M)");
+        if (align > 1) r = std::min<int64_t>((r + align / 2) / align * align, M);
+        r = std::max<int64_t>(r, p->cuts[static_cast<size_t>(c) - 1]);
+        const int64_t pos = std::lower_bound(row_idx, row_idx + nnz, static_cast<int32_t>(r)) - row_idx;   // ... taken whole
+        p->cuts[static_cast<size_t>(c)] = r;
+        p->offsets[static_cast<size_t>(c)] = std::max<int64_t>(pos, p->offsets[static_cast<size_t>(c) - 1]);
+    }
+    for (int c = 0; c < chunks; ++c)   // nonzeros in a chunk without rows: the rows cannot be sorted
+        if (p->cuts[static_cast<size_t>(c) + 1] == p->cuts[static_cast<size_t>(c)] && p->offsets[static_cast<size_t>(c) + 1] != p->offsets[static_cast<size_t>(c)])
+            return bad(SDDMM_B200_ERR_INDEX, "COO row indices must be sorted and inside [0, M)");
+    return run_chunks(p, chunks, N, K, nullptr, row_idx, col_idx, s_val, A, B, p_val);
 }
 
 // Same pattern, new numbers: nothing here blocks, so one host thread enqueues every chunk (copies chained as above,

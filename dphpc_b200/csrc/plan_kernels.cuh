@@ -100,18 +100,19 @@ __global__ void k_count_bytes(const unsigned char *__restrict__ flags, int64_t n
     if ((threadIdx.x & 31) == 0 && local) atomicAdd(out, (unsigned long long)local);
 }
 
-// COO (sorted by row) -> row_ptr.  Thread j owns the rows in (row[j-1], row[j]].
-__global__ void k_coo_to_row_ptr(const int32_t *__restrict__ row, int64_t nnz, int32_t M, int32_t *__restrict__ rp,
+// COO (sorted by row) -> row_ptr.  Thread j owns the rows in (row[j-1], row[j]].  `base` is subtracted from every row index
+// (a slice of a larger matrix that starts at row `base`).
+__global__ void k_coo_to_row_ptr(const int32_t *__restrict__ row, int64_t nnz, int32_t M, int32_t base, int32_t *__restrict__ rp,
                                  PlanCounters *__restrict__ pc) {
     for (int64_t j = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; j <= nnz;
          j += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int prev = (j == 0) ? -1 : row[j - 1];
-        const int cur = (j == nnz) ? M : row[j];
+        const int64_t prev = (j == 0) ? -1 : static_cast<int64_t>(row[j - 1]) - base;
+        const int64_t cur = (j == nnz) ? M : static_cast<int64_t>(row[j]) - base;
         if (prev < -1 || prev >= M || cur < 0 || cur > M || (j < nnz && cur >= M) || cur < prev) {
             pc->bad_coo = 1;
             continue;
         }
-        for (int r = prev + 1; r <= cur; ++r) rp[r] = static_cast<int32_t>(j);
+        for (int64_t r = prev + 1; r <= cur; ++r) rp[r] = static_cast<int32_t>(j);
     }
 }
 

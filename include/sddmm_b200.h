@@ -198,7 +198,13 @@ int sddmm_b200_pipeline_destroy(sddmm_b200_pipeline *p);
 int sddmm_b200_pipeline_sddmm_csr(sddmm_b200_pipeline *p, int64_t M, int64_t N, int64_t K, const int32_t *row_ptr,
                                   const int32_t *col_idx, const float *s_val, const float *A, const float *B,
                                   float *p_val /* nnz, out */);
-/* The pattern of the last successful sddmm_b200_pipeline_sddmm_csr call with new S.val, A and B (iterative
+/* COO form (Competitor<T>::init_coo / run_coo / cleanup_coo, src/benchmark/competitor.hpp:28-34): rows sorted as COO<T>
+ * keeps them (src/matrices/COO.hpp:39), otherwise SDDMM_B200_ERR_INDEX.  The row indices are not rewritten on the host:
+ * every range is re-based on the device. */
+int sddmm_b200_pipeline_sddmm_coo(sddmm_b200_pipeline *p, int64_t M, int64_t N, int64_t K, int64_t nnz, const int32_t *row_idx,
+                                  const int32_t *col_idx, const float *s_val, const float *A, const float *B,
+                                  float *p_val /* nnz, out */);
+/* The pattern of the last successful sddmm_b200_pipeline_sddmm_csr / _coo call with new S.val, A and B (iterative
  * callers: no counterpart in the reference, which re-uploads everything): only the numbers cross the link,
  * plans are kept, ranges overlap in the same way.  SDDMM_B200_ERR_STATE without such a call. */
 int sddmm_b200_pipeline_update_csr(sddmm_b200_pipeline *p, const float *s_val, const float *A, const float *B,

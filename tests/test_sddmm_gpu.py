@@ -353,6 +353,8 @@ def test_pipeline_matches_oracle_and_engine(engines, oracle, cfg, scale, K, mode
         p = pl.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
         assert 1 < pl.last_chunks() <= chunks
         p_again = pl.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)   # the object is reusable
+        p_coo = pl.sddmm_coo(d.M, d.N, d.K, oracle.coo_rows(d.M, d.row_ptr), d.col_idx, d.s_val, d.A, d.B)
+        assert 1 < pl.last_chunks() <= chunks
         # same pattern, new numbers: only S.val, A, B travel, the plans stay
         rng = np.random.default_rng(11)
         sv2 = rng.uniform(-1, 1, d.s_val.size).astype(np.float32)
@@ -364,6 +366,7 @@ def test_pipeline_matches_oracle_and_engine(engines, oracle, cfg, scale, K, mode
     rows = oracle.coo_rows(d.M, d.row_ptr)
     bound = oracle_lib.abs_dot_bound(rows, d.col_idx, d.s_val, d.A, d.B)
     oracle_lib.assert_values_close(p, p_ref, bound, TOL[mode], f"pipeline {mode} cfg{cfg}")
+    oracle_lib.assert_values_close(p_coo, p_ref, bound, TOL[mode], f"pipeline coo {mode} cfg{cfg}")   # (its cuts may differ by a row)
     p_one = engines[mode].sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
     oracle_lib.assert_values_close(p, p_one, bound, 2 * TOL[mode], f"pipeline vs one engine {mode} cfg{cfg}")
     p2_ref = oracle.sddmm_csr(d.M, K, d.row_ptr, d.col_idx, sv2, A2, B2)
@@ -405,6 +408,18 @@ def test_pipeline_edges(oracle):
         ci_bad[-1] = N
         with pytest.raises(SddmmError) as ei:
             pl.sddmm_csr(M, N, K, rp, ci_bad, sv, A, B)
+        assert ei.value.code == 2
+        rows = oracle.coo_rows(M, rp)
+        oracle_lib.assert_values_close(pl.sddmm_coo(M, N, K, rows, ci, sv, A, B), p_ref, bound, 1e-5, "pipeline ragged coo")
+        rows_bad = rows.copy()
+        rows_bad[250000], rows_bad[250001] = rows_bad[-1], rows_bad[0]   # unsorted inside a chunk
+        with pytest.raises(SddmmError) as ei:
+            pl.sddmm_coo(M, N, K, rows_bad, ci, sv, A, B)
+        assert ei.value.code == 2
+        rows_bad = rows.copy()
+        rows_bad[-1] = M
+        with pytest.raises(SddmmError) as ei:
+            pl.sddmm_coo(M, N, K, rows_bad, ci, sv, A, B)
         assert ei.value.code == 2
         with pytest.raises(SddmmError) as ei:   # the failed call left no usable pattern
             pl.update_csr_raw(sv, A, B, np.zeros(ci.size, np.float32))
