@@ -578,6 +578,38 @@ def main():
                 dd.close()
         line["per_config"] = per
 
+    # ---- N > 1: the large configurations on the same row shards, kernel only (their N = 1 figures are in the N = 1 line) ----
+    if world > 1 and not args.no_extra and args.scale == 1.0:
+        per = {}
+        for c in (3, 4, 5):
+            ms_local, nnz_c, k_c = 1e30, 0, CONFIG_K[c]
+            try:
+                dd = d if c == cfg else Dataset(c, k_c, 1.0)
+                nnz_c = int(dd.nnz)
+                cc = row_cuts(dd.row_ptr, world, align=64 if dd.M >= 64 * 8 * world else 1)
+                a, b = int(cc[rank]), int(cc[rank + 1])
+                ja, jb = int(dd.row_ptr[a]), int(dd.row_ptr[b])
+                if b > a:
+                    e2 = Engine(local, "fp32")
+                    e2.upload_csr(b - a, dd.N, dd.K, (dd.row_ptr[a:b + 1].astype(np.int64) - ja).astype(np.int32), dd.col_idx[ja:jb],
+                                  dd.s_val[ja:jb], dd.A[a:b], dd.B)
+                    ms_local, _ = kernel_only_stats(e2, 10, 3, flush)
+                    e2.close()
+                else:
+                    ms_local = 0.0
+                if dd is not d:
+                    dd.close()
+            except Exception as ex:  # report, never hide (the collective below still runs on every rank)
+                sys.stderr.write(f"rank {rank}: config {c}: {ex}\n")
+            tt = torch.tensor([ms_local], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+            key = f"config{c}_k{k_c}_fp32"
+            per[key] = ({"error": "a rank failed (see stderr)"} if ms >= 1e29 else
+                        {"ms": ms, "gflops": 2.0 * nnz_c * k_c / ms / 1e6, "what": f"{world} nnz-balanced row shards, max over ranks"})
+        if rank == 0:
+            line["per_config"] = per
+
     if rank == 0:
         print(json.dumps(line), flush=True)
     eng.close()
