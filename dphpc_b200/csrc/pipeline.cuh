@@ -29,7 +29,7 @@ struct sddmm_b200_pipeline {
     int64_t K = 0;
     bool ready = false;                 // the last sddmm_csr call succeeded: its pattern and plans are in the engines
     int last_chunks = 0;
-    int64_t min_chunk_bytes = int64_t(64) << 20;   // a chunk costs a plan (a handful of stream round trips): not below this much traffic each
+    int64_t min_chunk_bytes = int64_t(64) << 20;   // a chunk costs a plan (a handful of stream round trips): about this much traffic each, or more
     std::string err;
 };
 
@@ -214,7 +214,7 @@ int sddmm_b200_pipeline_sddmm_csr(sddmm_b200_pipeline *p, int64_t M, int64_t N, 
 
     // small inputs: fewer chunks, down to one (nothing to overlap; every chunk costs a plan)
     const int64_t bytes = nnz * 12 + (M + N) * K * 4;
-    const int chunks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(p->engines.size()), bytes / p->min_chunk_bytes)));
+    const int chunks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(p->engines.size()), (bytes + p->min_chunk_bytes / 2) / p->min_chunk_bytes)));
     p->cuts = chunk_cuts(row_ptr, M, chunks);
     for (int c = 0; c <= chunks; ++c) {   // the cut rows index col_idx / s_val on the host: check them here, the rest on the device
         const int64_t at = row_ptr[p->cuts[static_cast<size_t>(c)]];
@@ -261,7 +261,7 @@ int sddmm_b200_pipeline_sddmm_coo(sddmm_b200_pipeline *p, int64_t M, int64_t N, 
     if (M >= (int64_t(1) << 31) - 1) return bad(SDDMM_B200_ERR_ARG, "int32 index range exceeded");
     if (nnz > 0 && (!row_idx || !col_idx || !s_val || !p_val)) return bad(SDDMM_B200_ERR_ARG, "null pointer argument");
     const int64_t bytes = nnz * 16 + (M + N) * K * 4;
-    const int chunks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(p->engines.size()), bytes / p->min_chunk_bytes)));
+    const int chunks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(p->engines.size()), (bytes + p->min_chunk_bytes / 2) / p->min_chunk_bytes)));
     const int64_t align = M >= int64_t(64) * 8 * chunks ? 64 : 1;
     p->cuts.assign(static_cast<size_t>(chunks) + 1, 0);
     p->offsets.assign(static_cast<size_t>(chunks) + 1, 0);

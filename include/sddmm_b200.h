@@ -187,9 +187,9 @@ int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int6
  * back, the next one's inputs are already crossing the (full-duplex) host link.  B crosses
  * the link once.  The result is the same as upload_csr + run + download on one engine
  * (every nonzero is computed by the same kernels; which rows reach the tensor-core tiles is
- * decided per range).  A range is not made smaller than 64 MB of host-link traffic (12 bytes
- * per nonzero + A + B; sddmm_b200_pipeline_set_min_chunk_bytes changes that), so small inputs
- * run as one range.  For full overlap the host buffers should be pinned
+ * decided per range).  The number of ranges is the host-link traffic (12 bytes per nonzero + A + B)
+ * divided by 64 MB, rounded, at most `chunks` (sddmm_b200_pipeline_set_min_chunk_bytes changes the
+ * 64 MB), so small inputs run as one range.  One call at a time per pipeline object.  For full overlap the host buffers should be pinned
  * (sddmm_b200_host_alloc); pageable buffers work, with less overlap.
  * Errors: the status codes above; sddmm_b200_pipeline_last_error names the row range. */
 typedef struct sddmm_b200_pipeline sddmm_b200_pipeline;
