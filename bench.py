@@ -16,7 +16,13 @@ total work is fixed).  Rank 0 prints one JSON line.
   e2e       same metric through the host-buffer call sddmm_b200_pipeline_sddmm_csr (pinned host
             buffers: H2D of S, A, B + device-side plan, run, D2H of P.val, overlapped over row
             chunks), host wall clock, max over ranks; e2e.single_engine = the same through
-            upload_csr -> run -> download on one engine
+            upload_csr -> run -> download on one engine; e2e.competitor = the C++ competitor
+            GPUB200::init_csr + run_csr + cleanup_csr on the harness' pageable containers
+  per_config  kernel-only figures of the other configurations and modes and of the K sweep
+            (K = 64, 128, 256 in fp32 and bf16 storage), on the same kind of row shards, each
+            with its own roofline fraction; max over ranks
+  parity    every rank checks a sample of its shard's output against the CPU oracle outside
+            the timed region
   roofline  algorithmic bytes of the dominant kernel / its mean device time, against the
             measured HBM copy bandwidth (MEASURED_PEAKS.json) or the 6650 GB/s fallback
   cpu_baseline  the reference's CPUBasic::run_csr (oracle/_ref, else the oracle port) on the host
@@ -36,7 +42,7 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
-sys.path.insert(0, str(ROOT / "tests"))
+sys.path.insert(0, str(ROOT / "oracle"))   # the CPU checker: used by the cpu_baseline leg and the reference arm only
 
 CONFIG_K = {1: 32, 2: 32, 3: 64, 4: 32, 5: 32}
 CONFIG_NAME = {
@@ -46,7 +52,7 @@ CONFIG_NAME = {
     4: "config4 power-law 2,601,977^2 nnz 36.2M",
     5: "config5 poisson-rows 1,453,908^2 nnz 37.5M",
 }
-DEFAULT_CONFIG = 2
+DEFAULT_CONFIG = 5   # the largest K=32 configuration (configs[4]); it fits one GPU
 FALLBACK_HBM_GBS = 6650.0
 L2_FLUSH_BYTES = 512 << 20
 
@@ -289,6 +295,117 @@ def kernel_only_stats(eng, steps, warmup, flush):
     return float(np.mean(tot)), {k: float(np.mean(v)) for k, v in per.items()}
 
 
+def shard_of(d, rank, world):
+    """This rank's nnz-balanced row range of a dataset (64-row aligned cuts keep the global tile grid)."""
+    from dphpc_b200.partition import row_cuts
+    cuts = row_cuts(d.row_ptr, world, align=64 if d.M >= 64 * 8 * world else 1)
+    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+    j0, j1 = int(d.row_ptr[r0]), int(d.row_ptr[r1])
+    rp = (d.row_ptr[r0:r1 + 1].astype(np.int64) - j0).astype(np.int32)
+    return {"r0": r0, "r1": r1, "j0": j0, "j1": j1, "rp": rp, "M": r1 - r0, "nnz": j1 - j0}
+
+
+def dominant_kernel(kern, plan):
+    """The kernel that owns most nonzeros (when two kernels overlap on the device, the event pair of the small residual
+    kernel also spans its wait for a free SM, so time alone does not say which one dominates)."""
+    if not kern:
+        return None
+    if len(kern) > 1:
+        return "sddmm_dense_tile_kernel" if 2 * plan["dense_nnz"] >= plan["nnz"] else "sddmm_rowtile_kernel"
+    return next(iter(kern))
+
+
+def roofline_block(eng, plan, kern, mode, K, cfg, world, peak, peak_src):
+    dom = dominant_kernel(kern, plan)
+    if not dom:
+        return None
+    dom_ms = float(kern[dom])
+    alg = eng.algorithmic_bytes()
+    if len(kern) > 1:   # split the compulsory bytes between the kernels by the nonzeros each one owns
+        share = plan["dense_nnz"] / max(1, plan["nnz"])
+        alg = alg * (share if "dense" in dom else 1.0 - share)
+    ach = alg / (dom_ms * 1e-3) / 1e9
+    eb = 2 if mode == "bf16" else 4
+    out = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+           # the committed ncu capture is of the whole matrix on one GPU: no figure for a shard of it
+           "traffic": measured_traffic(dom, f"config{cfg}_k{K}_{mode}") if world == 1 else None,
+           "algorithmic_bytes_per_launch": int(alg), "launch_ms": dom_ms, "peak_source": peak_src, "kernels_ms": dict(kern),
+           # what the same nonzeros would move if no gathered B row were ever reused (every nonzero fetches its own B row)
+           "gather_model_bytes": int(eb * K * (plan["rows_nonempty"] + plan["nnz"]) + 12 * plan["nnz"] + 4 * (plan["rows"] + 1))}
+    if "dense" in dom:
+        # the dense contraction the tensor cores execute: 64x64xK' per tile (K' = 3K for the 3-term tf32 split)
+        kp = 3 * K if mode == "fp32_tc" else K
+        tpeak, tsrc = tensor_peak()
+        tfl = 2.0 * 64 * 64 * kp * plan["dense_tiles"] / (dom_ms * 1e-3) / 1e12
+        out["tensor"] = {"dense_tile_tflops": tfl, "peak_tflops": tpeak, "frac": tfl / tpeak, "peak_source": tsrc,
+                         "note": "tensor throughput is not what bounds this path (8 B per nonzero of HBM traffic is)"}
+    return out
+
+
+def parity_sample(p, d, sh, mode, sample=200000, edge_rows=2000):
+    """Outside the timed region: this rank's downloaded P shard against the CPU oracle -- `sample` random nonzeros plus the
+    first and last `edge_rows` rows of the shard.  Returns (checked nonzeros, max |err| / (tol * |s| sum|ab|))."""
+    import oracle_lib
+    tol = 1e-5 if mode in ("fp32", "fp32_tc") else 1e-2
+    orc = oracle_lib.Oracle()
+    r0, r1, j0, nnz = sh["r0"], sh["r1"], sh["j0"], sh["nnz"]
+    if nnz == 0:
+        return 0, 0.0
+    A, B = np.ascontiguousarray(d.A), np.ascontiguousarray(d.B)
+    worst, checked = 0.0, 0
+    for a, b in {(r0, min(r1, r0 + edge_rows)), (max(r0, r1 - edge_rows), r1)}:
+        ja, jb = int(d.row_ptr[a]), int(d.row_ptr[b])
+        if jb <= ja:
+            continue
+        ref = np.zeros(d.nnz, np.float32)
+        orc.sddmm_csr_rows(a, b, d.K, d.row_ptr, d.col_idx, d.s_val, A, B, ref)
+        rows = np.repeat(np.arange(a, b), np.diff(d.row_ptr[a:b + 1]))
+        bound = oracle_lib.abs_dot_bound(rows, d.col_idx[ja:jb], d.s_val[ja:jb], A, B)
+        err = np.abs(p[ja - j0:jb - j0].astype(np.float64) - ref[ja:jb])
+        worst = max(worst, float(np.max(err / (tol * bound + 1e-30))))
+        checked += jb - ja
+    rng = np.random.default_rng(1234 + r0)
+    idx = np.sort(rng.choice(nnz, min(sample, nnz), replace=False)) + j0
+    rows = (np.searchsorted(d.row_ptr, idx, side="right") - 1).astype(np.int64)
+    want = oracle_lib.dot_f64(rows, d.col_idx[idx], d.s_val[idx], A, B)
+    bound = oracle_lib.abs_dot_bound(rows, d.col_idx[idx], d.s_val[idx], A, B)
+    err = np.abs(p[idx - j0].astype(np.float64) - want)
+    worst = max(worst, float(np.max(err / (max(tol, 2e-6) * bound + 1e-30))))
+    if not np.isfinite(p).all():
+        worst = float("inf")
+    return checked + idx.size, worst
+
+
+def competitor_e2e(cfg, K, mode, runs=3):
+    """init_csr + run_csr + cleanup_csr of the C++ competitor on the harness' pageable std::vector containers: what a
+    maintainer who registers GPUB200 in the reference's driver gets (total_ns column of the CSV)."""
+    exe = ROOT / "dphpc_b200" / "sddmm_bench"
+    if not exe.exists():
+        return None
+    try:
+        res = subprocess.run([str(exe), "--config", str(cfg), "-k", str(K), "--num_runs", str(runs), "--mode", mode, "--no_cpu"],
+                             capture_output=True, text=True, timeout=600)
+        name = "GPU-B200" if mode == "fp32" else f"GPU-B200-{mode}"
+        rows = [ln.split(",") for ln in res.stdout.splitlines() if ln.startswith(name + ",")]
+        csr = [r for r in rows if r[2] == "CSR"]
+        if res.returncode not in (0, 3) or not csr:
+            return {"error": (res.stderr or res.stdout)[-300:]}
+        tot = float(np.median([int(r[7]) for r in csr])) * 1e-9
+        return {"value": 2.0 * int(csr[0][6]) * K / tot / 1e9, "unit": "GFLOP/s", "ms_per_step": tot * 1e3,
+                "init_ms": float(np.median([int(r[8]) for r in csr])) * 1e-6, "comp_ms": float(np.median([int(r[9]) for r in csr])) * 1e-6,
+                "cleanup_ms": float(np.median([int(r[10]) for r in csr])) * 1e-6,
+                "what": f"sddmm_bench: Competitors::GPUB200 ({mode}) init_csr + run_csr + cleanup_csr on pageable host containers, "
+                        f"median of {len(csr)} runs, one GPU"}
+    except Exception as ex:   # report, never hide
+        return {"error": str(ex)}
+
+
+# kernel-only table: every configuration BASELINE.json names, every storage mode, and the K sweep of the last one
+PER_CONFIG = [(2, 32, "fp32_tc"), (2, 32, "tf32"), (2, 32, "bf16"), (2, 32, "fp32"), (3, 64, "fp32"), (4, 32, "fp32"), (4, 32, "bf16"),
+              (5, 32, "fp32"), (5, 32, "bf16"), (5, 64, "fp32"), (5, 64, "bf16"), (5, 128, "fp32"), (5, 128, "bf16"),
+              (5, 256, "fp32"), (5, 256, "bf16")]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -298,9 +415,9 @@ def main():
     ap.add_argument("--config", type=int, default=DEFAULT_CONFIG, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--k", type=int, default=0)
     ap.add_argument("--mode", default="fp32_tc", choices=["fp32", "bf16", "tf32", "fp32_tc"],
-                    help="fp32_tc (default): fp32-grade results, dense tiles on tcgen05; fp32: FMA everywhere")
+                    help="fp32_tc (default): fp32-grade results, dense tiles on tcgen05 where S has them; fp32: FMA everywhere")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload (profiling captures only)")
-    ap.add_argument("--no-extra", action="store_true", help="skip the per-config table and the CPU baseline")
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-config table, the parity sample and the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "engine" and args.scale == 1.0 else args.warmup
@@ -312,7 +429,6 @@ def main():
 
     import torch  # device buffers for the L2 flush and the NCCL broadcast only
     from dphpc_b200 import Dataset, Engine, Pipeline, load_engine_lib
-    from dphpc_b200.partition import row_cuts
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the SDDMM engine has no CPU path")
@@ -322,13 +438,24 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
+    def max_over_ranks(x):
+        if dist is None:
+            return float(x)
+        tt = torch.tensor([float(x)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    def sum_over_ranks(x):
+        if dist is None:
+            return float(x)
+        tt = torch.tensor([float(x)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.SUM)
+        return float(tt.item())
+
     cfg, K = args.config, args.k or CONFIG_K[args.config]
     d = Dataset(cfg, K, args.scale)
-    cuts = row_cuts(d.row_ptr, world, align=64 if d.M >= 64 * 8 * world else 1)   # shards keep the global 64-row tile grid
-    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
-    j0, j1 = int(d.row_ptr[r0]), int(d.row_ptr[r1])
-    rp_local = (d.row_ptr[r0:r1 + 1].astype(np.int64) - j0).astype(np.int32)
-    Mloc, nnz_loc = r1 - r0, j1 - j0
+    sh = shard_of(d, rank, world)
+    r0, r1, j0, j1, rp_local, Mloc, nnz_loc = sh["r0"], sh["r1"], sh["j0"], sh["j1"], sh["rp"], sh["M"], sh["nnz"]
     if Mloc < 1:
         raise SystemExit(f"rank {rank}: empty row range; use fewer GPUs for this workload")
 
@@ -393,18 +520,14 @@ def main():
         for name, ms in eng.kernel_times():
             kern.setdefault(name, []).append(ms)
     eng.set_kernel_timing(False)
+    kern = {k: float(np.mean(v)) for k, v in kern.items()}
     # keep the GPU busy a little longer so the clock sampler sees it under load even for short runs
     t_end = time.perf_counter() + (0.6 if rank == 0 else 0.0)
     while time.perf_counter() < t_end:
         eng.run(); eng.sync()
     clocks = sampler.stop() if sampler else None
     t_local = float(np.sum(step_ms))
-    if dist is not None:
-        tt = torch.tensor([t_local], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        t_total = float(tt.item())
-    else:
-        t_total = t_local
+    t_total = max_over_ranks(t_local)
     ms_per_step = t_total / args.steps
     # per-rank shard size and time (how well the nnz-balanced row cuts balance the device time)
     per_rank = None
@@ -419,78 +542,58 @@ def main():
     flops = 2.0 * d.nnz * K
     value = flops / (ms_per_step * 1e-3) / 1e9
 
+    # ---- parity of what was just timed: this rank's P shard against the CPU oracle (outside the timed region) ----
+    parity = None
+    if not args.no_extra:
+        checked, worst = 0, float("inf")
+        try:
+            eng.run()
+            p_shard = eng.download()
+            checked, worst = parity_sample(p_shard, d, sh, args.mode)
+            del p_shard
+        except Exception as ex:  # report, never hide (the collectives below still run on every rank)
+            sys.stderr.write(f"rank {rank}: parity check failed to run: {ex}\n")
+        worst_all = max_over_ranks(worst if np.isfinite(worst) else 1e30)
+        checked_all = sum_over_ranks(checked)
+        parity = {"checked_nnz": int(checked_all), "max_err_over_bound": worst_all, "ok": bool(worst_all <= 1.0), "ranks": world,
+                  "what": "per rank: 200 000 sampled nonzeros of its shard against a float64 dot product, first and last 2 000 rows "
+                          "against the CPU oracle; err / (tol |s| sum_k |a b|), tol 1e-5 (fp32 modes) or 1e-2 (tf32, bf16); max over ranks"}
+
     # ---- end to end through the host-buffer API ---------------------------------------------
     e2e = None
     if not args.no_e2e:
+        n_e2e = max(3, min(args.steps, 10))
+
+        def timed(step, warm):
+            for _ in range(warm):
+                step()
+            barrier()
+            ts = []
+            for _ in range(n_e2e):
+                t0 = time.perf_counter()
+                step()
+                ts.append(time.perf_counter() - t0)
+            return max_over_ranks(float(np.mean(ts)))
+
         def e2e_step():
             eng.upload_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B)
             eng.run()
             eng.download_raw(h_P)
-        for _ in range(2):
-            e2e_step()
-        n_e2e = max(3, min(args.steps, 10))
-        barrier()
-        ts = []
-        for _ in range(n_e2e):
-            t0 = time.perf_counter()
-            e2e_step()
-            ts.append(time.perf_counter() - t0)
-        t_e2e = float(np.mean(ts))
-        if dist is not None:
-            tt = torch.tensor([t_e2e], dtype=torch.float64, device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            t_e2e = float(tt.item())
+        t_e2e = timed(e2e_step, 2)
+
         # the same step when the pattern stays (iterative callers): only A, B and S.val travel up, the plan is kept
         def reuse_step():
             eng.update_raw(h_A, h_B, h_sv)
             eng.run()
             eng.download_raw(h_P)
-        reuse_step()
-        barrier()
-        tr = []
-        for _ in range(n_e2e):
-            t0 = time.perf_counter()
-            reuse_step()
-            tr.append(time.perf_counter() - t0)
-        t_reuse = float(np.mean(tr))
-        if dist is not None:
-            tt = torch.tensor([t_reuse], dtype=torch.float64, device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            t_reuse = float(tt.item())
+        t_reuse = timed(reuse_step, 1)
         # the one-call form of the same sequence: row chunks whose upload, plan + run and download overlap on the full-duplex host link
         pipe = Pipeline(local, args.mode, chunks=4)
-        def pipe_step():
-            pipe.sddmm_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B, h_P)
-        for _ in range(2):
-            pipe_step()
-        barrier()
-        tp = []
-        for _ in range(n_e2e):
-            t0 = time.perf_counter()
-            pipe_step()
-            tp.append(time.perf_counter() - t0)
-        t_pipe = float(np.mean(tp))
+        t_pipe = timed(lambda: pipe.sddmm_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B, h_P), 2)
         pipe_chunks = pipe.last_chunks()
         # ... and when the pattern stays: only the numbers travel, chunk by chunk
-        def pipe_reuse_step():
-            pipe.update_csr_raw(h_sv, h_A, h_B, h_P)
-        pipe_reuse_step()
-        barrier()
-        tpr = []
-        for _ in range(n_e2e):
-            t0 = time.perf_counter()
-            pipe_reuse_step()
-            tpr.append(time.perf_counter() - t0)
-        t_pipe_reuse = float(np.mean(tpr))
+        t_pipe_reuse = timed(lambda: pipe.update_csr_raw(h_sv, h_A, h_B, h_P), 1)
         pipe.close()
-        if dist is not None:
-            tt = torch.tensor([t_pipe_reuse], dtype=torch.float64, device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            t_pipe_reuse = float(tt.item())
-        if dist is not None:
-            tt = torch.tensor([t_pipe], dtype=torch.float64, device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            t_pipe = float(tt.item())
         h2d = 4 * (Mloc + 1) + 8 * nnz_loc + 4 * K * (Mloc + d.N)
         e2e = {"value": flops / t_pipe / 1e9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(4 * nnz_loc),
                "ms_per_step": t_pipe * 1e3, "steps": n_e2e, "chunks": pipe_chunks,
@@ -504,41 +607,13 @@ def main():
                                          "P.val -> pinned host; row chunks overlapped)",
                                  "single_engine": {"value": flops / t_reuse / 1e9, "unit": "GFLOP/s", "ms_per_step": t_reuse * 1e3,
                                                    "what": "update_dense + update_values + run + download on one engine"}}}
+        if rank == 0 and world == 1 and args.scale == 1.0 and not args.no_extra:
+            e2e["competitor"] = competitor_e2e(cfg, K, args.mode)
         eng.nnz = nnz_loc
 
     # ---- roofline of the dominant kernel (this rank's shard) -------------------------------------
     peak, peak_src = hbm_peak()
-    # dominant kernel = the one that owns most nonzeros (when the two kernels of the tensor modes overlap on
-    # the device, the event pair of the small residual kernel also spans its wait for a free SM)
-    dom = None
-    if kern:
-        dom = max(kern, key=lambda k: np.mean(kern[k]))
-        if len(kern) > 1:
-            dom = "sddmm_dense_tile_kernel" if 2 * plan["dense_nnz"] >= plan["nnz"] else "sddmm_rowtile_kernel"
-    roofline = None
-    if dom:
-        dom_ms = float(np.mean(kern[dom]))
-        alg = eng.algorithmic_bytes()
-        if len(kern) > 1:
-            # split the compulsory bytes between the kernels by the nonzeros each one owns
-            share = plan["dense_nnz"] / max(1, plan["nnz"])
-            share = share if "dense" in dom else 1.0 - share
-            alg = alg * share
-        ach = alg / (dom_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "traffic": measured_traffic(dom, f"config{cfg}_k{K}_{args.mode}"), "algorithmic_bytes_per_launch": int(alg),
-                    "launch_ms": dom_ms, "peak_source": peak_src,
-                    "kernels_ms": {k: float(np.mean(v)) for k, v in kern.items()}}
-        # what the same nonzeros would move if no gathered B row were ever reused (every nonzero fetches its own B row)
-        eb = 2 if args.mode == "bf16" else 4
-        roofline["gather_model_bytes"] = int(eb * K * (plan["rows_nonempty"] + plan["nnz"]) + 12 * plan["nnz"] + 4 * (plan["rows"] + 1))
-        if "dense" in dom:
-            # the dense contraction the tensor cores execute: 64x64xK' per tile (K' = 3K for the 3-term tf32 split)
-            kp = 3 * K if args.mode == "fp32_tc" else K
-            tpeak, tsrc = tensor_peak()
-            tfl = 2.0 * 64 * 64 * kp * plan["dense_tiles"] / (dom_ms * 1e-3) / 1e12
-            roofline["tensor"] = {"dense_tile_tflops": tfl, "peak_tflops": tpeak, "frac": tfl / tpeak, "peak_source": tsrc,
-                                  "note": "tensor throughput is not what bounds this path (8 B per nonzero of HBM traffic is)"}
+    roofline = roofline_block(eng, plan, kern, args.mode, K, cfg, world, peak, peak_src)
 
     line = None
     if rank == 0:
@@ -548,65 +623,63 @@ def main():
             "dtype": {"fp32": "f32", "fp32_tc": "f32 (tf32x3 on dense tiles)", "tf32": "tf32", "bf16": "bf16"}[args.mode],
             "data": "synthetic", "config": workload_config(cfg, K, args.mode, world),
             "e2e": e2e, "gpu_launches": int(args.steps * plan["n_kernels"]), "roofline": roofline, "clocks": clocks,
-            "wall_s_timed_region": wall, "per_rank": per_rank,
+            "wall_s_timed_region": wall, "per_rank": per_rank, "parity": parity,
             "plan": {k: plan[k] for k in ("nnz", "rows_nonempty", "cols_touched", "max_row_nnz", "rowtile_nnz", "rowtile_items",
                                           "rowtile_rows_per_stage", "rowtile_grid", "rowtile_smem_bytes", "dense_nnz", "dense_tiles",
-                                          "rowgroup_nnz", "rowgroup_rows", "n_kernels")},
+                                          "rowgroup_nnz", "rowgroup_rows", "rowseg_nnz", "rowseg_units", "rowseg_panels", "rowseg_grid",
+                                          "n_kernels")},
         }
         line["hbm_gb_per_s_algorithmic"] = eng.algorithmic_bytes() / (float(np.mean(step_ms)) * 1e-3) / 1e9
 
-    # ---- the other K=32 / K=64 configurations, kernel only (N = 1), and the CPU baseline --------------
+    # ---- CPU baseline (rank 0 at N = 1) ----------------------------------------------------------------
     if rank == 0 and world == 1 and not args.no_extra and args.scale == 1.0:
         base, _, _ = cpu_reference(d.M, d.N, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, max_nnz=int(8e8 / K), reps=3)
         line["cpu_baseline"] = base
-        per = {}
-        modes = {2: ["fp32", "fp32_tc", "tf32", "bf16"], 3: ["fp32"], 4: ["fp32"], 5: ["fp32", "bf16"]}
-        for c in (2, 3, 4, 5):
-            dd = d if c == cfg else Dataset(c, CONFIG_K[c], 1.0)
-            for m in modes[c]:
-                try:
-                    e2 = Engine(local, m)
-                    e2.upload_csr(dd.M, dd.N, dd.K, dd.row_ptr, dd.col_idx, dd.s_val, dd.A, dd.B)
-                    ms, ks = kernel_only_stats(e2, 10, 3, flush)
-                    ab = e2.algorithmic_bytes()
-                    per[f"config{c}_k{dd.K}_{m}"] = {"ms": ms, "gflops": 2.0 * dd.nnz * dd.K / ms / 1e6, "gb_per_s": ab / ms / 1e6,
-                                                    "hbm_frac": ab / ms / 1e6 / peak, "kernels_ms": ks}
-                    e2.close()
-                except Exception as ex:  # report, never hide
-                    per[f"config{c}_k{dd.K}_{m}"] = {"error": str(ex)}
-            if dd is not d:
-                dd.close()
-        line["per_config"] = per
 
-    # ---- N > 1: the large configurations on the same row shards, kernel only (their N = 1 figures are in the N = 1 line) ----
-    if world > 1 and not args.no_extra and args.scale == 1.0:
+    # ---- every other configuration / mode and the K sweep, kernel only, on the same kind of row shards -----------------
+    if not args.no_extra and args.scale == 1.0:
         per = {}
-        for c in (3, 4, 5):
-            ms_local, nnz_c, k_c = 1e30, 0, CONFIG_K[c]
+        cache = {}   # (config, K) -> dataset; generated once, shared by the modes
+        for c, k_c, m in PER_CONFIG:
+            key = f"config{c}_k{k_c}_{m}"
+            ms_local, alg_local, nnz_c, plan_c, kern_c, e2 = 1e30, 0.0, 0, None, {}, None
             try:
-                dd = d if c == cfg else Dataset(c, k_c, 1.0)
+                if (c, k_c) not in cache:
+                    for dd_old in cache.values():
+                        if dd_old is not d:
+                            dd_old.close()
+                    cache.clear()
+                    cache[(c, k_c)] = d if (c, k_c) == (cfg, K) else Dataset(c, k_c, 1.0)
+                dd = cache[(c, k_c)]
                 nnz_c = int(dd.nnz)
-                cc = row_cuts(dd.row_ptr, world, align=64 if dd.M >= 64 * 8 * world else 1)
-                a, b = int(cc[rank]), int(cc[rank + 1])
-                ja, jb = int(dd.row_ptr[a]), int(dd.row_ptr[b])
-                if b > a:
-                    e2 = Engine(local, "fp32")
-                    e2.upload_csr(b - a, dd.N, dd.K, (dd.row_ptr[a:b + 1].astype(np.int64) - ja).astype(np.int32), dd.col_idx[ja:jb],
-                                  dd.s_val[ja:jb], dd.A[a:b], dd.B)
-                    ms_local, _ = kernel_only_stats(e2, 10, 3, flush)
-                    e2.close()
+                s2 = shard_of(dd, rank, world)
+                if s2["M"] > 0 and s2["nnz"] > 0:
+                    e2 = Engine(local, m)
+                    e2.upload_csr(s2["M"], dd.N, dd.K, s2["rp"], dd.col_idx[s2["j0"]:s2["j1"]], dd.s_val[s2["j0"]:s2["j1"]],
+                                  dd.A[s2["r0"]:s2["r1"]], dd.B)
+                    ms_local, kern_c = kernel_only_stats(e2, 10, 3, flush)
+                    alg_local, plan_c = float(e2.algorithmic_bytes()), e2.plan()
                 else:
                     ms_local = 0.0
-                if dd is not d:
-                    dd.close()
-            except Exception as ex:  # report, never hide (the collective below still runs on every rank)
-                sys.stderr.write(f"rank {rank}: config {c}: {ex}\n")
-            tt = torch.tensor([ms_local], dtype=torch.float64, device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            ms = float(tt.item())
-            key = f"config{c}_k{k_c}_fp32"
-            per[key] = ({"error": "a rank failed (see stderr)"} if ms >= 1e29 else
-                        {"ms": ms, "gflops": 2.0 * nnz_c * k_c / ms / 1e6, "what": f"{world} nnz-balanced row shards, max over ranks"})
+            except Exception as ex:  # report, never hide (the collectives below still run on every rank)
+                sys.stderr.write(f"rank {rank}: {key}: {ex}\n")
+                ms_local = 1e30
+            finally:
+                if e2 is not None:
+                    e2.close()
+            ms = max_over_ranks(ms_local)
+            alg = sum_over_ranks(alg_local)
+            if rank == 0:
+                if ms >= 1e29 or ms <= 0:
+                    per[key] = {"error": "a rank failed (see stderr)"}
+                else:
+                    per[key] = {"ms": ms, "gflops": 2.0 * nnz_c * k_c / ms / 1e6, "gb_per_s": alg / ms / 1e6, "hbm_frac": alg / ms / 1e6 / (peak * world),
+                                "kernels_ms_rank0": kern_c, "kernel": dominant_kernel(kern_c, plan_c) if plan_c else None,
+                                "what": f"{world} nnz-balanced row shard(s), max over ranks; fraction = algorithmic bytes of all shards / time / "
+                                        f"({world} x HBM peak)"}
+        for dd_old in cache.values():
+            if dd_old is not d:
+                dd_old.close()
         if rank == 0:
             line["per_config"] = per
 

@@ -85,7 +85,7 @@ def build_bench(force: bool = False) -> Path:
     srcs = [p for p in src_dir.rglob("*") if p.suffix in (".cpp", ".hpp", ".h")]
     if force or _newer(BENCH_BIN, srcs + [ENGINE_LIB, DATASETS_LIB]):
         cmd = [
-            "g++", "-O2", "-std=c++17", "-Wall", "-I", str(src_dir), "-I", str(INCLUDE),
+            "g++", "-O2", "-ffp-contract=off", "-std=c++17", "-Wall", "-I", str(src_dir), "-I", str(INCLUDE),
             "-o", str(BENCH_BIN), str(main),
             "-L", str(PKG), "-lsddmm_b200", "-lsddmm_datasets", f"-Wl,-rpath,{PKG}", "-Wl,-rpath,$ORIGIN", "-pthread",
         ]

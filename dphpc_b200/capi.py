@@ -21,6 +21,7 @@ FP32, TF32, BF16, FP32_TC = 0, 1, 2, 3
 MODES = {"fp32": FP32, "tf32": TF32, "bf16": BF16, "fp32_tc": FP32_TC}
 FLAG_NO_DENSE_TILES = 1
 FLAG_NO_ROW_GROUPS = 2
+FLAG_NO_ROW_SEGMENTS = 4
 HIST_BINS = 20
 
 STATUS = {
@@ -38,7 +39,7 @@ ENGINE_SYMBOLS = [
     "sddmm_b200_host_free", "sddmm_b200_sddmm_csr_prealloc", "sddmm_b200_set_kernel_timing",
     "sddmm_b200_pipeline_create", "sddmm_b200_pipeline_destroy", "sddmm_b200_pipeline_sddmm_csr",
     "sddmm_b200_pipeline_last_chunks", "sddmm_b200_pipeline_last_error", "sddmm_b200_pipeline_set_min_chunk_bytes",
-    "sddmm_b200_pipeline_update_csr", "sddmm_b200_pipeline_sddmm_coo",
+    "sddmm_b200_pipeline_update_csr", "sddmm_b200_pipeline_sddmm_coo", "sddmm_b200_set_knob",
 ]
 DATASET_SYMBOLS = [
     "sddmm_dataset_create", "sddmm_dataset_create_uniform", "sddmm_dataset_destroy", "sddmm_dataset_dims",
@@ -64,6 +65,8 @@ class PlanInfo(C.Structure):
         ("rowgroup_rows", C.c_int32),
         ("rowgroup_grid", C.c_int32),
         ("n_kernels", C.c_int32), ("n_devices", C.c_int32),
+        ("rowseg_nnz", C.c_int64),
+        ("rowseg_units", C.c_int32), ("rowseg_panels", C.c_int32), ("rowseg_grid", C.c_int32), ("reserved0", C.c_int32),
     ]
 
     def as_dict(self) -> dict:
@@ -111,6 +114,7 @@ def load_engine_lib() -> C.CDLL:
     lib.sddmm_b200_last_kernel_ms.argtypes = [H, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_char_p)]
     lib.sddmm_b200_set_kernel_timing.argtypes = [H, C.c_int]
     lib.sddmm_b200_get_plan.argtypes = [H, C.POINTER(PlanInfo)]
+    lib.sddmm_b200_set_knob.argtypes = [H, C.c_char_p, C.c_double]
     lib.sddmm_b200_algorithmic_bytes.argtypes = [H]
     lib.sddmm_b200_algorithmic_bytes.restype = C.c_int64
     lib.sddmm_b200_flops.argtypes = [H]
@@ -291,6 +295,10 @@ class Engine:
             self._check(self.lib.sddmm_b200_last_kernel_ms(self.h, i, C.byref(ms), C.byref(name)), "last_kernel_ms")
             out.append(((name.value or b"?").decode(), float(ms.value)))
         return out
+
+    def set_knob(self, name: str, value: float):
+        """Planner knob (see sddmm_b200_set_knob); a negative value hands the decision back to the planner."""
+        self._check(self.lib.sddmm_b200_set_knob(self.h, name.encode(), float(value)), "set_knob")
 
     def plan(self) -> dict:
         info = PlanInfo()

@@ -13,7 +13,6 @@ constexpr unsigned kFullMask = 0xffffffffu;
 enum DeviceError : int {
     kDevOk = 0,
     kDevMbarrierTimeout = 1,   // a bounded mbarrier wait ran out
-    kDevTmemAllocFailed = 2,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -23,9 +22,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
 // ---- mbarrier + bulk async copy (TMA, 1-D, non-multicast) -------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_inval(uint64_t *bar) {
-    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // make barrier initialisation visible to the async proxy
 __device__ __forceinline__ void fence_mbar_init() {

@@ -12,12 +12,16 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <new>
+#include <utility>
 #include <vector>
 
 #include "../../include/sddmm_b200.h"
 #include "kernel_dense_tile.cuh"
 #include "kernel_rowgroup.cuh"
+#include "kernel_rowseg.cuh"
 #include "kernel_rowtile.cuh"
 #include "plan_kernels.cuh"
 
@@ -112,6 +116,19 @@ struct sddmm_b200_engine {
     int32_t rg_first = 0;          // first row of the first full group
     int32_t rg_groups = 0;         // ceil(M / rg_rows)
 
+    // row-segment path (short and power-law rows; column panels when B is much larger than L2)
+    int2 *d_units = nullptr;
+    int32_t *d_unit_off = nullptr;     // per (panel, row): units before it (scan of the counts)
+    int32_t *d_scan_tiles = nullptr;
+    int64_t unit_cap = 0;
+    int32_t panels = 1;                // column panels the unit list is ordered by
+    int32_t panel_cols = 0;            // columns per panel
+    int32_t n_units = 0;
+    bool use_seg = false;
+    int l2_bytes = 0;
+    // tuning knobs (sddmm_b200_set_knob; defaults from the environment at create): < 0 = decide automatically
+    double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_evict_last = -1, knob_b_fraction = -1;
+
     // plan
     sddmm_b200_plan_info plan;
     bool use_scalar = false;
@@ -175,6 +192,27 @@ int ensure_arena(sddmm_b200_engine *e, size_t bytes) {
     return SDDMM_B200_OK;
 }
 
+// Upper bound of the row-tile kernel's dynamic shared memory: two buffers of kMaxStageBytes of A rows plus a row_ptr
+// slice of at most kMaxStageBytes / 16 + 1 entries (the shortest staged row is 16 bytes).
+constexpr int kRowTileMaxSmem = 2 * (kMaxStageBytes + (kMaxStageBytes / 16 + 1) * 4 + 32);
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (function, device) pair, not to an engine: it is raised
+// ONCE per pair to the upper bound, so that engines that share a GPU (chunked calls, a device listed twice, the
+// allocation-free entry) can never leave each other with a limit below what their own launch asks for.
+int ensure_dynamic_smem_limit(const void *fn, int device, int bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, int> raised;
+    std::lock_guard<std::mutex> lock(mu);
+    int &have = raised[{fn, device}];
+    if (have >= bytes) return SDDMM_B200_OK;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return SDDMM_B200_ERR_CUDA;
+    }
+    have = bytes;
+    return SDDMM_B200_OK;
+}
+
 template <typename ET>
 using RowTileFn = void (*)(const RowTileArgs);
 
@@ -200,6 +238,28 @@ int round_up_cpl(int64_t K) {
 
 size_t elem_bytes(const sddmm_b200_engine *e) { return e->mode == SDDMM_B200_BF16 ? 2 : 4; }
 
+double env_double(const char *name, double fallback) {
+    const char *v = std::getenv(name);
+    return v ? std::atof(v) : fallback;
+}
+
+// Column panels of the row-segment path.  B is cut into panels when it is much larger than the L2 cache, so that the
+// gathers of one panel hit in L2; every panel pass reads the A rows it touches again and shortens the runs a row
+// contributes (a run of fewer than ~6 nonzeros leaves most of a segment's 8 slots empty), which bounds the count.
+int choose_panels(const sddmm_b200_engine *e) {
+    if (e->knob_panels >= 1 && e->knob_panels <= 64) return static_cast<int>(e->knob_panels);
+    if (e->knob_panel_mb <= 0) return 1;   // off unless a panel size is asked for
+    const double eb = static_cast<double>(elem_bytes(e));
+    const double b_bytes = static_cast<double>(e->N) * e->K * eb, a_bytes = static_cast<double>(e->M) * e->K * eb;
+    const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
+    if (b_bytes <= 0.75 * l2) return 1;
+    const double panel = e->knob_panel_mb > 0 ? e->knob_panel_mb * (1 << 20) : 0.4 * l2;
+    int64_t p = static_cast<int64_t>((b_bytes + panel - 1) / panel);
+    p = std::min<int64_t>(p, e->nnz / std::max<int64_t>(1, 6 * e->M));           // keep runs of ~6 nonzeros and more
+    while (p > 1 && p * a_bytes > 0.6 * static_cast<double>(e->nnz) * e->K * eb) --p;   // re-reading A must stay cheaper than the gathers it saves
+    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(p, 32)));
+}
+
 // Lay out the arena for the current dimensions and point the views into it.
 int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     Carve c;
@@ -221,10 +281,22 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     const size_t o_pc = c.take(sizeof(PlanCounters));
     const size_t o_err = c.take(sizeof(int32_t));
     const size_t o_gok = c.take(M / 2 + 4);   // one byte per row group (groups of >= 2 rows, plus the leading partial group)
+    // row-segment path: unit list (upper bound: one unit per 8 nonzeros plus one ragged unit per row and panel), scan scratch
+    e->panels = choose_panels(e);
+    e->panel_cols = static_cast<int32_t>((N + e->panels - 1) / e->panels);
+    const size_t runs = std::min(M * static_cast<size_t>(e->panels), nnz);
+    e->unit_cap = static_cast<int64_t>(nnz / 8 + runs + 8);
+    const size_t scan_n = M * static_cast<size_t>(e->panels);
+    const size_t o_units = c.take(static_cast<size_t>(e->unit_cap) * sizeof(int2));
+    const size_t o_uoff = c.take((scan_n + 1) * 4);
+    const size_t o_stile = c.take((scan_n / kScanTile + 2) * 4);
     // dense-tile path: only carved when the mode, K and the size of the 64x64 tile grid allow it
     e->tiles_per_row = static_cast<int32_t>((N + 63) / 64);
     e->tile_grid = static_cast<int64_t>((M + 63) / 64) * e->tiles_per_row;
-    const bool tc_mode = e->mode == SDDMM_B200_TF32 || e->mode == SDDMM_B200_FP32_TC;
+    // tensor-core modes.  bf16 takes the same kind::tf32 kernel: the fp32 copies of A and B are rounded to bf16 in place at
+    // upload, every bf16 value is exactly a tf32 value (8 against 11 significand bits), so the tile products are exactly the
+    // bf16-input / fp32-accumulate ones.
+    const bool tc_mode = e->mode == SDDMM_B200_TF32 || e->mode == SDDMM_B200_FP32_TC || e->mode == SDDMM_B200_BF16;
     e->dense_possible = tc_mode && !(e->flags & SDDMM_B200_FLAG_NO_DENSE_TILES) && K % 32 == 0 && K <= 256 &&
                         e->tile_grid <= (int64_t(1) << 22) && nnz >= kDenseMinCount;
     e->dense_cap = e->dense_possible ? static_cast<int32_t>(std::min<int64_t>(e->tile_grid, e->nnz / kDenseMinCount + 1)) : 0;
@@ -249,6 +321,9 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     e->d_item_ids = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_ii) : nullptr;
     e->d_Ax = split ? reinterpret_cast<float *>(b + o_ax) : nullptr;
     e->d_Bx = split ? reinterpret_cast<float *>(b + o_bx) : nullptr;
+    e->d_units = reinterpret_cast<int2 *>(b + o_units);
+    e->d_unit_off = reinterpret_cast<int32_t *>(b + o_uoff);
+    e->d_scan_tiles = reinterpret_cast<int32_t *>(b + o_stile);
     e->d_rp = reinterpret_cast<int32_t *>(b + o_rp);
     e->d_group_ok = reinterpret_cast<uint8_t *>(b + o_gok);
     e->d_col = reinterpret_cast<int32_t *>(b + o_col);
@@ -287,6 +362,7 @@ int convert_storage(sddmm_b200_engine *e) {
         CU_TRY(e, cudaGetLastError());
     }
     if (e->mode != SDDMM_B200_BF16) return SDDMM_B200_OK;
+    // (the fp32 copies keep the rounded values: the dense-tile kernel reads them through its tensor maps)
     k_f32_to_bf16<<<grid_for(e->M * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_A32, e->d_A16, e->M * e->K);
     k_f32_to_bf16<<<grid_for(e->N * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_B32, e->d_B16, e->N * e->K);
     CU_TRY(e, cudaGetLastError());
@@ -359,7 +435,8 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     int st = make_operand_map(e, &e->map_a, split ? e->d_Ax : e->d_A32, e->M, kx);
     if (!st) st = make_operand_map(e, &e->map_b, split ? e->d_Bx : e->d_B32, e->N, kx);
     if (st) return st;
-    CU_TRY(e, cudaFuncSetAttribute(sddmm_dense_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DenseSmem::kDynamicBytes));
+    if (ensure_dynamic_smem_limit(reinterpret_cast<const void *>(sddmm_dense_tile_kernel), e->device, DenseSmem::kDynamicBytes))
+        return fail(e, SDDMM_B200_ERR_CUDA, "dense-tile kernel: cannot raise the dynamic shared memory limit");
     CU_TRY(e, cudaFuncSetAttribute(sddmm_dense_tile_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     e->n_dense = n_dense;
     e->n_residual_items = pc.residual_items;
@@ -453,6 +530,70 @@ int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     return SDDMM_B200_OK;
 }
 
+template <typename ET>
+using RowSegFn = void (*)(const RowSegArgs);
+
+template <typename ET, bool HINT>
+RowSegFn<ET> pick_rowseg_hint(int cpl, bool exact) {
+    switch (cpl) {
+        case 1: return exact ? sddmm_rowseg_kernel<1, true, ET, HINT> : sddmm_rowseg_kernel<1, false, ET, HINT>;
+        case 2: return exact ? sddmm_rowseg_kernel<2, true, ET, HINT> : sddmm_rowseg_kernel<2, false, ET, HINT>;
+        case 4: return exact ? sddmm_rowseg_kernel<4, true, ET, HINT> : sddmm_rowseg_kernel<4, false, ET, HINT>;
+        case 8: return exact ? sddmm_rowseg_kernel<8, true, ET, HINT> : sddmm_rowseg_kernel<8, false, ET, HINT>;
+        default: return nullptr;
+    }
+}
+template <typename ET>
+RowSegFn<ET> pick_rowseg(int cpl, bool exact, bool hint = false) {
+    return hint ? pick_rowseg_hint<ET, true>(cpl, exact) : pick_rowseg_hint<ET, false>(cpl, exact);
+}
+
+// Row segments: the unit list (rows cut into segments of at most 8 nonzeros, panel-major when B is cut into column
+// panels) is counted, scanned and written on the device; the host only reads the total.  Taken unless the rows are
+// long on average (the A-row-tile kernel keeps the A chunk of a long row in registers over the whole row).
+int build_rowseg_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
+    const int seg_env = e->knob_rowseg < 0 ? -1 : static_cast<int>(e->knob_rowseg);   // 0 never, 1 whenever possible
+    e->use_seg = false;
+    e->n_units = 0;
+    if ((e->flags & SDDMM_B200_FLAG_NO_ROW_SEGMENTS) || seg_env == 0 || e->M >= kUnitRowLimit) return SDDMM_B200_OK;
+    const double mean_len = static_cast<double>(e->nnz) / static_cast<double>(std::max<unsigned long long>(1, base_pc.rows_nonempty));
+    if (seg_env != 1 && mean_len > 512.0) return SDDMM_B200_OK;
+    const int32_t panels = base_pc.unsorted_cols ? 1 : e->panels;   // a panel run is a contiguous piece of a row only when its columns are sorted
+    const int32_t M = static_cast<int32_t>(e->M);
+    const int64_t n = static_cast<int64_t>(panels) * M;
+    const int n_tiles = static_cast<int>((n + kScanTile - 1) / kScanTile);
+    const int cap = e->sm_count * 32;
+    cudaStream_t s = e->stream;
+    k_unit_count<<<grid_for(n, kBlock, cap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, panels, e->panel_cols, e->d_unit_off);
+    k_scan_tile_sums<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, n, e->d_scan_tiles);
+    k_scan_sums<<<1, kScanBlock, 0, s>>>(e->d_scan_tiles, n_tiles, &e->d_pc->units);
+    k_scan_apply<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, n, e->d_scan_tiles);
+    k_unit_fill<<<grid_for(n * 32, kBlock, cap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, panels, e->panel_cols, e->d_unit_off, e->d_units);
+    CU_TRY(e, cudaGetLastError());
+    PlanCounters pc;
+    if (int rc = read_counters(e, &pc)) return rc;
+    if (pc.units == 0 || pc.units > static_cast<unsigned long long>(e->unit_cap) || pc.units >= (1ull << 31))
+        return fail(e, SDDMM_B200_ERR_CUDA, "row-segment plan: %llu units for a list of %lld", pc.units, (long long)e->unit_cap);
+    const bool exact = e->K == 32 * e->cpl;
+    const void *fn = (e->mode == SDDMM_B200_BF16) ? reinterpret_cast<const void *>(pick_rowseg<__nv_bfloat16>(e->cpl, exact))
+                                                  : reinterpret_cast<const void *>(pick_rowseg<float>(e->cpl, exact));
+    int occ = 0;
+    CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kRowSegWarps * 32, 0));
+    if (occ < 1) return fail(e, SDDMM_B200_ERR_CUDA, "row-segment kernel does not fit on an SM");
+    e->n_units = static_cast<int32_t>(pc.units);
+    e->use_seg = true;
+    sddmm_b200_plan_info &p = e->plan;
+    const int64_t n_quads = (static_cast<int64_t>(e->n_units) + 3) / 4;
+    p.rowseg_nnz = e->nnz;
+    p.rowseg_units = e->n_units;
+    p.rowseg_panels = panels;
+    p.rowseg_grid = static_cast<int32_t>(std::min<int64_t>((n_quads + kRowSegWarps - 1) / kRowSegWarps, static_cast<int64_t>(e->sm_count) * occ));
+    p.rowtile_nnz = 0;
+    p.rowtile_items = 0;
+    p.n_kernels = 1;
+    return SDDMM_B200_OK;
+}
+
 int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
     const int cap = e->sm_count * 8;
     cudaStream_t s = e->stream;
@@ -514,10 +655,14 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
         if (st) return st;
     }
     e->rg_rows = 0;
+    e->use_seg = false;
     if (!e->use_scalar && e->n_dense == 0) {
         int st = build_rowgroup_plan(e, pc);
         if (st) return st;
         if (e->rg_rows) return SDDMM_B200_OK;
+        st = build_rowseg_plan(e, pc);
+        if (st) return st;
+        if (e->use_seg) return SDDMM_B200_OK;
     }
     p.rowtile_nnz = e->nnz - p.dense_nnz;
     p.rowtile_items = e->n_residual_items;
@@ -543,7 +688,7 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
 
     const void *fn = (e->mode == SDDMM_B200_BF16) ? reinterpret_cast<const void *>(pick_rowtile<__nv_bfloat16>(e->cpl, e->K == 32 * e->cpl))
                                                   : reinterpret_cast<const void *>(pick_rowtile<float>(e->cpl, e->K == 32 * e->cpl));
-    CU_TRY(e, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p.rowtile_smem_bytes));
+    if (ensure_dynamic_smem_limit(fn, e->device, kRowTileMaxSmem)) return fail(e, SDDMM_B200_ERR_CUDA, "row-tile kernel: cannot raise the dynamic shared memory limit");
     int occ = 0;
     CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kBlock, p.rowtile_smem_bytes));
     if (occ < 1) return fail(e, SDDMM_B200_ERR_CUDA, "row-tile kernel does not fit on an SM (smem %d B)", p.rowtile_smem_bytes);
@@ -645,6 +790,24 @@ int launch_all(sddmm_b200_engine *e) {
         pick_rowgroup(e->rg_rows, static_cast<int>(e->K / 32))<<<p.rowgroup_grid, kRowGroupWarps * 32, 0, e->stream>>>(g);
         return mark_kernel(e, "sddmm_rowgroup_kernel", e->stream);
     }
+    if (e->use_seg) {
+        RowSegArgs g;
+        g.units = e->d_units; g.col_idx = e->d_col; g.s_val = e->d_sval; g.p_val = e->d_pval;
+        g.n_units = e->n_units; g.K = static_cast<int32_t>(e->K);
+        // L2 is asked to keep the gathered B rows when they can stay: one column panel at a time
+        g.b_evict_last = e->knob_b_evict_last >= 0 ? static_cast<int32_t>(e->knob_b_evict_last) : (p.rowseg_panels > 1 ? 1 : 0);
+        g.b_fraction = e->knob_b_fraction > 0 ? static_cast<float>(std::min(1.0, e->knob_b_fraction)) : 1.0f;
+        const bool exact = e->K == 32 * e->cpl;
+        if ((st = begin_kernel(e, e->stream))) return st;
+        if (e->mode == SDDMM_B200_BF16) {
+            g.A = e->d_A16; g.B = e->d_B16;
+            pick_rowseg<__nv_bfloat16>(e->cpl, exact, g.b_evict_last != 0)<<<p.rowseg_grid, kRowSegWarps * 32, 0, e->stream>>>(g);
+        } else {
+            g.A = e->d_A32; g.B = e->d_B32;
+            pick_rowseg<float>(e->cpl, exact, g.b_evict_last != 0)<<<p.rowseg_grid, kRowSegWarps * 32, 0, e->stream>>>(g);
+        }
+        return mark_kernel(e, "sddmm_rowseg_kernel", e->stream);
+    }
     // the two kernels write disjoint nonzeros: when both run, the row-tile kernel goes to the side stream
     static const bool no_side = std::getenv("SDDMM_B200_NO_SIDE_STREAM") != nullptr;   // tuning / debugging knob
     const bool both = e->n_dense > 0 && e->n_residual_items > 0 && !no_side;
@@ -713,6 +876,11 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     e->device = device;
     e->mode = mode;
     e->flags = flags;
+    e->knob_panels = env_double("SDDMM_B200_PANELS", -1);
+    e->knob_panel_mb = env_double("SDDMM_B200_PANEL_MB", -1);
+    e->knob_rowseg = env_double("SDDMM_B200_ROWSEG", -1);
+    e->knob_b_evict_last = env_double("SDDMM_B200_B_EVICT_LAST", -1);
+    e->knob_b_fraction = env_double("SDDMM_B200_B_FRACTION", -1);
     DeviceGuard g(device);
     bool ok = g.ok;
     ok = ok && cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -723,6 +891,7 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     ok = ok && cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&e->ev_h2d, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess;
+    ok = ok && cudaDeviceGetAttribute(&e->l2_bytes, cudaDevAttrL2CacheSize, device) == cudaSuccess;
     ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&e->h_err), sizeof(int32_t), cudaHostAllocDefault) == cudaSuccess;
     ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&e->h_pc), sizeof(PlanCounters), cudaHostAllocDefault) == cudaSuccess;
     if (!ok) {
@@ -890,6 +1059,20 @@ int sddmm_b200_set_kernel_timing(sddmm_b200_engine *e, int enabled) {
     return SDDMM_B200_OK;
 }
 
+int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value) {
+    if (!e || !name) return SDDMM_B200_ERR_ARG;
+    struct { const char *name; double *slot; } knobs[] = {
+        {"panels", &e->knob_panels}, {"panel_mb", &e->knob_panel_mb}, {"rowseg", &e->knob_rowseg},
+        {"b_evict_last", &e->knob_b_evict_last}, {"b_fraction", &e->knob_b_fraction},
+    };
+    for (auto &k : knobs)
+        if (std::strcmp(name, k.name) == 0) {
+            *k.slot = value;
+            return SDDMM_B200_OK;
+        }
+    return fail(e, SDDMM_B200_ERR_ARG, "unknown knob '%s'", name);
+}
+
 int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info) {
     if (!e || !info) return SDDMM_B200_ERR_ARG;
     if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "get_plan before upload");
@@ -953,6 +1136,11 @@ int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int6
     if (M < 1 || N < 1 || K < 1 || nnz < 0 || device < 0 || device >= kPreallocMaxDevices) return SDDMM_B200_ERR_ARG;
     if (!d_row_ptr || !d_A || !d_B || (nnz > 0 && (!d_col_idx || !d_s_val || !d_p_val))) return SDDMM_B200_ERR_ARG;
     if (M >= (int64_t(1) << 31) - 1 || N >= (int64_t(1) << 31) - 1) return SDDMM_B200_ERR_ARG;
+    // the kernel reads col_idx, A and B with 16-byte accesses (the engine's own arena is 256-byte aligned; a caller's
+    // pointer into the middle of a larger buffer may not be) -- refused here rather than faulting on the GPU
+    auto misaligned = [](const void *ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) != 0; };
+    if (misaligned(d_A, 16) || misaligned(d_B, 16) || (nnz > 0 && misaligned(d_col_idx, 16))) return SDDMM_B200_ERR_ARG;
+    if (misaligned(d_row_ptr, 4) || (nnz > 0 && (misaligned(d_s_val, 4) || misaligned(d_p_val, 4)))) return SDDMM_B200_ERR_ARG;
     if (nnz > kPreallocMaxNnz) return SDDMM_B200_ERR_UNSUPPORTED;        // the work-item table would not fit the fixed scratch
     const int cpl = round_up_cpl(K);
     if (K % 4 != 0 || cpl == 0) return SDDMM_B200_ERR_UNSUPPORTED;      // only the row-tile kernel (K % 4 == 0, K <= 256) is offered here
@@ -982,7 +1170,7 @@ int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int6
     const int smem = static_cast<int>(rowtile_smem_bytes(static_cast<int>(R), static_cast<uint32_t>(K * 4)));
     const bool exact = (K == 32 * cpl);
     RowTileFn<float> fn = pick_rowtile<float>(cpl, exact);
-    if (cudaFuncSetAttribute(reinterpret_cast<const void *>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return SDDMM_B200_ERR_CUDA;
+    if (ensure_dynamic_smem_limit(reinterpret_cast<const void *>(fn), device, kRowTileMaxSmem)) return SDDMM_B200_ERR_CUDA;
     int occ = 0, sms = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, reinterpret_cast<const void *>(fn), kBlock, smem) != cudaSuccess || occ < 1) return SDDMM_B200_ERR_CUDA;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return SDDMM_B200_ERR_CUDA;

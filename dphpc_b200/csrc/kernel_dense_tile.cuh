@@ -152,7 +152,10 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseCtasPerSm)
 sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b) {
     extern __shared__ unsigned char dense_smem_raw[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(dense_smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment by an OFFSET into the shared array (not by rounding a generic address): every pointer below
+    // stays a shared-memory pointer for the compiler, so its loads and stores are shared-space instructions that it may
+    // reorder against the global stores of the sampling loop
+    unsigned char *smem = dense_smem_raw + ((1024u - (smem_u32(dense_smem_raw) & 1023u)) & 1023u);
     float *sAcc = reinterpret_cast<float *>(smem + DenseSmem::kAcc);
     float *sSval = reinterpret_cast<float *>(smem + DenseSmem::kSval);
     uint4 *sRows = reinterpret_cast<uint4 *>(smem + DenseSmem::kRows);
@@ -165,19 +168,91 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     const int lane = tid & 31;
     const int n_jobs = (args.n_tiles + 1) >> 1;
 
-    if (tid == 0) {
+    // Start-up, kept short: the producer thread initialises the barriers itself and requests the operands of its first
+    // job at once; the epilogue warps request the row records of their first job; only then does the CTA meet at the
+    // barrier behind which the tensor memory address is known.
+    const bool is_producer = (tid == kDenseEpiWarps * 32);
+    int first0 = 0, first1 = 0;   // producer: tile ids of the CTA's first job
+    if (is_producer) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+        if (static_cast<int>(blockIdx.x) < n_jobs) {
+            first0 = args.tile_ids[2 * blockIdx.x];
+            first1 = (2 * static_cast<int>(blockIdx.x) + 1 < args.n_tiles) ? args.tile_ids[2 * blockIdx.x + 1] : first0;
+        }
         mbar_init(ops_full, 1);
         mbar_init(ops_free, 1);
         mbar_init(acc_full, 1);
         mbar_init(acc_free, kDenseEpiWarps);
         fence_mbar_init();
+        fence_proxy_async_smem();
     }
     if (warp == 0) {  // one warp allocates the tensor memory for the CTA
-        __syncwarp();  // lane 0 comes out of the barrier-init branch: re-converge before the warp-wide alloc
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    fence_proxy_async_smem();
+
+    // ---- producer state and helpers (used by the one producer thread) ----
+    // Iterations = (job, k-block) pairs of this CTA in order.  The TMA of iteration it + 1 is issued
+    // right after the MMAs of iteration it (it waits for them to release the operand buffer).
+    const int kbs = args.k_blocks;
+    const int my_jobs = (n_jobs - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const uint32_t total = static_cast<uint32_t>(my_jobs) * static_cast<uint32_t>(kbs);
+    int cur0 = first0, cur1 = first1, nxt0 = 0, nxt1 = 0;   // ids of the job being requested / of the one after (read a job ahead of their use)
+    bool prod_ok = true;
+    // tile ids of a job (the second tile of the last job may be missing: its operands repeat the first)
+    auto load_ids = [&](uint32_t j, int &t0, int &t1) {
+        const int job = static_cast<int>(blockIdx.x) + static_cast<int>(j) * static_cast<int>(gridDim.x);
+        t0 = args.tile_ids[2 * job];
+        t1 = ((2 * job + 1) < args.n_tiles) ? args.tile_ids[2 * job + 1] : t0;
+    };
+    // request operand k-block `it` (called once per it, in order)
+    auto issue_tma = [&](uint32_t it) -> bool {
+        const uint32_t ph = it & 1u;
+        const uint32_t j = it / kbs;
+        const int kb = static_cast<int>(it % kbs);
+        if (kb == 0 && it > 0) {
+            cur0 = nxt0;
+            cur1 = nxt1;
+            if (j + 1 < static_cast<uint32_t>(my_jobs)) load_ids(j + 1, nxt0, nxt1);
+        }
+        const int r0 = (cur0 / args.tiles_per_row) * kDenseTile, c0 = (cur0 % args.tiles_per_row) * kDenseTile;
+        const int r1 = (cur1 / args.tiles_per_row) * kDenseTile, c1 = (cur1 % args.tiles_per_row) * kDenseTile;
+        // operand buffer free again?  (read by the MMAs of k-block it - 1)
+        if (!mbar_wait_bounded(ops_free, ph ^ 1u)) return false;
+        unsigned char *sa = smem + DenseSmem::kStage0;
+        unsigned char *sb = sa + kOperandBytes;
+        mbar_expect_tx(ops_full, DenseSmem::kStageBytes);
+        const int x = kb * 32;
+        tma_load_2d(sa, &map_a, x, r0, ops_full);
+        tma_load_2d(sa + kHalfOperandBytes, &map_a, x, r1, ops_full);
+        tma_load_2d(sb, &map_b, x, c0, ops_full);
+        tma_load_2d(sb + kHalfOperandBytes, &map_b, x, c1, ops_full);
+        return true;
+    };
+    // raw descriptors of one job -> record buffer `buf` (threads 0..127: one tile row each)
+    auto fetch_rows = [&](int job, int buf) {
+        if (tid < 128 && job < n_jobs) {
+            uint4 *dst = sRows + buf * 128 + tid;
+            const int t = 2 * job + (tid >> 6);
+            if (t < args.n_tiles) {
+                const DenseTileDesc *d = args.descs + t;
+                cp_async_4(&dst->x, &d->start[tid & 63]);
+                cp_async_8(&dst->z, &d->mask[tid & 63]);
+            } else {
+                *dst = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+
+    // ---- before the CTA barrier: first operand request (producer), first row records (epilogue warps) ----
+    if (is_producer) {
+        if (my_jobs > 1) load_ids(1, nxt0, nxt1);
+        if (total > 0) prod_ok = issue_tma(0);
+    } else if (warp < kDenseEpiWarps && static_cast<int>(blockIdx.x) < n_jobs) {
+        fetch_rows(blockIdx.x, 0);
+        cp_async_commit();
+    }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -185,50 +260,8 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
 
     if (warp == kDenseEpiWarps) {
         // ===================== producer + MMA issuer (one thread) =====================
-        // Iterations = (job, k-block) pairs of this CTA in order.  The TMA of iteration it + 1 is issued
-        // right after the MMAs of iteration it (it waits for them to release the operand buffer).
         if (lane == 0) {
-            const int kbs = args.k_blocks;
-            const int my_jobs = (n_jobs - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-            const uint32_t total = static_cast<uint32_t>(my_jobs) * static_cast<uint32_t>(kbs);
-            bool ok = true;
-
-            // tile ids of a job (the second tile of the last job may be missing: its operands repeat the first)
-            auto load_ids = [&](uint32_t j, int &t0, int &t1) {
-                const int job = static_cast<int>(blockIdx.x) + static_cast<int>(j) * static_cast<int>(gridDim.x);
-                t0 = args.tile_ids[2 * job];
-                t1 = ((2 * job + 1) < args.n_tiles) ? args.tile_ids[2 * job + 1] : t0;
-            };
-            int cur0 = 0, cur1 = 0, nxt0 = 0, nxt1 = 0;   // ids of the job being requested / of the one after (read a job ahead of their use)
-            if (my_jobs > 0) load_ids(0, cur0, cur1);
-            if (my_jobs > 1) load_ids(1, nxt0, nxt1);
-
-            // request operand k-block `it` (called once per it, in order)
-            auto issue_tma = [&](uint32_t it) -> bool {
-                const uint32_t ph = it & 1u;
-                const uint32_t j = it / kbs;
-                const int kb = static_cast<int>(it % kbs);
-                if (kb == 0 && it > 0) {
-                    cur0 = nxt0;
-                    cur1 = nxt1;
-                    if (j + 1 < static_cast<uint32_t>(my_jobs)) load_ids(j + 1, nxt0, nxt1);
-                }
-                const int r0 = (cur0 / args.tiles_per_row) * kDenseTile, c0 = (cur0 % args.tiles_per_row) * kDenseTile;
-                const int r1 = (cur1 / args.tiles_per_row) * kDenseTile, c1 = (cur1 % args.tiles_per_row) * kDenseTile;
-                // operand buffer free again?  (read by the MMAs of k-block it - 1)
-                if (!mbar_wait_bounded(ops_free, ph ^ 1u)) return false;
-                unsigned char *sa = smem + DenseSmem::kStage0;
-                unsigned char *sb = sa + kOperandBytes;
-                mbar_expect_tx(ops_full, DenseSmem::kStageBytes);
-                const int x = kb * 32;
-                tma_load_2d(sa, &map_a, x, r0, ops_full);
-                tma_load_2d(sa + kHalfOperandBytes, &map_a, x, r1, ops_full);
-                tma_load_2d(sb, &map_b, x, c0, ops_full);
-                tma_load_2d(sb + kHalfOperandBytes, &map_b, x, c1, ops_full);
-                return true;
-            };
-
-            if (total > 0) ok = issue_tma(0);
+            bool ok = prod_ok;
             uint32_t jb = 0;  // jobs whose MMAs have been issued (phase of acc_free / acc_full)
             for (uint32_t it = 0; it < total && ok; ++it) {
                 const int kb = static_cast<int>(it % kbs);
@@ -279,20 +312,6 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
         const uint32_t pbelow = (1u << pshift) - 1u;
         const int stride_jobs = static_cast<int>(gridDim.x);
 
-        // raw descriptors of one job -> record buffer `buf` (threads 0..127: one tile row each) ...
-        auto fetch_rows = [&](int job, int buf) {
-            if (tid < 128 && job < n_jobs) {
-                uint4 *dst = sRows + buf * 128 + tid;
-                const int t = 2 * job + (tid >> 6);
-                if (t < args.n_tiles) {
-                    const DenseTileDesc *d = args.descs + t;
-                    cp_async_4(&dst->x, &d->start[tid & 63]);
-                    cp_async_8(&dst->z, &d->mask[tid & 63]);
-                } else {
-                    *dst = make_uint4(0u, 0u, 0u, 0u);
-                }
-            }
-        };
         // ... and, once they have landed (same thread), the number of 16-byte granules that cover the run
         auto finish_rows = [&](int job, int buf) {
             if (tid < 128 && job < n_jobs) {
@@ -340,9 +359,7 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
 
         uint32_t jb = 0;
         bool ok = true;
-        if (static_cast<int>(blockIdx.x) < n_jobs) {   // first job of the CTA: the only exposed fetches
-            fetch_rows(blockIdx.x, 0);
-            cp_async_commit();
+        if (static_cast<int>(blockIdx.x) < n_jobs) {   // first job of the CTA: the only exposed fetches (requested before the CTA barrier)
             cp_async_wait_group<0>();
             finish_rows(blockIdx.x, 0);
             epi_barrier();

@@ -29,6 +29,7 @@ struct PlanCounters {
     int rowgroups;
     int group_count[9];                  // matching row groups, same slots
     int residual_items;
+    unsigned long long units;            // row segments of the row-segment path
 };
 
 __device__ __forceinline__ int len_bin(int len) {
@@ -114,13 +115,6 @@ __global__ void k_coo_to_row_ptr(const int32_t *__restrict__ row, int64_t nnz, i
         }
         for (int64_t r = prev + 1; r <= cur; ++r) rp[r] = static_cast<int32_t>(j);
     }
-}
-
-// row_ptr slice re-based to start at zero (multi-device row-range shards)
-__global__ void k_rebase(int32_t *__restrict__ rp, int64_t n, int32_t base) {
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
-        rp[i] -= base;
 }
 
 // one thread per work item: rows holding its first and last nonzero
@@ -263,10 +257,14 @@ __global__ void k_split_concat_tf32(const float *__restrict__ in, float *__restr
     }
 }
 
-__global__ void k_f32_to_bf16(const float *__restrict__ in, __nv_bfloat16 *__restrict__ out, int64_t n) {
+// bf16 storage: out = bf16(in), and `in` keeps the rounded value (as fp32) for the tensor-core path
+__global__ void k_f32_to_bf16(float *__restrict__ in, __nv_bfloat16 *__restrict__ out, int64_t n) {
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
-        out[i] = __float2bfloat16_rn(in[i]);
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const __nv_bfloat16 r = __float2bfloat16_rn(in[i]);
+        out[i] = r;
+        in[i] = __bfloat162float(r);
+    }
 }
 
 }  // namespace sddmm

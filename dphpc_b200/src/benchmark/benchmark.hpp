@@ -3,9 +3,10 @@
 // Same flow and CSV schema as the reference's SDDMM::Benchmark<T> (src/benchmark/benchmark.hpp:45-190;
 // schema: src/main.cpp:355-358) so its plot scripts read the output unchanged:
 //   competitor,dataset,mat_repr,M,N,K,NZ,total_ns,init_ns,comp_ns,cleanup_ns,correctness,num_thread_blocks,num_threads_per_block
-// Timing: host clock around each phase; GPU competitors' compute phase is taken from the device
-// (the engine's own CUDA events around its kernels) when the competitor offers it, since the
+// Timing: host clock around each phase; a GPU competitor's compute phase is taken from the device
+// (its own CUDA events around its kernels) when it implements SDDMM::DeviceTimed, since the
 // reference's event pair on the legacy default stream (:160-164) cannot see another stream.
+// The harness names no concrete competitor.
 // If the dataset carries no expected result, the first competitor provides it (reference: :50-61).
 #pragma once
 #include <chrono>
@@ -16,8 +17,7 @@
 #include <vector>
 
 #include "competitor.hpp"
-#include "competitors/gpu/gpu_b200.hpp"
-#include "competitors/gpu/gpu_b200_multi.hpp"
+#include "competitors/gpu/device_timed.hpp"
 #include "dataset.hpp"
 #include "utils/util.hpp"
 
@@ -102,9 +102,8 @@ private:
         timing_result r;
         r.comp_ns = ns(t1, t2);
         if (c->is_gpu()) {
-            float ms = 0.f;   // the engine's own device time instead of the host clock around run_*
-            if (auto *eng = dynamic_cast<Competitors::GPUB200 *>(c)) ms = eng->last_kernel_ms();
-            else if (auto *multi = dynamic_cast<Competitors::GPUB200Multi *>(c)) ms = multi->last_kernel_ms();
+            float ms = 0.f;   // the competitor's own device time, if it offers one, instead of the host clock around run_*
+            if (auto *timed = dynamic_cast<DeviceTimed *>(c)) ms = timed->last_kernel_ms();
             if (ms > 0.f) r.comp_ns = static_cast<uint64_t>(static_cast<double>(ms) * 1e6);
         }
         cleanup();

@@ -21,12 +21,13 @@
 #include <string>
 
 #include "benchmark/competitor.hpp"
+#include "device_timed.hpp"
 #include "matrices/matrices.h"
 #include "sddmm_b200.h"
 
 namespace Competitors {
 
-class GPUB200 : public SDDMM::Competitor<float> {
+class GPUB200 : public SDDMM::Competitor<float>, public SDDMM::DeviceTimed {
     using T = float;
 
 public:
@@ -78,7 +79,7 @@ public:
     bool is_gpu() override { return true; }
 
     // device time of the kernels of the last run_* (ms); the harness' own event pair also sees launch overhead
-    float last_kernel_ms() {
+    float last_kernel_ms() override {
         float ms = 0.f;
         if (ready_) sddmm_b200_last_run_ms(engine_, &ms);
         return ms;
@@ -108,7 +109,8 @@ private:
         if (!ready_) return;
         sddmm_b200_plan_info info;
         if (sddmm_b200_get_plan(engine_, &info) == SDDMM_B200_OK) {
-            set_num_thread_blocks(info.dense_tiles > 0 ? info.dense_grid : info.rowtile_grid);
+            set_num_thread_blocks(info.dense_tiles > 0 ? info.dense_grid : info.rowgroup_rows > 0 ? info.rowgroup_grid
+                                  : info.rowseg_units > 0 ? info.rowseg_grid : info.rowtile_grid);
             set_num_threads_per_block(info.dense_tiles > 0 ? info.dense_block : info.rowtile_block);
         }
     }

@@ -25,12 +25,13 @@
 #include <vector>
 
 #include "benchmark/competitor.hpp"
+#include "device_timed.hpp"
 #include "matrices/matrices.h"
 #include "sddmm_b200.h"
 
 namespace Competitors {
 
-class GPUB200Multi : public SDDMM::Competitor<float> {
+class GPUB200Multi : public SDDMM::Competitor<float>, public SDDMM::DeviceTimed {
     using T = float;
 
 public:
@@ -130,7 +131,7 @@ public:
     int shards() const { return static_cast<int>(engines_.size()); }
     const std::vector<int64_t> &cuts() const { return cuts_; }        // rows of shard g: [cuts[g], cuts[g+1])
     // device time of the slowest shard in the last run_* (ms)
-    float last_kernel_ms() {
+    float last_kernel_ms() override {
         float worst = 0.f;
         for (int g = 0; ready_ && g < shards(); ++g) {
             float ms = 0.f;
@@ -195,7 +196,8 @@ private:
         for (int g = 0; g < shards(); ++g) {
             sddmm_b200_plan_info info;
             if (active(g) && sddmm_b200_get_plan(engines_[static_cast<size_t>(g)], &info) == SDDMM_B200_OK) {
-                blocks += info.dense_tiles > 0 ? info.dense_grid : (info.rowgroup_rows > 0 ? info.rowgroup_grid : info.rowtile_grid);
+                blocks += info.dense_tiles > 0 ? info.dense_grid : info.rowgroup_rows > 0 ? info.rowgroup_grid
+                          : info.rowseg_units > 0 ? info.rowseg_grid : info.rowtile_grid;
                 threads = info.dense_tiles > 0 ? info.dense_block : info.rowtile_block;
             }
         }

@@ -3,8 +3,10 @@
 // --data_folder is accepted and ignored) plus --config, --scale, --mode, and --mtx FILE (MatrixMarket coordinate file) or
 // --edges FILE --rows M --cols N (SNAP edge list), read with the reference's rules (src/benchmark/dataset.hpp:122-181, 270-313);
 // --multi adds the row-sharded competitor that uses every visible GPU from this one process.
-// The first competitor is the correctness baseline of the harness; here that is GPU-B200 in fp32
-// mode (the independent CPU check lives in the test-suite, not in this binary).
+// The first competitor is the correctness baseline of the harness (src/benchmark/benchmark.hpp:50-61): CPU-Basic, as in
+// the reference's driver (src/main.cpp:18-20), so every GPU row's `correctness` is a comparison with the host
+// computation.  --no_cpu drops it (the baseline is then GPU-B200 in fp32 mode and the column only says that the
+// other modes agree with it).
 #include <cstdlib>
 #include <cstring>
 #include <iostream>
@@ -13,6 +15,9 @@
 #include <vector>
 
 #include "benchmark/benchmark.hpp"
+#include "competitors/cpu/cpu_check.hpp"
+#include "competitors/gpu/gpu_b200.hpp"
+#include "competitors/gpu/gpu_b200_multi.hpp"
 
 namespace {
 
@@ -22,6 +27,7 @@ struct Options {
     double scale = 1.0;
     bool header = true;
     bool multi = false;   // also run the row-sharded competitor on every visible GPU
+    bool cpu = true;      // CPU-Basic first: the correctness baseline
     std::vector<std::string> modes{"fp32", "fp32_tc"};   // tf32 / bf16 on request: their 1e-2 error fails the 1e-3 check
 };
 
@@ -35,7 +41,7 @@ int mode_id(const std::string &m) {
 
 void usage() {
     std::cerr << "usage: sddmm_bench [--config 1..5 (default: all) | --mtx FILE | --edges FILE --rows M --cols N] [-k K] [--num_runs R] [--scale s]"
-                 " [--mode fp32,tf32,...] [--multi] [--no_csv_header]\n";
+                 " [--mode fp32,tf32,...] [--multi] [--no_cpu] [--no_csv_header]\n";
 }
 
 }  // namespace
@@ -56,6 +62,7 @@ int main(int argc, char **argv) {
         else if (a == "--scale") o.scale = std::atof(next());
         else if (a == "--no_csv_header") o.header = false;
         else if (a == "--multi") o.multi = true;
+        else if (a == "--no_cpu") o.cpu = false;
         else if (a == "-d" || a == "--data_folder") next();
         else if (a == "--mode") {
             o.modes.clear();
@@ -71,6 +78,7 @@ int main(int argc, char **argv) {
         return 1;
     }
     std::vector<std::shared_ptr<SDDMM::Competitor<float>>> competitors;
+    if (o.cpu) competitors.push_back(std::make_shared<Competitors::CPUCheck>());
     competitors.push_back(std::make_shared<Competitors::GPUB200>(SDDMM_B200_FP32, 0, "GPU-B200"));
     for (const std::string &m : o.modes) {
         const int id = mode_id(m);

@@ -51,7 +51,8 @@ enum {
 /* flags for sddmm_b200_create */
 enum {
     SDDMM_B200_FLAG_NO_DENSE_TILES = 1u << 0, /* never take the tensor-core tile path */
-    SDDMM_B200_FLAG_NO_ROW_GROUPS  = 1u << 1  /* never merge rows with identical column lists */
+    SDDMM_B200_FLAG_NO_ROW_GROUPS  = 1u << 1, /* never merge rows with identical column lists */
+    SDDMM_B200_FLAG_NO_ROW_SEGMENTS = 1u << 2 /* never take the row-segment kernel (the A-row-tile kernel runs instead) */
 };
 
 #define SDDMM_B200_HIST_BINS 20
@@ -82,6 +83,12 @@ typedef struct sddmm_b200_plan_info {
     int32_t rowgroup_grid;
     int32_t n_kernels;             /* kernels one run() launches                      */
     int32_t n_devices;
+    /* row segments (rows cut into pieces of at most 8 nonzeros; the path for short and power-law rows) */
+    int64_t rowseg_nnz;            /* nonzeros handled by the row-segment kernel      */
+    int32_t rowseg_units;          /* segments                                        */
+    int32_t rowseg_panels;         /* column panels the segment list is ordered by (1: none) */
+    int32_t rowseg_grid;
+    int32_t reserved0;
 } sddmm_b200_plan_info;
 
 /* ---- life cycle ---------------------------------------------------------
@@ -144,6 +151,16 @@ int sddmm_b200_last_run_ms(sddmm_b200_engine *e, float *ms);
 int sddmm_b200_last_kernel_ms(sddmm_b200_engine *e, int index, float *ms, const char **name);
 int sddmm_b200_set_kernel_timing(sddmm_b200_engine *e, int enabled);
 int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info);
+/* Tuning knobs of the planner (the thread-grid command-line options of the reference's driver, src/main.cpp:326-348, and
+ * the density threshold of GPUDynamic, src/competitors/gpu/gpu_dynamic.hpp:72-73, play this role there).  A negative
+ * value hands the decision back to the planner; a knob takes effect at the next upload (the two cache knobs at the
+ * next run).  Defaults come from the environment variables SDDMM_B200_<NAME IN CAPITALS> at create.
+ *   "panels"        column panels of the row-segment path (1..64)
+ *   "panel_mb"      target size of one panel of B in MiB
+ *   "rowseg"        0: never take the row-segment kernel, 1: take it whenever it applies
+ *   "b_evict_last"  0/1: gathers of B carry an L2 evict_last hint
+ *   "b_fraction"    share of the B lines that hint applies to, (0, 1] */
+int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value);
 /* compulsory traffic e*K*(M+ + N+) + 12*nnz + 4*(M+1) with e = bytes per stored
  * element of A/B; extends the read-only model of plots/plot_roofline.py:30 */
 int64_t sddmm_b200_algorithmic_bytes(sddmm_b200_engine *e);
@@ -168,6 +185,10 @@ const char *sddmm_b200_version(void);
  *
  *   - fp32, CSR, K % 4 == 0 and K <= 256, nnz <= 2^27 (134 217 728); anything else returns
  *     SDDMM_B200_ERR_UNSUPPORTED and touches nothing.  row_ptr/col_idx are trusted (not validated).
+ *   - alignment: d_col_idx, d_A and d_B must be 16-byte aligned (the kernel reads them with 128-bit
+ *     accesses), d_row_ptr, d_s_val and d_p_val 4-byte aligned; a row-shard slice such as
+ *     d_col_idx + offset qualifies only when offset % 4 == 0.  Anything else returns
+ *     SDDMM_B200_ERR_ARG before any launch.
  *   - synchronous: work is enqueued on `cuda_stream` (a cudaStream_t, may be 0) and the call
  *     returns after that stream has drained.
  *   - the first call on a device looks up the array's device address; make that call outside

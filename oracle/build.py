@@ -23,6 +23,7 @@ HERE = Path(__file__).resolve().parent
 ORACLE_LIB = HERE / "liboracle.so"
 REF_DIR = HERE / "_ref"
 REF_LIB = REF_DIR / "libsddmm_ref.so"
+REF_HARNESS = REF_DIR / "ref_harness_bench"
 # the reference checkout: SDDMM_REFERENCE_ROOT, else a directory "reference" beside this repository
 REFERENCE_ROOT = Path(os.environ.get("SDDMM_REFERENCE_ROOT", str(HERE.parent.parent / "reference")))
 CUDA_INCLUDE = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
@@ -69,6 +70,30 @@ def build_ref(force: bool = False):
     return REF_LIB
 
 
+def build_ref_harness(force: bool = False):
+    """The reference's unmodified Benchmark<T> + datasets + CPU-Basic, with this repository's GPU-B200 competitor
+    registered next to it (oracle/ref_harness_main.cpp); links the CUDA runtime (the harness times with CUDA events)
+    and the engine's C-ABI library.  Returns None when the reference, the CUDA runtime or the engine library is absent."""
+    pkg = HERE.parent / "dphpc_b200"
+    cuda_lib = CUDA_INCLUDE.parent / "lib64"
+    if not reference_present() or not (pkg / "libsddmm_b200.so").exists() or not cuda_lib.exists():
+        return REF_HARNESS if REF_HARNESS.exists() else None
+    src = HERE / "ref_harness_main.cpp"
+    deps = [src, pkg / "src" / "competitors" / "gpu" / "gpu_b200.hpp", HERE.parent / "include" / "sddmm_b200.h"]
+    if force or _stale(REF_HARNESS, deps):
+        REF_DIR.mkdir(exist_ok=True)
+        _run([
+            "g++", "-std=c++17", "-O2", "-w", "-include", "cstdint", "-include", "cassert",
+            "-I", str(REFERENCE_ROOT / "src"), "-I", str(CUDA_INCLUDE), "-I", str(HERE.parent / "include"),
+            "-idirafter", str(pkg / "src"),   # only gpu_b200.hpp comes from here: every other header is the reference's
+            "-o", str(REF_HARNESS), str(src),
+            "-L", str(pkg), "-lsddmm_b200", "-L", str(cuda_lib), "-lcudart",
+            "-Wl,-rpath,$ORIGIN/../../dphpc_b200", f"-Wl,-rpath,{cuda_lib}", "-pthread",
+        ])
+    return REF_HARNESS
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
+    print(build_ref_harness(force="--force" in sys.argv))

@@ -218,3 +218,55 @@ def assert_values_close(p, p_ref, bound, tol, what=""):
         i = int(np.argmax(err / np.maximum(lim, 1e-300)))
         raise AssertionError(f"{what}: {int(bad.sum())} of {p.size} values off; worst at {i}: got {p[i]!r} want {p_ref[i]!r} "
                              f"err {err[i]:.3e} limit {lim[i]:.3e}")
+
+
+def host_threads(limit=32):
+    import os
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, min(limit, n))
+
+
+def sddmm_csr_all_rows(oracle, M, K, row_ptr, col_idx, s_val, A, B, threads=None):
+    """The oracle over EVERY row, the rows cut into nnz-balanced ranges that run on a thread pool (each range is one
+    call of the same C loop; ctypes releases the GIL).  Bit-identical to one call over all rows."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    row_ptr, col_idx, s_val, A, B = _i32(row_ptr), _i32(col_idx), _f32(s_val), _f32(A), _f32(B)
+    nnz = int(row_ptr[M])
+    out = np.empty(nnz, np.float32)
+    threads = threads or host_threads()
+    cuts = np.unique(np.concatenate([[0], np.searchsorted(row_ptr, np.arange(1, threads) * (nnz / threads)), [M]]).astype(np.int64))
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        list(pool.map(lambda ab: oracle.sddmm_csr_rows(int(ab[0]), int(ab[1]), K, row_ptr, col_idx, s_val, A, B, out),
+                      zip(cuts[:-1], cuts[1:])))
+    return out
+
+
+def abs_dot_bound_all_rows(oracle, M, K, row_ptr, col_idx, s_val, A, B, threads=None):
+    """|s_ij| * sum_k |a_ik b_jk| for every nonzero of a CSR matrix: the oracle's own loop on the absolute values
+    (fp32 accumulation of non-negative terms: relative error ~K * 2^-24, widened by the factor below)."""
+    b = sddmm_csr_all_rows(oracle, M, K, row_ptr, col_idx, np.abs(_f32(s_val)), np.abs(_f32(A)), np.abs(_f32(B)), threads)
+    return b.astype(np.float64) * (1.0 + 1e-4)
+
+
+def abs_dot_bound_rows(row_ptr, col_idx, s_val, A, B, threads=None, chunk=1 << 19):
+    """abs_dot_bound for a whole CSR matrix (row indices expanded chunk by chunk, chunks on a thread pool)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    row_ptr = np.asarray(row_ptr, np.int64)
+    nnz = int(row_ptr[-1])
+    A32, B32 = np.abs(np.asarray(A, np.float32)), np.abs(np.asarray(B, np.float32))
+    out = np.empty(nnz, np.float64)
+
+    def work(a):
+        b = min(nnz, a + chunk)
+        rows = np.searchsorted(row_ptr, np.arange(a, b), side="right") - 1
+        prod = np.einsum("ik,ik->i", A32[rows].astype(np.float64), B32[col_idx[a:b]].astype(np.float64))
+        out[a:b] = prod * np.abs(np.asarray(s_val[a:b], np.float64))
+
+    with ThreadPoolExecutor(max_workers=threads or host_threads()) as pool:
+        list(pool.map(work, range(0, nnz, chunk)))
+    return out

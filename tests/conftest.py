@@ -7,8 +7,8 @@ import pytest
 ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
-if str(ROOT / "tests") not in sys.path:
-    sys.path.insert(0, str(ROOT / "tests"))
+if str(ROOT / "oracle") not in sys.path:
+    sys.path.insert(0, str(ROOT / "oracle"))   # oracle_lib: the CPU checker's bindings
 
 
 def pytest_configure(config):
@@ -30,6 +30,7 @@ def _native_built():
     ob.build_ref()
     pkg_build.build_datasets()
     pkg_build.build_engine()
+    ob.build_ref_harness()   # (needs the engine library; only where the reference checkout is present)
     yield
 
 

@@ -9,6 +9,9 @@
 
 #include "benchmark/benchmark.hpp"
 #include "check.hpp"
+#include "competitors/cpu/cpu_check.hpp"
+#include "competitors/gpu/gpu_b200.hpp"
+#include "competitors/gpu/gpu_b200_multi.hpp"
 
 extern "C" {
 void oracle_sddmm_csr(int32_t M, int32_t K, const int32_t *row_ptr, const int32_t *col_idx, const float *s_val, const float *A,

@@ -22,7 +22,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
-sys.path.insert(0, str(ROOT / "tests"))
+sys.path.insert(0, str(ROOT / "oracle"))
 
 import oracle_lib  # noqa: E402
 from dphpc_b200 import Dataset  # noqa: E402

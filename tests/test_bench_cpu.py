@@ -44,3 +44,21 @@ def test_row_sharded_cpu_baseline_covers_every_nonzero_once(oracle):
             assert shards.step() > 0
         finally:
             shards.close()
+
+
+def test_roofline_script_reads_the_driver_csv(tmp_path):
+    # the corrected-constants roofline table over the benchmark driver's CSV schema (plot only where matplotlib exists)
+    csv = tmp_path / "runs.csv"
+    csv.write_text("competitor,dataset,mat_repr,M,N,K,NZ,total_ns,init_ns,comp_ns,cleanup_ns,correctness,num_thread_blocks,num_threads_per_block\n"
+                   "GPU-B200,cfg,CSR,1000,1000,32,50000,900000,500000,100000,300000,1,10,256\n"
+                   "GPU-B200,cfg,CSR,1000,1000,32,50000,900000,500000,300000,300000,1,10,256\n"
+                   "GPU-B200,cfg,CSR,1000,1000,32,50000,900000,500000,200000,300000,0,10,256\n")
+    res = subprocess.run([sys.executable, str(ROOT / "dphpc_b200" / "plots" / "plot_roofline.py"), str(csv), "--hbm-gbs", "1000",
+                          "--out", str(tmp_path / "r.png")], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0, res.stderr[-2000:]
+    rows = [ln.split(",") for ln in res.stdout.splitlines() if ln.startswith("GPU-B200")]
+    assert len(rows) == 1
+    flops, nbytes, secs = 2 * 32 * 50000 + 50000, 4 * 32 * 2000 + 12 * 50000 + 4 * 1001, 200000e-9   # median of the two correct runs
+    assert abs(float(rows[0][4]) - flops / nbytes) < 1e-4 * flops / nbytes
+    assert abs(float(rows[0][5]) - flops / secs) < 1e-4 * flops / secs
+    assert abs(float(rows[0][7]) - (nbytes / secs) / 1e12) < 1e-4      # fraction of the 1000 GB/s roof

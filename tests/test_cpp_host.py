@@ -95,3 +95,24 @@ def test_benchmark_driver_reads_matrix_files(tmp_path):
         header = next(ln.split(",") for ln in res.stdout.splitlines() if ln.startswith("competitor"))
         ci = header.index("correctness")
         assert len(rows) >= 2 and all(r[ci].strip() == "1" for r in rows), res.stdout[-2000:]
+
+
+@pytest.mark.gpu
+def test_competitor_under_the_reference_harness_unmodified():
+    # oracle/_ref/ref_harness_bench = the reference's own Benchmark<float>, datasets and CPU-Basic (first competitor =
+    # correctness baseline) compiled from its sources where they lie, with GPU-B200 registered beside it.  The binary is
+    # built where the reference checkout is present and travels as a prebuilt file.
+    exe = ROOT / "oracle" / "_ref" / "ref_harness_bench"
+    if not exe.exists():
+        pytest.skip("oracle/_ref/ref_harness_bench not built (reference checkout absent)")
+    res = subprocess.run([str(exe), "2"], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    rows = [ln.split(",") for ln in res.stdout.splitlines() if ln.count(",") >= 13]
+    mine = [r for r in rows if r[0].startswith("GPU-B200")]
+    datasets = {r[1] for r in mine}
+    assert {"Dummy", "RandomWithDensity", "LatinHypercube"} <= datasets, res.stdout[-3000:]
+    assert {r[2] for r in mine} == {"CSR", "COO"}
+    wrong = [r[:3] for r in mine if r[11].strip() != "1"]
+    assert not wrong, f"correctness = 0 under the reference's harness: {wrong}\n{res.stderr[-2000:]}"
+    assert all(int(r[9]) > 0 for r in mine)   # the harness' own CUDA-event pair saw the compute phase
+    assert "entry_device_kept=1" in res.stdout

@@ -58,7 +58,7 @@ def _rank_main(rank, world, port, out_dir):
     import torch.distributed as dist
 
     sys.path.insert(0, str(ROOT))
-    sys.path.insert(0, str(ROOT / "tests"))
+    sys.path.insert(0, str(ROOT / "oracle"))
     import oracle_lib
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))

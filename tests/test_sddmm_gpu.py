@@ -225,23 +225,24 @@ def test_update_values_and_dense_keep_the_plan(engines, oracle):
     assert np.array_equal(e.download(), p1)
 
 
-# ---- full BASELINE sizes: size-independent properties + sampled comparison --------------------------
-@pytest.mark.parametrize("cfg,K,mode", [(2, 32, "fp32"), (2, 32, "fp32_tc"), (2, 32, "tf32"), (3, 64, "fp32"), (4, 32, "fp32"),
-                                        (5, 32, "fp32"), (5, 32, "bf16"), (2, 64, "fp32_tc"), (3, 32, "fp32_tc"), (5, 128, "bf16")])
-def test_full_size_properties(engines, oracle, cfg, K, mode):
+# ---- full BASELINE sizes: EVERY nonzero against the oracle, plus size-independent properties --------------------------
+def full_compare(p, d, oracle, tol, what):
+    """All nonzeros of a full-size result against the CPU oracle (row ranges on a thread pool)."""
+    ref = oracle_lib.sddmm_csr_all_rows(oracle, d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    bound = oracle_lib.abs_dot_bound_all_rows(oracle, d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    oracle_lib.assert_values_close(p, ref, bound, tol, what)
+    return ref, bound
+
+
+@pytest.mark.parametrize("cfg,K,mode", [(2, 32, "fp32"), (2, 32, "fp32_tc"), (2, 32, "tf32"), (2, 32, "bf16"), (3, 64, "fp32"),
+                                        (4, 32, "fp32"), (4, 32, "bf16"), (5, 32, "fp32"), (5, 32, "bf16"), (2, 64, "fp32_tc"),
+                                        (3, 32, "fp32_tc"), (5, 128, "bf16"), (5, 64, "fp32")])
+def test_full_size_all_nonzeros(engines, oracle, cfg, K, mode):
     d = Dataset(cfg, K, 1.0)
     e = engines[mode]
     p = e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
-    assert np.isfinite(p).all()
-    # (a) a slice of rows from the middle and the ends against the oracle
-    for r0 in (0, d.M // 2, d.M - 2000):
-        r1 = r0 + 2000
-        a, b = int(d.row_ptr[r0]), int(d.row_ptr[r1])
-        ref = np.zeros(d.nnz, np.float32)
-        oracle.sddmm_csr_rows(r0, r1, d.K, d.row_ptr, d.col_idx, d.s_val, np.ascontiguousarray(d.A), np.ascontiguousarray(d.B), ref)
-        rows = np.repeat(np.arange(r0, r1), np.diff(d.row_ptr[r0:r1 + 1]))
-        bound = oracle_lib.abs_dot_bound(rows, d.col_idx[a:b], d.s_val[a:b], d.A, d.B)
-        oracle_lib.assert_values_close(p[a:b], ref[a:b], bound, TOL[mode], f"cfg{cfg} rows {r0}..{r1}")
+    # (a) every nonzero against the oracle
+    full_compare(p, d, oracle, TOL[mode], f"cfg{cfg} K={K} {mode} full size")
     # (b) 200 000 random nonzeros against a float64 dot product
     rng = np.random.default_rng(cfg)
     idx = np.sort(rng.choice(d.nnz, 200000, replace=False))
@@ -259,6 +260,150 @@ def test_full_size_properties(engines, oracle, cfg, K, mode):
     # (d) COO upload gives the same bits
     if cfg in (2, 5):
         assert np.array_equal(e.sddmm_coo(d.M, d.N, d.K, d.row_idx(), d.col_idx, d.s_val, d.A, d.B), p)
+    d.close()
+
+
+@pytest.mark.parametrize("mode", ["fp32_tc", "tf32", "bf16", "fp32"])
+def test_full_size_config2_randomly_placed_blocks(engines, oracle, mode):
+    # configs[1] as BASELINE words it: 64x64 blocks at arbitrary (not grid-aligned) offsets
+    d = Dataset(2, 32, 1.0, variant=1)
+    p = engines[mode].sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    full_compare(p, d, oracle, TOL[mode], f"cfg2 unaligned blocks {mode} full size")
+    d.close()
+
+
+def test_golden_and_config1_against_the_reference_itself(engines, ref, oracle):
+    # where the reference's own CPU path is at hand (oracle/_ref: its headers compiled unmodified) the GPU result is
+    # compared with IT, not only with the restatement
+    f = lambda b: np.array(b, np.uint32).view(np.float32)  # noqa: E731
+    for name in sorted(GOLD["random"]):
+        g = GOLD["random"][name]
+        A, B = f(g["A_bits"]).reshape(g["M"], g["K"]), f(g["B_bits"]).reshape(g["N"], g["K"])
+        rp, ci, sv = np.array(g["row_ptr"], np.int32), np.array(g["col_idx"], np.int32), f(g["s_val_bits"])
+        want = ref.cpu_basic_csr(g["M"], g["N"], g["K"], rp, ci, sv, A, B)
+        bound = oracle_lib.abs_dot_bound(oracle.coo_rows(g["M"], rp), ci, sv, A, B)
+        for mode in ("fp32", "fp32_tc"):
+            oracle_lib.assert_values_close(engines[mode].sddmm_csr(g["M"], g["N"], g["K"], rp, ci, sv, A, B), want, bound, 1e-5, name)
+    for cfg, scale, K in ((1, 1.0, 32), (2, 0.05, 32), (4, 0.002, 32), (5, 0.003, 64)):
+        d = Dataset(cfg, K, scale)
+        want = ref.cpu_basic_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        want_coo = ref.cpu_basic_coo(d.M, d.N, d.K, d.row_idx(), d.col_idx, d.s_val, d.A, d.B)
+        bound = oracle_lib.abs_dot_bound(oracle.coo_rows(d.M, d.row_ptr), d.col_idx, d.s_val, d.A, d.B)
+        for mode in MODES:
+            oracle_lib.assert_values_close(engines[mode].sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B), want, bound,
+                                           TOL[mode], f"cfg{cfg} {mode} vs reference CSR")
+            oracle_lib.assert_values_close(engines[mode].sddmm_coo(d.M, d.N, d.K, d.row_idx(), d.col_idx, d.s_val, d.A, d.B), want_coo,
+                                           bound, TOL[mode], f"cfg{cfg} {mode} vs reference COO")
+        d.close()
+
+
+# ---- the row-segment kernel and its column panels -------------------------------------------------------------
+@pytest.mark.parametrize("cfg,scale,K,mode,panels", [(5, 0.01, 32, "fp32", 1), (5, 0.01, 32, "fp32", 3), (5, 0.01, 64, "fp32", 4),
+                                                      (4, 0.01, 32, "fp32", 2), (4, 0.01, 32, "bf16", 5), (5, 0.005, 128, "bf16", 2),
+                                                      (5, 0.004, 256, "fp32", 3), (5, 0.01, 36, "fp32", 2), (2, 0.1, 32, "fp32", 7),
+                                                      (1, 1.0, 32, "fp32", 64)])
+def test_row_segments_and_column_panels(oracle, cfg, scale, K, mode, panels):
+    # rows cut into segments of at most 8 nonzeros; with column panels the segment list is ordered panel-major
+    d = Dataset(cfg, K, scale)
+    e = Engine(0, mode)
+    try:
+        e.set_knob("rowseg", 1)
+        e.set_knob("panels", panels)
+        p = check(e, mode, oracle, d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, what=f"row segments cfg{cfg} K={K} {mode} P={panels}")
+        plan = e.plan()
+        assert [n for n, _ in e.kernel_times()] == ["sddmm_rowseg_kernel"]
+        assert plan["rowseg_nnz"] == d.nnz and plan["rowseg_panels"] == panels and plan["rowtile_nnz"] == 0
+        lens = np.diff(d.row_ptr).astype(np.int64)
+        if panels == 1:
+            assert plan["rowseg_units"] == int(((lens + 7) // 8).sum())
+        else:
+            assert int(((lens + 7) // 8).sum()) <= plan["rowseg_units"] <= d.nnz // 8 + min(d.nnz, d.M * panels)
+        p_coo = check(e, mode, oracle, d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, coo=True, what="row segments coo")
+        assert np.array_equal(p, p_coo)
+        # the same input through the A-row-tile kernel
+        e2 = Engine(0, mode, flags=4)
+        q = e2.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        assert [n for n, _ in e2.kernel_times()] == ["sddmm_rowtile_kernel"] and e2.plan()["rowseg_units"] == 0
+        e2.close()
+        bound = oracle_lib.abs_dot_bound(oracle.coo_rows(d.M, d.row_ptr), d.col_idx, d.s_val, d.A, d.B)
+        oracle_lib.assert_values_close(q, p, bound, 2 * TOL[mode], "row-segment kernel vs row-tile kernel")
+    finally:
+        e.close()
+        d.close()
+
+
+def test_row_segments_edge_shapes(oracle):
+    rng = np.random.default_rng(12)
+    e = Engine(0, "fp32")
+    e.set_knob("rowseg", 1)
+    e.set_knob("panels", 3)
+
+    def dense(m, k):
+        return rng.uniform(-1, 1, (m, k)).astype(np.float32)
+
+    try:
+        # one 50 000-nnz row between empty rows; rows of exactly 8, 9, 1 nonzeros; a single column
+        N = 60000
+        cols = np.sort(rng.choice(N, 50000, replace=False)).astype(np.int32)
+        check(e, "fp32", oracle, 4, N, 32, [0, 0, 50000, 50000, 50000], cols, rng.random(50000, dtype=np.float32), dense(4, 32), dense(N, 32),
+              what="segments: one long row")
+        lens = [8, 9, 1, 0, 16, 7, 0, 0, 33]
+        rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        ci = np.concatenate([np.sort(rng.choice(100, n, replace=False)) for n in lens]).astype(np.int32)
+        check(e, "fp32", oracle, len(lens), 100, 20, rp, ci, rng.random(ci.size, dtype=np.float32), dense(len(lens), 20), dense(100, 20),
+              what="segments: ragged rows")
+        assert e.plan()["rowseg_panels"] == 3
+        check(e, "fp32", oracle, 5, 1, 4, [0, 1, 1, 2, 3, 3], [0, 0, 0], [1, 2, 3], dense(5, 4), dense(1, 4), what="segments: N=1")
+        # unsorted columns inside rows: a panel run would not be contiguous, so the list is built without panels
+        d = Dataset(uniform=(200, 300, 5000), K=32, seed=2)
+        ci = d.col_idx.copy()
+        for i in range(d.M):
+            a, b = d.row_ptr[i], d.row_ptr[i + 1]
+            ci[a:b] = rng.permutation(ci[a:b])
+        check(e, "fp32", oracle, d.M, d.N, d.K, d.row_ptr, ci, d.s_val, d.A, d.B, what="segments: unsorted columns")
+        assert e.plan()["rowseg_panels"] == 1 and e.plan()["rowseg_units"] > 0
+        # K the chunked kernels cannot take falls to the scalar kernel whatever the knob says
+        check(e, "fp32", oracle, d.M, d.N, 3, d.row_ptr, d.col_idx, d.s_val, dense(d.M, 3), dense(d.N, 3), what="segments: K=3")
+        assert e.plan()["rowseg_units"] == 0
+    finally:
+        e.close()
+
+
+def test_two_engines_on_one_device_keep_their_launch_limits(oracle):
+    # the dynamic shared memory limit of a kernel belongs to the device, not to an engine: an engine whose rows are short
+    # (small stage) must not leave another engine, whose plan needs a large stage, with a limit below its launch
+    long_rows = Dataset(uniform=(600, 4000, 600 * 400), K=32, seed=3)      # mean row length 400 -> few rows per stage
+    short_rows = Dataset(uniform=(60000, 4000, 60000 * 4), K=32, seed=4)   # mean row length 4 -> 256 rows per stage
+    a, b = Engine(0, "fp32", flags=4), Engine(0, "fp32", flags=4)          # (flags=4: the row-tile kernel)
+    try:
+        b.upload_csr(short_rows.M, short_rows.N, 32, short_rows.row_ptr, short_rows.col_idx, short_rows.s_val, short_rows.A, short_rows.B)
+        a.upload_csr(long_rows.M, long_rows.N, 32, long_rows.row_ptr, long_rows.col_idx, long_rows.s_val, long_rows.A, long_rows.B)
+        assert b.plan()["rowtile_smem_bytes"] > a.plan()["rowtile_smem_bytes"]
+        for eng, d in ((b, short_rows), (a, long_rows), (b, short_rows)):
+            eng.run()
+            p = eng.download()
+            want = oracle.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+            bound = oracle_lib.abs_dot_bound(oracle.coo_rows(d.M, d.row_ptr), d.col_idx, d.s_val, d.A, d.B)
+            oracle_lib.assert_values_close(p, want, bound, 1e-5, "two engines on one device")
+    finally:
+        a.close()
+        b.close()
+    # chunked call whose first half has short rows and whose second half has long ones, then the pattern replayed
+    rp = np.concatenate([short_rows.row_ptr, long_rows.row_ptr[1:] + short_rows.row_ptr[-1]]).astype(np.int32)
+    ci = np.concatenate([short_rows.col_idx, long_rows.col_idx])
+    sv = np.concatenate([short_rows.s_val, long_rows.s_val])
+    A = np.concatenate([short_rows.A, long_rows.A])
+    B = short_rows.B
+    M = rp.size - 1
+    want = oracle.sddmm_csr(M, 32, rp, ci, sv, A, B)
+    bound = oracle_lib.abs_dot_bound(oracle.coo_rows(M, rp), ci, sv, A, B)
+    with Pipeline(0, "fp32", flags=4, chunks=2, min_chunk_bytes=1 << 20) as pl:
+        p = pl.sddmm_csr(M, 4000, 32, rp, ci, sv, A, B)
+        assert pl.last_chunks() == 2
+        oracle_lib.assert_values_close(p, want, bound, 1e-5, "chunked call, short then long rows")
+        out = np.zeros(ci.size, np.float32)
+        pl.update_csr_raw(sv, A, B, out)
+        oracle_lib.assert_values_close(out, want, bound, 1e-5, "chunked call replayed")
 
 
 def _blocked_pattern(rng, n_block_rows, G, N, blocks_per_row, break_every=0):
@@ -321,7 +466,7 @@ def test_row_groups_not_taken_without_structure(engines):
     d = Dataset(5, 32, 0.002)
     e = engines["fp32"]
     e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
-    assert e.plan()["rowgroup_rows"] == 0 and e.plan()["rowtile_nnz"] == d.nnz
+    assert e.plan()["rowgroup_rows"] == 0 and e.plan()["rowseg_nnz"] + e.plan()["rowtile_nnz"] == d.nnz
 
 
 def test_kernel_timing_is_opt_in():

@@ -5,7 +5,9 @@ allocator owns the whole GPU, a latency-critical loop that must not take the all
 synchronisation.  They hand over device buffers they already own; the kernel's own scratch (work-item table and
 error word) sits in a fixed array inside the library.  This test feeds the entry point device tensors, twice in a
 row with different inputs (the scratch keeps the previous call's contents), and compares each result with what the
-regular upload/run/download path returns for the same inputs.  It is collected last on purpose.
+regular upload/run/download path returns for the same inputs and with the CPU oracle.  That nothing is allocated is
+checked with the driver's own free-memory figure (cudaMemGetInfo) around a call: torch's allocator counter would not
+see a cudaMalloc made inside the library.  It is collected last on purpose.
 """
 import ctypes as C
 
@@ -18,7 +20,7 @@ from dphpc_b200 import Dataset, Engine, load_engine_lib
 pytestmark = pytest.mark.gpu
 
 
-def call_prealloc(lib, torch, d):
+def call_prealloc(lib, torch, d, repeat=1):
     dev = torch.device("cuda", 0)
     rp = torch.from_numpy(np.ascontiguousarray(d.row_ptr)).to(dev)
     ci = torch.from_numpy(np.ascontiguousarray(d.col_idx)).to(dev)
@@ -27,12 +29,22 @@ def call_prealloc(lib, torch, d):
     B = torch.from_numpy(np.ascontiguousarray(d.B)).to(dev)
     P = torch.full((d.nnz,), 7.0, dtype=torch.float32, device=dev)   # stale values must be overwritten
     torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
-    st = lib.sddmm_b200_sddmm_csr_prealloc(0, C.c_void_p(0), d.M, d.N, d.K, d.nnz, C.c_void_p(rp.data_ptr()), C.c_void_p(ci.data_ptr()),
-                                           C.c_void_p(sv.data_ptr()), C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()),
-                                           C.c_void_p(P.data_ptr()))
+
+    def call():
+        return lib.sddmm_b200_sddmm_csr_prealloc(0, C.c_void_p(0), d.M, d.N, d.K, d.nnz, C.c_void_p(rp.data_ptr()),
+                                                 C.c_void_p(ci.data_ptr()), C.c_void_p(sv.data_ptr()), C.c_void_p(A.data_ptr()),
+                                                 C.c_void_p(B.data_ptr()), C.c_void_p(P.data_ptr()))
+
+    st = call()   # (the first call in a process also loads the kernel image and looks the scratch array up)
     assert st == 0, f"status {st}"
-    assert torch.cuda.memory_allocated() == before
+    for _ in range(repeat):
+        free_before, _ = torch.cuda.mem_get_info(0)
+        alloc_before = torch.cuda.memory_allocated()
+        st = call()
+        assert st == 0, f"status {st}"
+        free_after, _ = torch.cuda.mem_get_info(0)
+        assert free_after == free_before, f"the call changed the device's free memory by {free_before - free_after} bytes"
+        assert torch.cuda.memory_allocated() == alloc_before
     return P.cpu().numpy()
 
 
@@ -44,11 +56,13 @@ def test_prealloc_entry_matches_the_engine_twice_in_a_row():
     for cfg, scale, K in ((4, 0.01, 32), (5, 0.004, 64)):     # second call: other shape, other K, smaller table
         d = Dataset(cfg, K, scale)
         want = eng.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
-        got = call_prealloc(lib, torch, d)
+        got = call_prealloc(lib, torch, d, repeat=2)
         # the bar of the other fp32 GPU tests: |got - want| <= 1e-5 * |s| * sum_k |a b| per nonzero
         rows = np.repeat(np.arange(d.M), np.diff(d.row_ptr))
         bound = oracle_lib.abs_dot_bound(rows, d.col_idx, d.s_val, d.A, d.B)
-        oracle_lib.assert_values_close(got, want, bound, 1e-5, f"prealloc entry, config {cfg}")
+        oracle_lib.assert_values_close(got, want, bound, 1e-5, f"prealloc entry vs engine, config {cfg}")
+        ref = oracle_lib.Oracle().sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        oracle_lib.assert_values_close(got, ref, bound, 1e-5, f"prealloc entry vs CPU oracle, config {cfg}")
         d.close()
     eng.close()
 
@@ -61,3 +75,10 @@ def test_prealloc_entry_rejects_what_it_cannot_hold():
     assert lib.sddmm_b200_sddmm_csr_prealloc(0, None, 10, 10, 30, 5, one, one, one, one, one, one) == 6      # K % 4 != 0
     assert lib.sddmm_b200_sddmm_csr_prealloc(0, None, 10, 10, 512, 5, one, one, one, one, one, one) == 6     # K > 256
     assert lib.sddmm_b200_sddmm_csr_prealloc(0, None, 0, 10, 32, 5, one, one, one, one, one, one) == 1
+    # pointers the kernel's 128-bit accesses could not take (a slice at an odd offset of a larger buffer): bad argument,
+    # reported on the host before anything is launched
+    odd = C.c_void_p(20)
+    for k in range(6):
+        ptrs = [one] * 6
+        ptrs[k] = odd if k in (1, 3, 4) else C.c_void_p(18)   # col_idx, A, B: 16-byte rule; row_ptr, S.val, P.val: 4-byte rule
+        assert lib.sddmm_b200_sddmm_csr_prealloc(0, None, 10, 10, 32, 5, *ptrs) == 1, k
