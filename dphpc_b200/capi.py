@@ -40,6 +40,8 @@ ENGINE_SYMBOLS = [
     "sddmm_b200_pipeline_create", "sddmm_b200_pipeline_destroy", "sddmm_b200_pipeline_sddmm_csr",
     "sddmm_b200_pipeline_last_chunks", "sddmm_b200_pipeline_last_error", "sddmm_b200_pipeline_set_min_chunk_bytes",
     "sddmm_b200_pipeline_update_csr", "sddmm_b200_pipeline_sddmm_coo", "sddmm_b200_set_knob",
+    "sddmm_b200_spmm", "sddmm_b200_last_spmm_ms", "sddmm_b200_row_cuts", "sddmm_b200_stage_b",
+    "sddmm_b200_selftest_wait_timeout",
 ]
 DATASET_SYMBOLS = [
     "sddmm_dataset_create", "sddmm_dataset_create_uniform", "sddmm_dataset_destroy", "sddmm_dataset_dims",
@@ -115,6 +117,11 @@ def load_engine_lib() -> C.CDLL:
     lib.sddmm_b200_set_kernel_timing.argtypes = [H, C.c_int]
     lib.sddmm_b200_get_plan.argtypes = [H, C.POINTER(PlanInfo)]
     lib.sddmm_b200_set_knob.argtypes = [H, C.c_char_p, C.c_double]
+    lib.sddmm_b200_spmm.argtypes = [H, C.c_int64, C.c_void_p, C.c_void_p]
+    lib.sddmm_b200_selftest_wait_timeout.argtypes = [H, C.c_int]
+    lib.sddmm_b200_row_cuts.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_void_p]
+    lib.sddmm_b200_stage_b.argtypes = [C.POINTER(H), C.c_int, C.c_int64, C.c_int64, C.c_void_p]
+    lib.sddmm_b200_last_spmm_ms.argtypes = [H, C.POINTER(C.c_float)]
     lib.sddmm_b200_algorithmic_bytes.argtypes = [H]
     lib.sddmm_b200_algorithmic_bytes.restype = C.c_int64
     lib.sddmm_b200_flops.argtypes = [H]
@@ -295,6 +302,25 @@ class Engine:
             self._check(self.lib.sddmm_b200_last_kernel_ms(self.h, i, C.byref(ms), C.byref(name)), "last_kernel_ms")
             out.append(((name.value or b"?").decode(), float(ms.value)))
         return out
+
+    def spmm(self, X, out=None, rows: int | None = None) -> np.ndarray:
+        """Y = P X for the P of the last run(), computed on the device (P.val is not downloaded).  X: N x K2."""
+        pl = self.plan() if (X is None or rows is None) else None
+        X = None if X is None else _as(X, np.float32)   # None: X = B, the engine's own copy
+        K2 = int(pl["k"]) if X is None else X.shape[1]
+        M = int(rows if rows is not None else pl["rows"])
+        if out is None:
+            out = np.empty((M, K2), dtype=np.float32)
+        self._check(self.lib.sddmm_b200_spmm(self.h, K2, _ptr(X), _ptr(out)), "spmm")
+        return out
+
+    def spmm_raw(self, K2: int, x_ptr: int, y_ptr: int):
+        self._check(self.lib.sddmm_b200_spmm(self.h, int(K2), _ptr(x_ptr), _ptr(y_ptr)), "spmm")
+
+    def last_spmm_ms(self) -> float:
+        ms = C.c_float()
+        self._check(self.lib.sddmm_b200_last_spmm_ms(self.h, C.byref(ms)), "last_spmm_ms")
+        return float(ms.value)
 
     def set_knob(self, name: str, value: float):
         """Planner knob (see sddmm_b200_set_knob); a negative value hands the decision back to the planner."""

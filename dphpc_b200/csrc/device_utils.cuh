@@ -50,8 +50,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Bounded wait: gives up after kSpinLimit probes (each probe itself blocks for a
 // hardware-defined time slice), returns false and lets the caller bail out.
 constexpr uint32_t kSpinLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     return false;
@@ -111,21 +111,53 @@ __device__ __forceinline__ float dot4(const float4 &a, const float4 &b, float ac
     return acc;
 }
 
+// Wide bf16 chunks: 8 consecutive K elements (16 bytes), so that 8 lanes read a 128-byte piece of a bf16 row in ONE
+// request (with 4-element chunks a lane reads 8 bytes and a 128-byte piece takes two requests of half a line each).
+struct Bf16x8 {};
+struct F8 {
+    float4 lo, hi;
+};
+
 template <typename ET>
 struct ChunkOf;
 template <>
 struct ChunkOf<float> {
     using type = float4;
+    using areg = float4;
+    static constexpr int elems = 4;
 };
 template <>
 struct ChunkOf<__nv_bfloat16> {
     using type = uint2;
+    using areg = float4;
+    static constexpr int elems = 4;
+};
+template <>
+struct ChunkOf<Bf16x8> {
+    using type = uint4;
+    using areg = F8;
+    static constexpr int elems = 8;
 };
 
 __device__ __forceinline__ float4 ldg_chunk(const float4 *p) { return __ldg(p); }
 __device__ __forceinline__ uint2 ldg_chunk(const uint2 *p) { return __ldg(p); }
+__device__ __forceinline__ uint4 ldg_chunk(const uint4 *p) { return __ldg(p); }
 __device__ __forceinline__ float4 zero_chunk(float4) { return make_float4(0.f, 0.f, 0.f, 0.f); }
 __device__ __forceinline__ uint2 zero_chunk(uint2) { return make_uint2(0u, 0u); }
+
+// chunk as stored -> fp32 values; dot of an unpacked chunk with a stored one; scaling (masking) of an unpacked chunk
+__device__ __forceinline__ float4 unpack_chunk(const float4 &c) { return c; }
+__device__ __forceinline__ float4 unpack_chunk(const uint2 &c) { return chunk_to_f4(c); }
+__device__ __forceinline__ F8 unpack_chunk(const uint4 &c) {
+    F8 r;
+    r.lo = chunk_to_f4(make_uint2(c.x, c.y));
+    r.hi = chunk_to_f4(make_uint2(c.z, c.w));
+    return r;
+}
+__device__ __forceinline__ float dot_chunk(const float4 &a, const float4 &b, float acc) { return dot4(a, b, acc); }
+__device__ __forceinline__ float dot_chunk(const F8 &a, const F8 &b, float acc) { return dot4(a.hi, b.hi, dot4(a.lo, b.lo, acc)); }
+__device__ __forceinline__ void scale_chunk(float4 &a, float f) { a.x *= f; a.y *= f; a.z *= f; a.w *= f; }
+__device__ __forceinline__ void scale_chunk(F8 &a, float f) { scale_chunk(a.lo, f); scale_chunk(a.hi, f); }
 
 // Sum 8 per-lane partial values over the 8 lanes of an aligned lane group so
 // that lane g (0..7) of the group ends up with the complete sum of value g.

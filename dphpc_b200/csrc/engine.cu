@@ -23,6 +23,7 @@
 #include "kernel_rowgroup.cuh"
 #include "kernel_rowseg.cuh"
 #include "kernel_rowtile.cuh"
+#include "kernel_spmm.cuh"
 #include "plan_kernels.cuh"
 
 using namespace sddmm;
@@ -99,9 +100,17 @@ struct sddmm_b200_engine {
     int64_t tile_grid = 0;         // (M/64 rounded up) * (N/64 rounded up)
     int32_t tiles_per_row = 0;
     int32_t dense_cap = 0;
+    bool aligned_possible = false; // the 64-grid of aligned tiles is small enough to be counted cell by cell
     int32_t *d_tile_counts = nullptr;
-    uint32_t *d_tile_bitmap = nullptr;
-    int32_t *d_dense_ids = nullptr;
+    int2 *d_dense_origin = nullptr;     // {first row, first column} of every dense tile (aligned detection)
+    int2 *d_dense_origin2 = nullptr;    // ... (arbitrary-offset detection); `dense_origin` points at the list in use
+    const int2 *dense_origin = nullptr;
+    bool dense_own = false;             // the tiles in use may overlap: the kernel looks at their own masks
+    uint32_t *d_covered = nullptr;      // one bit per nonzero: owned by a dense tile
+    uint32_t *d_cand = nullptr;         // one bit per nonzero: starts a half-full 64-column window of its row
+    int2 *d_anchors = nullptr;          // candidate tile origins of the arbitrary-offset detection
+    int32_t *d_anchor_counts = nullptr;
+    int32_t anchor_cap = 0;
     DenseTileDesc *d_dense_descs = nullptr;
     int32_t *d_item_covered = nullptr;
     int32_t *d_item_ids = nullptr;
@@ -125,9 +134,26 @@ struct sddmm_b200_engine {
     int32_t panel_cols = 0;            // columns per panel
     int32_t n_units = 0;
     bool use_seg = false;
+    bool seg_residual = false;         // the row-segment kernel computes what the dense tiles left (units over the uncovered runs)
     int l2_bytes = 0;
     // tuning knobs (sddmm_b200_set_knob; defaults from the environment at create): < 0 = decide automatically
-    double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_evict_last = -1, knob_b_fraction = -1;
+    double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_evict_last = -1, knob_b_fraction = -1, knob_group_units = -1,
+           knob_offset_tiles = -1;
+    bool rg_units = false;             // row groups run as shared segments (row-segment group kernel) instead of the warp-per-group kernel
+
+    // B received from another engine (sddmm_b200_stage_b): the next upload may pass B = NULL
+    float *b_stage = nullptr;
+    size_t b_stage_cap = 0;
+    int64_t b_stage_n = 0, b_stage_k = 0;   // dimensions of the staged B (0: none)
+    cudaEvent_t ev_stage = nullptr;
+
+    // consumer of P on the device (Y = P X): its own buffers, grown on demand, and its own plain unit list
+    Arena spmm_arena;
+    int32_t spmm_units = 0;            // units in the consumer's list for the current upload (0: not built yet)
+    int64_t spmm_k2 = 0;
+    float *d_X = nullptr, *d_Y = nullptr;
+    int2 *d_spmm_units = nullptr;
+    cudaEvent_t ev_spmm0 = nullptr, ev_spmm1 = nullptr;
 
     // plan
     sddmm_b200_plan_info plan;
@@ -248,16 +274,17 @@ double env_double(const char *name, double fallback) {
 // contributes (a run of fewer than ~6 nonzeros leaves most of a segment's 8 slots empty), which bounds the count.
 int choose_panels(const sddmm_b200_engine *e) {
     if (e->knob_panels >= 1 && e->knob_panels <= 64) return static_cast<int>(e->knob_panels);
-    if (e->knob_panel_mb <= 0) return 1;   // off unless a panel size is asked for
     const double eb = static_cast<double>(elem_bytes(e));
-    const double b_bytes = static_cast<double>(e->N) * e->K * eb, a_bytes = static_cast<double>(e->M) * e->K * eb;
+    const double b_bytes = static_cast<double>(e->N) * e->K * eb;
     const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
-    if (b_bytes <= 0.75 * l2) return 1;
-    const double panel = e->knob_panel_mb > 0 ? e->knob_panel_mb * (1 << 20) : 0.4 * l2;
+    if (b_bytes <= l2) return 1;
+    if (e->mode == SDDMM_B200_BF16) return 1;   // measured: with bf16 storage the extra segments cost more than the saved DRAM reads
+    // measured on B200 (126 MB of L2): panels of about 96 MB are as good as smaller ones, and a run shorter than a segment
+    // wastes gather slots -- so at most one panel per 8 nonzeros of an average row, and never more than 4
+    const double panel = e->knob_panel_mb > 0 ? e->knob_panel_mb * (1 << 20) : 0.75 * l2;
     int64_t p = static_cast<int64_t>((b_bytes + panel - 1) / panel);
-    p = std::min<int64_t>(p, e->nnz / std::max<int64_t>(1, 6 * e->M));           // keep runs of ~6 nonzeros and more
-    while (p > 1 && p * a_bytes > 0.6 * static_cast<double>(e->nnz) * e->K * eb) --p;   // re-reading A must stay cheaper than the gathers it saves
-    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(p, 32)));
+    p = std::min<int64_t>(p, e->nnz / std::max<int64_t>(1, 8 * e->M));
+    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(p, 4)));
 }
 
 // Lay out the arena for the current dimensions and point the views into it.
@@ -287,7 +314,7 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     const size_t runs = std::min(M * static_cast<size_t>(e->panels), nnz);
     e->unit_cap = static_cast<int64_t>(nnz / 8 + runs + 8);
     const size_t scan_n = M * static_cast<size_t>(e->panels);
-    const size_t o_units = c.take(static_cast<size_t>(e->unit_cap) * sizeof(int2));
+    const size_t o_units = c.take(static_cast<size_t>(e->unit_cap) * sizeof(int4));   // (row groups use 16-byte headers)
     const size_t o_uoff = c.take((scan_n + 1) * 4);
     const size_t o_stile = c.take((scan_n / kScanTile + 2) * 4);
     // dense-tile path: only carved when the mode, K and the size of the 64x64 tile grid allow it
@@ -297,14 +324,20 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     // upload, every bf16 value is exactly a tf32 value (8 against 11 significand bits), so the tile products are exactly the
     // bf16-input / fp32-accumulate ones.
     const bool tc_mode = e->mode == SDDMM_B200_TF32 || e->mode == SDDMM_B200_FP32_TC || e->mode == SDDMM_B200_BF16;
-    e->dense_possible = tc_mode && !(e->flags & SDDMM_B200_FLAG_NO_DENSE_TILES) && K % 32 == 0 && K <= 256 &&
-                        e->tile_grid <= (int64_t(1) << 22) && nnz >= kDenseMinCount;
-    e->dense_cap = e->dense_possible ? static_cast<int32_t>(std::min<int64_t>(e->tile_grid, e->nnz / kDenseMinCount + 1)) : 0;
+    e->dense_possible = tc_mode && !(e->flags & SDDMM_B200_FLAG_NO_DENSE_TILES) && K % 32 == 0 && K <= 256 && nnz >= kDenseMinCount;
+    e->aligned_possible = e->dense_possible && e->tile_grid <= (int64_t(1) << 22);
+    // (tiles at arbitrary offsets may overlap, so there can be more of them than nnz / 2048; what does not fit is dropped)
+    e->dense_cap = e->dense_possible ? static_cast<int32_t>(2 * (e->nnz / kDenseMinCount) + 16) : 0;
+    e->anchor_cap = e->dense_possible ? static_cast<int32_t>(e->nnz / 256 + 64) : 0;
     const bool split = e->dense_possible && e->mode == SDDMM_B200_FP32_TC;
     const size_t tg = static_cast<size_t>(e->tile_grid);
-    const size_t o_tc = e->dense_possible ? c.take(tg * 4) : 0;
-    const size_t o_tb = e->dense_possible ? c.take((tg / 32 + 1) * 4) : 0;
-    const size_t o_di = e->dense_possible ? c.take(static_cast<size_t>(e->dense_cap) * 4) : 0;
+    const size_t o_tc = e->aligned_possible ? c.take(tg * 4) : 0;
+    const size_t o_di = e->dense_possible ? c.take(static_cast<size_t>(e->dense_cap) * sizeof(int2)) : 0;
+    const size_t o_di2 = e->dense_possible ? c.take(static_cast<size_t>(e->dense_cap) * sizeof(int2)) : 0;
+    const size_t o_cov = e->dense_possible ? c.take((nnz / 32 + 2) * 4) : 0;
+    const size_t o_cand = e->dense_possible ? c.take((nnz / 32 + 2) * 4) : 0;
+    const size_t o_anc = e->dense_possible ? c.take(static_cast<size_t>(e->anchor_cap) * sizeof(int2)) : 0;
+    const size_t o_ancc = e->dense_possible ? c.take(static_cast<size_t>(e->anchor_cap) * 4) : 0;
     const size_t o_dd = e->dense_possible ? c.take(static_cast<size_t>(e->dense_cap) * sizeof(DenseTileDesc)) : 0;
     const size_t o_ic = e->dense_possible ? c.take(static_cast<size_t>(std::max(n_items, 1)) * 4) : 0;
     const size_t o_ii = e->dense_possible ? c.take(static_cast<size_t>(std::max(n_items, 1)) * 4) : 0;
@@ -313,9 +346,13 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     int st = ensure_arena(e, c.off);
     if (st) return st;
     char *b = e->arena.base;
-    e->d_tile_counts = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_tc) : nullptr;
-    e->d_tile_bitmap = e->dense_possible ? reinterpret_cast<uint32_t *>(b + o_tb) : nullptr;
-    e->d_dense_ids = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_di) : nullptr;
+    e->d_tile_counts = e->aligned_possible ? reinterpret_cast<int32_t *>(b + o_tc) : nullptr;
+    e->d_dense_origin = e->dense_possible ? reinterpret_cast<int2 *>(b + o_di) : nullptr;
+    e->d_dense_origin2 = e->dense_possible ? reinterpret_cast<int2 *>(b + o_di2) : nullptr;
+    e->d_covered = e->dense_possible ? reinterpret_cast<uint32_t *>(b + o_cov) : nullptr;
+    e->d_cand = e->dense_possible ? reinterpret_cast<uint32_t *>(b + o_cand) : nullptr;
+    e->d_anchors = e->dense_possible ? reinterpret_cast<int2 *>(b + o_anc) : nullptr;
+    e->d_anchor_counts = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_ancc) : nullptr;
     e->d_dense_descs = e->dense_possible ? reinterpret_cast<DenseTileDesc *>(b + o_dd) : nullptr;
     e->d_item_covered = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_ic) : nullptr;
     e->d_item_ids = e->dense_possible ? reinterpret_cast<int32_t *>(b + o_ii) : nullptr;
@@ -404,28 +441,95 @@ int read_counters(sddmm_b200_engine *e, PlanCounters *out) {
     return SDDMM_B200_OK;
 }
 
+int cuda_status(sddmm_b200_engine *e, cudaError_t err);
+
 int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item_nnz, int n_items) {
     e->n_dense = 0;
     e->n_residual_items = n_items;
     if (!e->dense_possible || base_pc.unsorted_cols || base_pc.dup_cols || base_pc.max_row_nnz < 32) return SDDMM_B200_OK;
     const int cap = e->sm_count * 8;
     cudaStream_t s = e->stream;
-    const size_t tg = static_cast<size_t>(e->tile_grid);
-    CU_TRY(e, cudaMemsetAsync(e->d_tile_counts, 0, tg * 4, s));
-    CU_TRY(e, cudaMemsetAsync(e->d_tile_bitmap, 0, (tg / 32 + 1) * 4, s));
+    const int32_t M = static_cast<int32_t>(e->M);
+    CU_TRY(e, cudaMemsetAsync(e->d_covered, 0, (static_cast<size_t>(e->nnz) / 32 + 2) * 4, s));
     CU_TRY(e, cudaMemsetAsync(e->d_item_covered, 0, static_cast<size_t>(n_items) * 4, s));
-    k_tile_count<<<grid_for(e->M * 32, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_rp, e->d_col, static_cast<int32_t>(e->M), e->tiles_per_row,
-                                                                       e->d_tile_counts);
-    k_tile_select<<<grid_for(e->tile_grid, kBlock, cap), kBlock, 0, s>>>(e->d_tile_counts, e->tile_grid, kDenseMinCount, e->d_tile_bitmap,
-                                                                         e->d_dense_ids, e->dense_cap, e->d_pc);
-    CU_TRY(e, cudaGetLastError());
     PlanCounters pc;
-    if (int rc = read_counters(e, &pc)) return rc;
-    const int n_dense = std::min(pc.dense_tiles, e->dense_cap);
+    // ---- tiles on the 64-grid: count every cell, keep those at least half full ----
+    int n_aligned = 0;
+    unsigned long long aligned_nnz = 0;
+    if (e->aligned_possible) {
+        CU_TRY(e, cudaMemsetAsync(e->d_tile_counts, 0, static_cast<size_t>(e->tile_grid) * 4, s));
+        k_tile_count<<<grid_for(e->M * 32, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_rp, e->d_col, M, e->tiles_per_row, e->d_tile_counts);
+        k_tile_select<<<grid_for(e->tile_grid, kBlock, cap), kBlock, 0, s>>>(e->d_tile_counts, e->tile_grid, e->tiles_per_row, kDenseMinCount,
+                                                                             e->d_dense_origin, e->dense_cap, e->d_pc);
+        CU_TRY(e, cudaGetLastError());
+        if (int rc = read_counters(e, &pc)) return rc;
+        n_aligned = std::min(pc.dense_tiles, e->dense_cap);
+        aligned_nnz = pc.window_nnz;
+    }
+    int n_dense = n_aligned;
+    e->dense_origin = e->d_dense_origin;
+    bool offsets_used = false;   // the tiles in use come from the arbitrary-offset detection (they may overlap)
+    // ---- tiles at arbitrary offsets ("randomly placed blocks"): when the grid catches less than half of the nonzeros and
+    //      the rows are long enough to hold half-full 64-column windows at all ----
+    const bool try_offsets = e->knob_offset_tiles != 0 &&
+                             (e->knob_offset_tiles > 0 || (2 * aligned_nnz < static_cast<unsigned long long>(e->nnz) &&
+                                                           e->nnz >= 16 * static_cast<int64_t>(std::max<unsigned long long>(1, base_pc.rows_nonempty))));
+    if (try_offsets) {
+        const int wcap = e->sm_count * 32;
+        CU_TRY(e, cudaMemsetAsync(e->d_cand, 0, (static_cast<size_t>(e->nnz) / 32 + 2) * 4, s));
+        CU_TRY(e, cudaMemsetAsync(&e->d_pc->n_anchors, 0, sizeof(int), s));
+        k_window_candidates<<<grid_for(e->M * 32, kBlock, wcap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, 32, e->d_cand);
+        k_window_anchors<<<grid_for(e->M * 32, kBlock, wcap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, 32, e->d_cand, e->d_anchors, e->anchor_cap,
+                                                                              &e->d_pc->n_anchors);
+        CU_TRY(e, cudaGetLastError());
+        if (int rc = read_counters(e, &pc)) return rc;
+        const int n_anchors = std::min(pc.n_anchors, e->anchor_cap);
+        if (n_anchors > 0) {
+            CU_TRY(e, cudaMemsetAsync(e->d_anchor_counts, 0, static_cast<size_t>(n_anchors) * 4, s));
+            CU_TRY(e, cudaMemsetAsync(&e->d_pc->dense_tiles, 0, sizeof(int), s));
+            CU_TRY(e, cudaMemsetAsync(&e->d_pc->window_nnz, 0, sizeof(unsigned long long), s));
+            k_anchor_counts<<<grid_for(static_cast<int64_t>(n_anchors) * 64, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_rp, e->d_col, M, e->d_anchors,
+                                                                                                            n_anchors, e->d_anchor_counts);
+            k_anchor_select<<<grid_for(n_anchors, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_anchors, e->d_anchor_counts, n_anchors, kDenseMinCount,
+                                                                                    e->d_dense_origin2, e->dense_cap, e->d_pc);
+            CU_TRY(e, cudaGetLastError());
+            if (int rc = read_counters(e, &pc)) return rc;
+            // (windows may overlap, so their sum can count a nonzero twice; it still ranks the two detections)
+            if (pc.window_nnz > aligned_nnz) {
+                n_dense = std::min(pc.dense_tiles, e->dense_cap);
+                e->dense_origin = e->d_dense_origin2;
+                offsets_used = true;
+            }
+        }
+    }
     if (n_dense <= 0) return SDDMM_B200_OK;
-    k_tile_rows<DenseTileDesc><<<grid_for(static_cast<int64_t>(n_dense) * 64, kBlock, 1 << 30), kBlock, 0, s>>>(
-        e->d_rp, e->d_col, static_cast<int32_t>(e->M), e->tiles_per_row, e->d_dense_ids, n_dense, e->d_dense_descs, item_nnz,
-        e->d_item_covered);
+    // row descriptors and ownership (tile_owned: the anchor counters are free again)
+    auto describe = [&]() -> int {
+        CU_TRY(e, cudaMemsetAsync(&e->d_pc->dense_nnz, 0, sizeof(unsigned long long), s));
+        CU_TRY(e, cudaMemsetAsync(e->d_anchor_counts, 0, static_cast<size_t>(n_dense) * 4, s));
+        k_tile_rows<DenseTileDesc><<<grid_for(static_cast<int64_t>(n_dense) * 64, kBlock, 1 << 30), kBlock, 0, s>>>(
+            e->d_rp, e->d_col, M, e->dense_origin, n_dense, e->d_dense_descs, e->d_covered, item_nnz, e->d_item_covered, e->d_anchor_counts,
+            e->d_pc);
+        return cuda_status(e, cudaGetLastError());
+    };
+    if (int rc = describe()) return rc;
+    if (offsets_used) {
+        // windows at arbitrary offsets overlap: drop the tiles that own less than a quarter of a tile, then decide the
+        // ownership afresh among those that stay
+        int2 *kept = e->d_dense_origin;   // (the grid's list is not used)
+        CU_TRY(e, cudaMemsetAsync(&e->d_pc->dense_tiles, 0, sizeof(int), s));
+        k_tile_keep<<<grid_for(n_dense, kBlock, 1 << 30), kBlock, 0, s>>>(e->dense_origin, e->d_anchor_counts, n_dense, kDenseMinCount / 2, kept, e->d_pc);
+        CU_TRY(e, cudaGetLastError());
+        if (int rc = read_counters(e, &pc)) return rc;
+        if (pc.dense_tiles < n_dense) {
+            n_dense = pc.dense_tiles;
+            e->dense_origin = kept;
+            CU_TRY(e, cudaMemsetAsync(e->d_covered, 0, (static_cast<size_t>(e->nnz) / 32 + 2) * 4, s));
+            CU_TRY(e, cudaMemsetAsync(e->d_item_covered, 0, static_cast<size_t>(n_items) * 4, s));
+            if (n_dense <= 0) return SDDMM_B200_OK;
+            if (int rc = describe()) return rc;
+        }
+    }
     k_residual_items<<<grid_for(n_items, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_item_covered, n_items, item_nnz, e->nnz, e->d_item_ids,
                                                                           e->d_pc);
     CU_TRY(e, cudaGetLastError());
@@ -435,9 +539,12 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     int st = make_operand_map(e, &e->map_a, split ? e->d_Ax : e->d_A32, e->M, kx);
     if (!st) st = make_operand_map(e, &e->map_b, split ? e->d_Bx : e->d_B32, e->N, kx);
     if (st) return st;
-    if (ensure_dynamic_smem_limit(reinterpret_cast<const void *>(sddmm_dense_tile_kernel), e->device, DenseSmem::kDynamicBytes))
+    const bool own_masks = offsets_used;   // tiles off the grid may overlap
+    e->dense_own = own_masks;
+    const void *dense_fn = own_masks ? reinterpret_cast<const void *>(sddmm_dense_tile_kernel<true>) : reinterpret_cast<const void *>(sddmm_dense_tile_kernel<false>);
+    if (ensure_dynamic_smem_limit(dense_fn, e->device, DenseSmem::kDynamicBytes))
         return fail(e, SDDMM_B200_ERR_CUDA, "dense-tile kernel: cannot raise the dynamic shared memory limit");
-    CU_TRY(e, cudaFuncSetAttribute(sddmm_dense_tile_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    CU_TRY(e, cudaFuncSetAttribute(dense_fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     e->n_dense = n_dense;
     e->n_residual_items = pc.residual_items;
     sddmm_b200_plan_info &p = e->plan;
@@ -449,7 +556,7 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     // Resident CTAs per SM, from the kernel's own resources (the runtime's occupancy query answers 1 for this kernel):
     // shared memory (+1 KB the driver reserves per CTA), registers (allocated per warp in units of 256), tensor memory columns.
     cudaFuncAttributes fa;
-    CU_TRY(e, cudaFuncGetAttributes(&fa, sddmm_dense_tile_kernel));
+    CU_TRY(e, cudaFuncGetAttributes(&fa, dense_fn));
     int smem_per_sm = 0, regs_per_sm = 0;   // (single attributes: the full property query takes milliseconds)
     CU_TRY(e, cudaDeviceGetAttribute(&smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, e->device));
     CU_TRY(e, cudaDeviceGetAttribute(&regs_per_sm, cudaDevAttrMaxRegistersPerMultiprocessor, e->device));
@@ -472,6 +579,12 @@ using RowGroupFn = void (*)(const RowGroupArgs);
 RowGroupFn pick_rowgroup(int rows, int cpl) {
     if (cpl == 1) return rows == 2 ? sddmm_rowgroup_kernel<2, 1> : rows == 3 ? sddmm_rowgroup_kernel<3, 1> : sddmm_rowgroup_kernel<4, 1>;
     return rows == 2 ? sddmm_rowgroup_kernel<2, 2> : rows == 3 ? sddmm_rowgroup_kernel<3, 2> : sddmm_rowgroup_kernel<4, 2>;
+}
+
+using RowSegGroupFn = void (*)(const RowSegGroupArgs);
+RowSegGroupFn pick_rowseg_group(int rows, int cpl) {
+    if (cpl == 1) return rows == 2 ? sddmm_rowseg_group_kernel<1, 2> : rows == 3 ? sddmm_rowseg_group_kernel<1, 3> : sddmm_rowseg_group_kernel<1, 4>;
+    return rows == 2 ? sddmm_rowseg_group_kernel<2, 2> : rows == 3 ? sddmm_rowseg_group_kernel<2, 3> : sddmm_rowseg_group_kernel<2, 4>;
 }
 
 // Row groups: groups of 2, 3 or 4 consecutive rows with one column list (first full group at row 0 .. G-1) share each gather of B.
@@ -524,6 +637,31 @@ int build_rowgroup_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     p.rowgroup_groups = pc.group_count[bs];
     p.rowgroup_rows = best;
     p.rowgroup_grid = std::min((n_groups + kRowGroupWarps - 1) / kRowGroupWarps, e->sm_count * occ);
+    // Shared segments: the group's column list cut into units of 8 columns that serve all G rows (row-segment group kernel).
+    e->rg_units = e->knob_group_units != 0 && e->M < kUnitRowLimit;
+    if (e->rg_units) {
+        const int32_t M = static_cast<int32_t>(e->M);
+        const int n_tiles = static_cast<int>((e->M + kScanTile - 1) / kScanTile);
+        const int capb = e->sm_count * 32;
+        k_group_unit_count<<<grid_for(e->M, kBlock, capb), kBlock, 0, s>>>(e->d_rp, M, best, best_first, e->d_group_ok, e->d_unit_off);
+        k_scan_tile_sums<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
+        k_scan_sums<<<1, kScanBlock, 0, s>>>(e->d_scan_tiles, n_tiles, &e->d_pc->units);
+        k_scan_apply<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
+        k_group_unit_fill<<<grid_for(e->M * 32, kBlock, capb), kBlock, 0, s>>>(e->d_rp, M, best, best_first, e->d_group_ok, e->d_unit_off,
+                                                                               reinterpret_cast<int4 *>(e->d_units));
+        CU_TRY(e, cudaGetLastError());
+        if (int rc = read_counters(e, &pc)) return rc;
+        if (pc.units == 0 || pc.units > static_cast<unsigned long long>(e->unit_cap))
+            return fail(e, SDDMM_B200_ERR_CUDA, "row-group plan: %llu units for a list of %lld", pc.units, (long long)e->unit_cap);
+        e->n_units = static_cast<int32_t>(pc.units);
+        int occ2 = 0;
+        CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ2, pick_rowseg_group(best, static_cast<int>(e->K / 32)), kRowSegWarps * 32, 0));
+        if (occ2 < 1) return fail(e, SDDMM_B200_ERR_CUDA, "row-segment group kernel does not fit on an SM");
+        const int64_t n_quads = (static_cast<int64_t>(e->n_units) + 3) / 4;
+        p.rowseg_units = e->n_units;
+        p.rowseg_panels = 1;
+        p.rowgroup_grid = static_cast<int32_t>(std::min<int64_t>((n_quads + kRowSegWarps - 1) / kRowSegWarps, static_cast<int64_t>(e->sm_count) * occ2));
+    }
     p.rowtile_nnz = 0;
     p.rowtile_items = 0;
     p.n_kernels = 1;
@@ -548,6 +686,50 @@ RowSegFn<ET> pick_rowseg(int cpl, bool exact, bool hint = false) {
     return hint ? pick_rowseg_hint<ET, true>(cpl, exact) : pick_rowseg_hint<ET, false>(cpl, exact);
 }
 
+// The row-segment kernel instantiation for this engine's storage and K.  bf16 storage with K >= 64 reads 16-byte chunks
+// (8 elements: 8 lanes cover a 128-byte piece in one request), otherwise chunks of 4 elements.
+bool seg_wide_bf16(const sddmm_b200_engine *e) { return e->mode == SDDMM_B200_BF16 && e->K >= 64; }
+const void *seg_function(const sddmm_b200_engine *e, bool hint) {
+    if (seg_wide_bf16(e)) {
+        const int cpl = round_up_cpl((e->K + 1) / 2);   // chunks of 8: K / 64 lanes-rounds
+        return reinterpret_cast<const void *>(pick_rowseg<Bf16x8>(cpl, e->K == 64 * cpl, hint));
+    }
+    const bool exact = e->K == 32 * e->cpl;
+    return e->mode == SDDMM_B200_BF16 ? reinterpret_cast<const void *>(pick_rowseg<__nv_bfloat16>(e->cpl, exact, hint))
+                                      : reinterpret_cast<const void *>(pick_rowseg<float>(e->cpl, exact, hint));
+}
+
+// What the dense tiles left, as row segments: the uncovered runs of every row cut into units, so that the residual
+// kernel touches only those nonzeros (a kernel that walks all work items and skips the covered nonzeros costs as much as
+// the whole matrix when the tiles leave a little in every item).
+int build_residual_units(sddmm_b200_engine *e) {
+    if ((e->flags & SDDMM_B200_FLAG_NO_ROW_SEGMENTS) || e->knob_rowseg == 0 || e->M >= kUnitRowLimit) return SDDMM_B200_OK;
+    const int32_t M = static_cast<int32_t>(e->M);
+    const int n_tiles = static_cast<int>((e->M + kScanTile - 1) / kScanTile);
+    const int cap = e->sm_count * 32;
+    cudaStream_t s = e->stream;
+    k_residual_unit_count<<<grid_for(e->M, kBlock, cap), kBlock, 0, s>>>(e->d_rp, M, e->d_covered, e->d_unit_off);
+    k_scan_tile_sums<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
+    k_scan_sums<<<1, kScanBlock, 0, s>>>(e->d_scan_tiles, n_tiles, &e->d_pc->units);
+    k_scan_apply<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
+    CU_TRY(e, cudaGetLastError());
+    PlanCounters pc;
+    if (int rc = read_counters(e, &pc)) return rc;
+    if (pc.units == 0 || pc.units > static_cast<unsigned long long>(e->unit_cap)) return SDDMM_B200_OK;   // (the row-tile kernel takes the residual)
+    k_residual_unit_fill<<<grid_for(e->M, kBlock, cap), kBlock, 0, s>>>(e->d_rp, M, e->d_covered, e->d_unit_off, e->d_units);
+    CU_TRY(e, cudaGetLastError());
+    int occ = 0;
+    CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, seg_function(e, false), kRowSegWarps * 32, 0));
+    if (occ < 1) return SDDMM_B200_OK;
+    e->n_units = static_cast<int32_t>(pc.units);
+    e->seg_residual = true;
+    const int64_t n_quads = (static_cast<int64_t>(e->n_units) + 3) / 4;
+    e->plan.rowseg_units = e->n_units;
+    e->plan.rowseg_panels = 1;
+    e->plan.rowseg_grid = static_cast<int32_t>(std::min<int64_t>((n_quads + kRowSegWarps - 1) / kRowSegWarps, static_cast<int64_t>(e->sm_count) * occ));
+    return SDDMM_B200_OK;
+}
+
 // Row segments: the unit list (rows cut into segments of at most 8 nonzeros, panel-major when B is cut into column
 // panels) is counted, scanned and written on the device; the host only reads the total.  Taken unless the rows are
 // long on average (the A-row-tile kernel keeps the A chunk of a long row in registers over the whole row).
@@ -556,8 +738,6 @@ int build_rowseg_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     e->use_seg = false;
     e->n_units = 0;
     if ((e->flags & SDDMM_B200_FLAG_NO_ROW_SEGMENTS) || seg_env == 0 || e->M >= kUnitRowLimit) return SDDMM_B200_OK;
-    const double mean_len = static_cast<double>(e->nnz) / static_cast<double>(std::max<unsigned long long>(1, base_pc.rows_nonempty));
-    if (seg_env != 1 && mean_len > 512.0) return SDDMM_B200_OK;
     const int32_t panels = base_pc.unsorted_cols ? 1 : e->panels;   // a panel run is a contiguous piece of a row only when its columns are sorted
     const int32_t M = static_cast<int32_t>(e->M);
     const int64_t n = static_cast<int64_t>(panels) * M;
@@ -574,9 +754,7 @@ int build_rowseg_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     if (int rc = read_counters(e, &pc)) return rc;
     if (pc.units == 0 || pc.units > static_cast<unsigned long long>(e->unit_cap) || pc.units >= (1ull << 31))
         return fail(e, SDDMM_B200_ERR_CUDA, "row-segment plan: %llu units for a list of %lld", pc.units, (long long)e->unit_cap);
-    const bool exact = e->K == 32 * e->cpl;
-    const void *fn = (e->mode == SDDMM_B200_BF16) ? reinterpret_cast<const void *>(pick_rowseg<__nv_bfloat16>(e->cpl, exact))
-                                                  : reinterpret_cast<const void *>(pick_rowseg<float>(e->cpl, exact));
+    const void *fn = seg_function(e, false);
     int occ = 0;
     CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kRowSegWarps * 32, 0));
     if (occ < 1) return fail(e, SDDMM_B200_ERR_CUDA, "row-segment kernel does not fit on an SM");
@@ -650,9 +828,14 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
         p.n_kernels = 0;
         return SDDMM_B200_OK;
     }
+    e->seg_residual = false;
     if (!e->use_scalar) {
         int st = build_dense_plan(e, pc, item_nnz, n_items);
         if (st) return st;
+        if (e->n_dense > 0 && e->n_residual_items > 0) {
+            st = build_residual_units(e);
+            if (st) return st;
+        }
     }
     e->rg_rows = 0;
     e->use_seg = false;
@@ -669,6 +852,13 @@ int build_plan(sddmm_b200_engine *e, int item_nnz, int n_items) {
     const int dense_kernels = e->n_dense > 0 ? 1 : 0;
     if (e->n_residual_items == 0) {
         p.n_kernels = dense_kernels;
+        return SDDMM_B200_OK;
+    }
+    if (e->seg_residual) {   // the row-segment kernel computes what the tiles left
+        p.rowseg_nnz = p.rowtile_nnz;
+        p.rowtile_nnz = 0;
+        p.rowtile_items = 0;
+        p.n_kernels = 1 + dense_kernels;
         return SDDMM_B200_OK;
     }
     if (e->use_scalar) {
@@ -733,6 +923,7 @@ int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t
                   cudaMemcpyKind kind) {
     e->uploaded = false;
     e->ran = false;
+    e->spmm_units = 0;
     e->M = M; e->N = N; e->K = K; e->nnz = nnz;
     const int item_nnz = choose_item_nnz(e);
     const int n_items = static_cast<int>((nnz + item_nnz - 1) / item_nnz);
@@ -750,8 +941,10 @@ int upload_common(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t
     if (st) {   // nothing of a failed upload may still be reading the caller's buffers
         cudaStreamSynchronize(s2);
         cudaStreamSynchronize(s);
+        if (e->B_on_device == e->b_stage) e->B_on_device = nullptr;
         return st;
     }
+    if (e->B_on_device == e->b_stage) e->B_on_device = nullptr;
     e->uploaded = true;
     return SDDMM_B200_OK;
 }
@@ -771,6 +964,25 @@ int mark_kernel(sddmm_b200_engine *e, const char *name, cudaStream_t st) {
     return SDDMM_B200_OK;
 }
 
+// the row-segment kernel over the engine's unit list (the whole matrix, or what the dense tiles left)
+int launch_rowseg(sddmm_b200_engine *e, cudaStream_t stream) {
+    const sddmm_b200_plan_info &p = e->plan;
+    RowSegArgs g;
+    g.units = e->d_units; g.col_idx = e->d_col; g.s_val = e->d_sval; g.p_val = e->d_pval;
+    g.n_units = e->n_units; g.K = static_cast<int32_t>(e->K);
+    // L2 is asked to keep the gathered B rows when they can stay: one column panel at a time
+    g.b_evict_last = e->knob_b_evict_last >= 0 ? static_cast<int32_t>(e->knob_b_evict_last) : (p.rowseg_panels > 1 ? 1 : 0);
+    g.b_fraction = e->knob_b_fraction > 0 ? static_cast<float>(std::min(1.0, e->knob_b_fraction)) : 1.0f;
+    if (int st = begin_kernel(e, stream)) return st;
+    if (e->mode == SDDMM_B200_BF16) {
+        g.A = e->d_A16; g.B = e->d_B16;
+    } else {
+        g.A = e->d_A32; g.B = e->d_B32;
+    }
+    reinterpret_cast<RowSegFn<float>>(const_cast<void *>(seg_function(e, g.b_evict_last != 0)))<<<p.rowseg_grid, kRowSegWarps * 32, 0, stream>>>(g);
+    return mark_kernel(e, "sddmm_rowseg_kernel", stream);
+}
+
 int launch_all(sddmm_b200_engine *e) {
     const sddmm_b200_plan_info &p = e->plan;
     e->kernels_launched = 0;
@@ -782,6 +994,14 @@ int launch_all(sddmm_b200_engine *e) {
                                                                       static_cast<int32_t>(e->M), static_cast<int32_t>(e->K), e->nnz);
         return mark_kernel(e, "sddmm_scalar_kernel", e->stream);
     }
+    if (e->rg_rows && e->rg_units) {
+        RowSegGroupArgs g;
+        g.ghdr = reinterpret_cast<const int4 *>(e->d_units); g.col_idx = e->d_col; g.s_val = e->d_sval; g.p_val = e->d_pval;
+        g.A = e->d_A32; g.B = e->d_B32; g.n_units = e->n_units; g.K = static_cast<int32_t>(e->K);
+        if ((st = begin_kernel(e, e->stream))) return st;
+        pick_rowseg_group(e->rg_rows, static_cast<int>(e->K / 32))<<<p.rowgroup_grid, kRowSegWarps * 32, 0, e->stream>>>(g);
+        return mark_kernel(e, "sddmm_rowseg_group_kernel", e->stream);
+    }
     if (e->rg_rows) {
         RowGroupArgs g;
         g.row_ptr = e->d_rp; g.col_idx = e->d_col; g.s_val = e->d_sval; g.p_val = e->d_pval; g.A = e->d_A32; g.B = e->d_B32;
@@ -790,24 +1010,7 @@ int launch_all(sddmm_b200_engine *e) {
         pick_rowgroup(e->rg_rows, static_cast<int>(e->K / 32))<<<p.rowgroup_grid, kRowGroupWarps * 32, 0, e->stream>>>(g);
         return mark_kernel(e, "sddmm_rowgroup_kernel", e->stream);
     }
-    if (e->use_seg) {
-        RowSegArgs g;
-        g.units = e->d_units; g.col_idx = e->d_col; g.s_val = e->d_sval; g.p_val = e->d_pval;
-        g.n_units = e->n_units; g.K = static_cast<int32_t>(e->K);
-        // L2 is asked to keep the gathered B rows when they can stay: one column panel at a time
-        g.b_evict_last = e->knob_b_evict_last >= 0 ? static_cast<int32_t>(e->knob_b_evict_last) : (p.rowseg_panels > 1 ? 1 : 0);
-        g.b_fraction = e->knob_b_fraction > 0 ? static_cast<float>(std::min(1.0, e->knob_b_fraction)) : 1.0f;
-        const bool exact = e->K == 32 * e->cpl;
-        if ((st = begin_kernel(e, e->stream))) return st;
-        if (e->mode == SDDMM_B200_BF16) {
-            g.A = e->d_A16; g.B = e->d_B16;
-            pick_rowseg<__nv_bfloat16>(e->cpl, exact, g.b_evict_last != 0)<<<p.rowseg_grid, kRowSegWarps * 32, 0, e->stream>>>(g);
-        } else {
-            g.A = e->d_A32; g.B = e->d_B32;
-            pick_rowseg<float>(e->cpl, exact, g.b_evict_last != 0)<<<p.rowseg_grid, kRowSegWarps * 32, 0, e->stream>>>(g);
-        }
-        return mark_kernel(e, "sddmm_rowseg_kernel", e->stream);
-    }
+    if (e->use_seg) return launch_rowseg(e, e->stream);
     // the two kernels write disjoint nonzeros: when both run, the row-tile kernel goes to the side stream
     static const bool no_side = std::getenv("SDDMM_B200_NO_SIDE_STREAM") != nullptr;   // tuning / debugging knob
     const bool both = e->n_dense > 0 && e->n_residual_items > 0 && !no_side;
@@ -815,22 +1018,29 @@ int launch_all(sddmm_b200_engine *e) {
     if (both) CU_TRY(e, cudaStreamWaitEvent(e->side_stream, e->ev_run0, 0));   // (run() has just recorded it on the main stream)
     if (e->n_dense > 0) {
         DenseArgs d;
-        d.tile_ids = e->d_dense_ids; d.descs = e->d_dense_descs; d.s_val = e->d_sval; d.p_val = e->d_pval; d.err = e->d_err;
-        d.n_tiles = e->n_dense; d.tiles_per_row = e->tiles_per_row;
+        d.origins = e->dense_origin; d.descs = e->d_dense_descs; d.s_val = e->d_sval; d.p_val = e->d_pval; d.err = e->d_err;
+        d.n_tiles = e->n_dense;
         d.k_blocks = static_cast<int32_t>((e->mode == SDDMM_B200_FP32_TC ? 3 * e->K : e->K) / 32);
-        d.reserved = 0;
         d.nnz = e->nnz;
         if ((st = begin_kernel(e, e->stream))) return st;
-        sddmm_dense_tile_kernel<<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a, e->map_b);
+        if (e->dense_own) sddmm_dense_tile_kernel<true><<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a, e->map_b);
+        else sddmm_dense_tile_kernel<false><<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a, e->map_b);
         if ((st = mark_kernel(e, "sddmm_dense_tile_kernel", e->stream))) return st;
         if (e->n_residual_items == 0) return SDDMM_B200_OK;
+    }
+    if (e->seg_residual) {
+        if ((st = launch_rowseg(e, rt_stream))) return st;
+        if (both) {
+            CU_TRY(e, cudaEventRecord(e->ev_join, e->side_stream));
+            CU_TRY(e, cudaStreamWaitEvent(e->stream, e->ev_join, 0));
+        }
+        return SDDMM_B200_OK;
     }
     RowTileArgs a;
     a.row_ptr = e->d_rp; a.col_idx = e->d_col; a.s_val = e->d_sval; a.p_val = e->d_pval;
     a.item_rows = e->d_item_rows;
     a.item_ids = e->n_dense > 0 ? e->d_item_ids : nullptr;
-    a.skip_tile_bitmap = e->n_dense > 0 ? e->d_tile_bitmap : nullptr;
-    a.skip_tiles_per_row = e->tiles_per_row;
+    a.covered = e->n_dense > 0 ? e->d_covered : nullptr;
     a.err = e->d_err; a.nnz = e->nnz;
     a.M = static_cast<int32_t>(e->M); a.K = static_cast<int32_t>(e->K);
     a.n_items = p.rowtile_items; a.item_nnz = p.rowtile_item_nnz; a.rows_per_stage = p.rowtile_rows_per_stage;
@@ -847,6 +1057,15 @@ int launch_all(sddmm_b200_engine *e) {
         CU_TRY(e, cudaEventRecord(e->ev_join, e->side_stream));
         CU_TRY(e, cudaStreamWaitEvent(e->stream, e->ev_join, 0));
     }
+    return SDDMM_B200_OK;
+}
+
+// B = NULL in an upload: take the B that sddmm_b200_stage_b left on this engine's device (same N and K)
+int take_staged_b(sddmm_b200_engine *e, int64_t N, int64_t K, const float *B) {
+    if (B) return SDDMM_B200_OK;
+    if (!e->b_stage || e->b_stage_n != N || e->b_stage_k != K)
+        return fail(e, SDDMM_B200_ERR_ARG, "B = NULL needs a B of the same shape staged by sddmm_b200_stage_b");
+    if (!e->B_on_device) e->B_on_device = e->b_stage;   // (a chunked call sets its own source)
     return SDDMM_B200_OK;
 }
 
@@ -881,6 +1100,8 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     e->knob_rowseg = env_double("SDDMM_B200_ROWSEG", -1);
     e->knob_b_evict_last = env_double("SDDMM_B200_B_EVICT_LAST", -1);
     e->knob_b_fraction = env_double("SDDMM_B200_B_FRACTION", -1);
+    e->knob_group_units = env_double("SDDMM_B200_GROUP_UNITS", -1);
+    e->knob_offset_tiles = env_double("SDDMM_B200_OFFSET_TILES", -1);
     DeviceGuard g(device);
     bool ok = g.ok;
     ok = ok && cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -888,6 +1109,8 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     for (int i = 0; i < sddmm_b200_engine::kMaxKernels; ++i)
         ok = ok && cudaEventCreate(&e->ev_begin[i]) == cudaSuccess && cudaEventCreate(&e->ev_end[i]) == cudaSuccess;
     ok = ok && cudaEventCreate(&e->ev_run0) == cudaSuccess && cudaEventCreate(&e->ev_run1) == cudaSuccess;
+    ok = ok && cudaEventCreate(&e->ev_spmm0) == cudaSuccess && cudaEventCreate(&e->ev_spmm1) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&e->ev_stage, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&e->ev_h2d, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess;
@@ -910,6 +1133,11 @@ int sddmm_b200_destroy(sddmm_b200_engine *e) {
         DeviceGuard g(e->device);
         if (e->stream) cudaStreamSynchronize(e->stream);
         if (e->arena.base) cudaFree(e->arena.base);
+        if (e->spmm_arena.base) cudaFree(e->spmm_arena.base);
+        if (e->b_stage) cudaFree(e->b_stage);
+        if (e->ev_stage) cudaEventDestroy(e->ev_stage);
+        if (e->ev_spmm0) cudaEventDestroy(e->ev_spmm0);
+        if (e->ev_spmm1) cudaEventDestroy(e->ev_spmm1);
         if (e->h_err) cudaFreeHost(e->h_err);
         if (e->h_pc) cudaFreeHost(e->h_pc);
         if (e->side_stream) cudaStreamSynchronize(e->side_stream);
@@ -929,12 +1157,13 @@ int sddmm_b200_destroy(sddmm_b200_engine *e) {
 int sddmm_b200_upload_csr(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, const int32_t *row_ptr,
                           const int32_t *col_idx, const float *s_val, const float *A, const float *B) {
     if (!e) return SDDMM_B200_ERR_ARG;
-    if (!row_ptr || !A || !B) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    if (!row_ptr || !A) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
     if (M < 1) return fail(e, SDDMM_B200_ERR_ARG, "need M >= 1");
     const int64_t nnz = row_ptr[M];
     int st = check_dims(e, M, N, K, nnz);
     if (st) return st;
     if (nnz > 0 && (!col_idx || !s_val)) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    if ((st = take_staged_b(e, N, K, B))) return st;
     DeviceGuard g(e->device);
     return upload_common(e, M, N, K, nnz, row_ptr, nullptr, col_idx, s_val, A, B, cudaMemcpyHostToDevice);
 }
@@ -942,10 +1171,11 @@ int sddmm_b200_upload_csr(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K,
 int sddmm_b200_upload_coo(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz, const int32_t *row_idx,
                           const int32_t *col_idx, const float *s_val, const float *A, const float *B) {
     if (!e) return SDDMM_B200_ERR_ARG;
-    if (!A || !B) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    if (!A) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
     int st = check_dims(e, M, N, K, nnz);
     if (st) return st;
     if (nnz > 0 && (!row_idx || !col_idx || !s_val)) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    if ((st = take_staged_b(e, N, K, B))) return st;
     DeviceGuard g(e->device);
     static const int32_t dummy = 0;
     return upload_common(e, M, N, K, nnz, nullptr, nnz ? row_idx : &dummy, col_idx, s_val, A, B, cudaMemcpyHostToDevice);
@@ -992,6 +1222,8 @@ int sddmm_b200_run(sddmm_b200_engine *e) {
     if (!e) return SDDMM_B200_ERR_ARG;
     if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "run before upload");
     DeviceGuard g(e->device);
+    // (a wait that ran out in an earlier run must not be reported again: the error word starts every run clean)
+    CU_TRY(e, cudaMemsetAsync(e->d_err, 0, sizeof(int32_t), e->stream));
     CU_TRY(e, cudaEventRecord(e->ev_run0, e->stream));
     e->last_run_timed = e->kernel_timing;
     int st = launch_all(e);
@@ -1059,11 +1291,129 @@ int sddmm_b200_set_kernel_timing(sddmm_b200_engine *e, int enabled) {
     return SDDMM_B200_OK;
 }
 
+// ---- self-test of the bounded device-side wait --------------------------------------------------------------
+namespace {
+// One thread waits, with the given probe limit, on an mbarrier phase that nothing ever completes, records the time-out
+// in the error word exactly as the kernels do, and returns.  Nothing faults and nothing hangs: the wait is bounded.
+__global__ void k_wait_timeout_selftest(int32_t *err, uint32_t limit) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+        if (!mbar_wait_bounded(&bar, 0u, limit)) atomicCAS(err, kDevOk, kDevMbarrierTimeout);
+    }
+}
+}  // namespace
+
+int sddmm_b200_selftest_wait_timeout(sddmm_b200_engine *e, int probes) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "selftest before upload (the error word lives in the upload's buffers)");
+    if (probes < 1 || probes > (1 << 16)) return fail(e, SDDMM_B200_ERR_ARG, "probes must be in [1, 65536]");
+    DeviceGuard g(e->device);
+    CU_TRY(e, cudaMemsetAsync(e->d_err, 0, sizeof(int32_t), e->stream));
+    k_wait_timeout_selftest<<<1, 32, 0, e->stream>>>(e->d_err, static_cast<uint32_t>(probes));
+    CU_TRY(e, cudaGetLastError());
+    CU_TRY(e, cudaMemcpyAsync(e->h_err, e->d_err, sizeof(int32_t), cudaMemcpyDeviceToHost, e->stream));
+    e->ran = true;   // sync() reports the error word of the last enqueued work
+    return sddmm_b200_sync(e);
+}
+
+int sddmm_b200_row_cuts(const int32_t *row_ptr, int64_t M, int parts, int64_t align, int64_t *cuts) {
+    if (!row_ptr || !cuts || M < 0 || parts < 1) return SDDMM_B200_ERR_ARG;
+    const int64_t nnz = row_ptr[M];
+    cuts[0] = 0;
+    cuts[parts] = M;
+    for (int g = 1; g < parts; ++g) {
+        const int64_t target = nnz * g / parts;
+        int64_t r = std::lower_bound(row_ptr, row_ptr + M + 1, target) - row_ptr;   // first boundary at or past the target
+        r = std::min<int64_t>(r, M);
+        if (r > 0 && target - row_ptr[r - 1] < row_ptr[r] - target) --r;              // the closer boundary wins
+        if (align > 1) r = (r + align / 2) / align * align;
+        cuts[g] = std::max<int64_t>(cuts[g - 1], std::min<int64_t>(r, M));
+    }
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_stage_b(sddmm_b200_engine **engines, int n, int64_t N, int64_t K, const float *B) {
+    if (!engines || n < 1 || !B || N < 1 || K < 1) return SDDMM_B200_ERR_ARG;
+    for (int i = 0; i < n; ++i)
+        if (!engines[i]) return SDDMM_B200_ERR_ARG;
+    const size_t bytes = static_cast<size_t>(N) * static_cast<size_t>(K) * 4;
+    // a staging buffer on every engine's device
+    for (int i = 0; i < n; ++i) {
+        sddmm_b200_engine *e = engines[i];
+        DeviceGuard g(e->device);
+        if (!g.ok) return fail(e, SDDMM_B200_ERR_COMM, "device %d cannot be selected", e->device);
+        e->b_stage_n = e->b_stage_k = 0;
+        if (e->b_stage_cap < bytes) {
+            if (e->b_stage) cudaFree(e->b_stage);
+            e->b_stage = nullptr;
+            e->b_stage_cap = 0;
+            void *p = nullptr;
+            if (cudaMalloc(&p, bytes) != cudaSuccess) {
+                cudaGetLastError();
+                return fail(e, SDDMM_B200_ERR_OOM, "staging buffer for B (%zu bytes) on device %d", bytes, e->device);
+            }
+            e->b_stage = static_cast<float *>(p);
+            e->b_stage_cap = bytes;
+        }
+    }
+    // the host link is crossed once; then the copy doubles the set of devices that hold B in every round
+    // (device to device: over NVLink where the devices are peers, through the host otherwise)
+    int rc = SDDMM_B200_OK;
+    {
+        sddmm_b200_engine *e0 = engines[0];
+        DeviceGuard g(e0->device);
+        if (cudaMemcpyAsync(e0->b_stage, B, bytes, cudaMemcpyHostToDevice, e0->stream) != cudaSuccess ||
+            cudaEventRecord(e0->ev_stage, e0->stream) != cudaSuccess)
+            rc = fail(e0, SDDMM_B200_ERR_COMM, "upload of B to device %d: %s", e0->device, cudaGetErrorString(cudaGetLastError()));
+    }
+    for (int have = 1; have < n && !rc; have *= 2) {
+        for (int i = 0; i < have && have + i < n && !rc; ++i) {
+            sddmm_b200_engine *src = engines[i], *dst = engines[have + i];
+            DeviceGuard g(dst->device);
+            cudaError_t st = cudaStreamWaitEvent(dst->stream, src->ev_stage, 0);
+            if (st == cudaSuccess) {
+                if (src->device == dst->device) {
+                    st = cudaMemcpyAsync(dst->b_stage, src->b_stage, bytes, cudaMemcpyDeviceToDevice, dst->stream);
+                } else {
+                    int can = 0;
+                    if (cudaDeviceCanAccessPeer(&can, dst->device, src->device) == cudaSuccess && can) {
+                        const cudaError_t pe = cudaDeviceEnablePeerAccess(src->device, 0);   // (already enabled is fine)
+                        if (pe != cudaSuccess) cudaGetLastError();
+                    }
+                    st = cudaMemcpyPeerAsync(dst->b_stage, dst->device, src->b_stage, src->device, bytes, dst->stream);
+                }
+            }
+            if (st == cudaSuccess) st = cudaEventRecord(dst->ev_stage, dst->stream);
+            if (st != cudaSuccess) {
+                cudaGetLastError();
+                rc = fail(dst, SDDMM_B200_ERR_COMM, "copy of B from device %d to device %d: %s", src->device, dst->device, cudaGetErrorString(st));
+            }
+        }
+    }
+    for (int i = 0; i < n; ++i) {   // drain every stream, also after a failure: nothing may still read the caller's buffer
+        sddmm_b200_engine *e = engines[i];
+        DeviceGuard g(e->device);
+        if (cudaStreamSynchronize(e->stream) != cudaSuccess && !rc) {
+            cudaGetLastError();
+            rc = fail(e, SDDMM_B200_ERR_COMM, "copy of B to device %d did not complete", e->device);
+        }
+    }
+    if (rc) return rc;
+    for (int i = 0; i < n; ++i) {
+        engines[i]->b_stage_n = N;
+        engines[i]->b_stage_k = K;
+    }
+    return SDDMM_B200_OK;
+}
+
 int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value) {
     if (!e || !name) return SDDMM_B200_ERR_ARG;
     struct { const char *name; double *slot; } knobs[] = {
         {"panels", &e->knob_panels}, {"panel_mb", &e->knob_panel_mb}, {"rowseg", &e->knob_rowseg},
-        {"b_evict_last", &e->knob_b_evict_last}, {"b_fraction", &e->knob_b_fraction},
+        {"b_evict_last", &e->knob_b_evict_last}, {"b_fraction", &e->knob_b_fraction}, {"group_units", &e->knob_group_units},
+        {"offset_tiles", &e->knob_offset_tiles},
     };
     for (auto &k : knobs)
         if (std::strcmp(name, k.name) == 0) {
@@ -1071,6 +1421,110 @@ int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value) {
             return SDDMM_B200_OK;
         }
     return fail(e, SDDMM_B200_ERR_ARG, "unknown knob '%s'", name);
+}
+
+// ---- consumer of P on the device: Y = P X ----------------------------------------------------------------
+namespace {
+using SpmmFn = void (*)(const SpmmArgs);
+SpmmFn pick_spmm(int cpl, bool exact) {
+    switch (cpl) {
+        case 1: return exact ? sddmm_spmm_kernel<1, true> : sddmm_spmm_kernel<1, false>;
+        case 2: return exact ? sddmm_spmm_kernel<2, true> : sddmm_spmm_kernel<2, false>;
+        case 4: return exact ? sddmm_spmm_kernel<4, true> : sddmm_spmm_kernel<4, false>;
+        case 8: return exact ? sddmm_spmm_kernel<8, true> : sddmm_spmm_kernel<8, false>;
+        default: return nullptr;
+    }
+}
+
+// X, Y and the consumer's unit list live in their own buffer (grown on demand, kept across calls)
+int spmm_prepare(sddmm_b200_engine *e, int64_t K2) {
+    Carve c;
+    const size_t M = static_cast<size_t>(e->M), N = static_cast<size_t>(e->N), nnz = static_cast<size_t>(e->nnz);
+    const size_t cap = nnz / 8 + std::min(M, nnz) + 8;
+    const size_t o_x = c.take(N * K2 * 4), o_y = c.take(M * K2 * 4), o_u = c.take(cap * sizeof(int2));
+    const bool grow = c.off > e->spmm_arena.cap;
+    if (grow) {
+        if (e->spmm_arena.base) CU_TRY(e, cudaFree(e->spmm_arena.base));
+        e->spmm_arena.base = nullptr;
+        e->spmm_arena.cap = 0;
+        void *p = nullptr;
+        if (cudaMalloc(&p, c.off) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(e, SDDMM_B200_ERR_OOM, "consumer buffers of %zu bytes", c.off);
+        }
+        e->spmm_arena.base = static_cast<char *>(p);
+        e->spmm_arena.cap = c.off;
+        e->spmm_units = 0;
+    }
+    char *b = e->spmm_arena.base;
+    const bool moved = e->d_spmm_units != reinterpret_cast<int2 *>(b + o_u);
+    e->d_X = reinterpret_cast<float *>(b + o_x);
+    e->d_Y = reinterpret_cast<float *>(b + o_y);
+    e->d_spmm_units = reinterpret_cast<int2 *>(b + o_u);
+    e->spmm_k2 = K2;
+    if (e->spmm_units == 0 || moved) {   // plain row segments (one panel, no groups), counted / scanned / written on the device
+        const int32_t Mi = static_cast<int32_t>(e->M);
+        const int n_tiles = static_cast<int>((e->M + kScanTile - 1) / kScanTile);
+        const int capb = e->sm_count * 32;
+        cudaStream_t s = e->stream;
+        k_unit_count<<<grid_for(e->M, kBlock, capb), kBlock, 0, s>>>(e->d_rp, e->d_col, Mi, 1, 0, e->d_unit_off);
+        k_scan_tile_sums<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
+        k_scan_sums<<<1, kScanBlock, 0, s>>>(e->d_scan_tiles, n_tiles, &e->d_pc->units);
+        k_scan_apply<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
+        k_unit_fill<<<grid_for(e->M * 32, kBlock, capb), kBlock, 0, s>>>(e->d_rp, e->d_col, Mi, 1, 0, e->d_unit_off, e->d_spmm_units);
+        CU_TRY(e, cudaGetLastError());
+        PlanCounters pc;
+        if (int rc = read_counters(e, &pc)) return rc;
+        if (pc.units == 0 || pc.units > cap) return fail(e, SDDMM_B200_ERR_CUDA, "consumer plan: %llu units for a list of %zu", pc.units, cap);
+        e->spmm_units = static_cast<int32_t>(pc.units);
+    }
+    return SDDMM_B200_OK;
+}
+}  // namespace
+
+int sddmm_b200_spmm(sddmm_b200_engine *e, int64_t K2, const float *X, float *Y) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (!e->uploaded || !e->ran) return fail(e, SDDMM_B200_ERR_STATE, "spmm before run");
+    if (K2 < 4 || K2 % 4 != 0 || K2 > 256) return fail(e, SDDMM_B200_ERR_UNSUPPORTED, "the consumer needs K2 %% 4 == 0 and 4 <= K2 <= 256 (K2 = %lld)", (long long)K2);
+    if (!Y) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
+    if (!X && K2 != e->K) return fail(e, SDDMM_B200_ERR_ARG, "X = NULL means X = B, which needs K2 == K");
+    if (e->M >= kUnitRowLimit) return fail(e, SDDMM_B200_ERR_UNSUPPORTED, "the consumer handles fewer than 2^28 rows");
+    DeviceGuard g(e->device);
+    cudaStream_t s = e->stream;
+    const size_t ybytes = static_cast<size_t>(e->M) * K2 * 4;
+    if (e->nnz == 0) {
+        std::memset(Y, 0, ybytes);
+        return sddmm_b200_sync(e);
+    }
+    int st = spmm_prepare(e, K2);   // (uses the plan scratch of the main arena: nothing of the run still needs it)
+    if (st) return st;
+    if (X) CU_TRY(e, cudaMemcpyAsync(e->d_X, X, static_cast<size_t>(e->N) * K2 * 4, cudaMemcpyHostToDevice, s));
+    CU_TRY(e, cudaEventRecord(e->ev_spmm0, s));
+    CU_TRY(e, cudaMemsetAsync(e->d_Y, 0, ybytes, s));
+    SpmmArgs a;
+    a.units = e->d_spmm_units; a.col_idx = e->d_col; a.p_val = e->d_pval; a.X = X ? e->d_X : e->d_B32; a.Y = e->d_Y;
+    a.n_units = e->spmm_units; a.K2 = static_cast<int32_t>(K2);
+    const int cpl = round_up_cpl(K2);
+    SpmmFn fn = pick_spmm(cpl, K2 == 32 * cpl);
+    int occ = 0;
+    CU_TRY(e, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kSpmmWarps * 32, 0));
+    if (occ < 1) return fail(e, SDDMM_B200_ERR_CUDA, "consumer kernel does not fit on an SM");
+    const int64_t n_quads = (static_cast<int64_t>(e->spmm_units) + 3) / 4;
+    const int grid = static_cast<int>(std::min<int64_t>((n_quads + kSpmmWarps - 1) / kSpmmWarps, static_cast<int64_t>(e->sm_count) * occ));
+    fn<<<grid, kSpmmWarps * 32, 0, s>>>(a);
+    CU_TRY(e, cudaGetLastError());
+    CU_TRY(e, cudaEventRecord(e->ev_spmm1, s));
+    CU_TRY(e, cudaMemcpyAsync(Y, e->d_Y, ybytes, cudaMemcpyDeviceToHost, s));
+    return sddmm_b200_sync(e);
+}
+
+int sddmm_b200_last_spmm_ms(sddmm_b200_engine *e, float *ms) {
+    if (!e || !ms) return SDDMM_B200_ERR_ARG;
+    if (!e->spmm_k2) return fail(e, SDDMM_B200_ERR_STATE, "last_spmm_ms before spmm");
+    DeviceGuard g(e->device);
+    CU_TRY(e, cudaEventSynchronize(e->ev_spmm1));
+    CU_TRY(e, cudaEventElapsedTime(ms, e->ev_spmm0, e->ev_spmm1));
+    return SDDMM_B200_OK;
 }
 
 int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info) {
@@ -1177,7 +1631,7 @@ int sddmm_b200_sddmm_csr_prealloc(int device, void *cuda_stream, int64_t M, int6
 
     RowTileArgs a;
     a.row_ptr = d_row_ptr; a.col_idx = d_col_idx; a.s_val = d_s_val; a.p_val = d_p_val; a.A = d_A; a.B = d_B;
-    a.item_rows = item_rows; a.item_ids = nullptr; a.skip_tile_bitmap = nullptr; a.skip_tiles_per_row = 0;
+    a.item_rows = item_rows; a.item_ids = nullptr; a.covered = nullptr;
     a.err = err; a.nnz = nnz; a.M = static_cast<int32_t>(M); a.K = static_cast<int32_t>(K);
     a.n_items = n_items; a.item_nnz = kPreallocItemNnz; a.rows_per_stage = static_cast<int32_t>(R);
     fn<<<std::min(n_items, sms * occ), kBlock, smem, st>>>(a);

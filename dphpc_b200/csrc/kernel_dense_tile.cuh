@@ -57,22 +57,23 @@ constexpr int kTmemCols = 128;
 constexpr int kDenseCtasPerSm = 2;          // resident CTAs per SM the kernel is sized for (shared memory, registers)
 
 // Per dense tile: first nonzero of each of its 64 rows inside the tile's column
-// range (CSR position), and which of the 64 columns are present.
+// range (CSR position), which of the 64 columns are present, and which of those
+// this tile computes (tiles at arbitrary offsets may overlap: a nonzero is owned
+// by exactly one of them; for tiles that do not overlap own == mask).
 struct DenseTileDesc {
     int32_t start[kDenseTile];
     unsigned long long mask[kDenseTile];
+    unsigned long long own[kDenseTile];
 };
 
 struct DenseArgs {
-    const int32_t *tile_ids;        // n_tiles dense tiles: id = tile_row * tiles_per_row + tile_col
+    const int2 *origins;            // n_tiles dense tiles: {first row, first column}, any offset
     const DenseTileDesc *descs;     // n_tiles
     const float *s_val;
     float *p_val;
     int32_t *err;
     int32_t n_tiles;
-    int32_t tiles_per_row;
     int32_t k_blocks;               // operand row length / 32
-    int32_t reserved;
     int64_t nnz;                    // bound of every S.val / P.val position (checked builds only)
 };
 
@@ -85,7 +86,8 @@ struct DenseSmem {
     static constexpr uint32_t kSval = kAcc + kAccBytes;           // 128 rows x kDenseSvalStride floats: the S.val run of each tile row, as it lies in memory
     static constexpr uint32_t kSvalBytes = 128 * kDenseSvalStride * 4;
     static constexpr uint32_t kRows = kSval + kSvalBytes;         // 3 buffers x 128 row records {first CSR position, 16-byte granules of the run, mask lo, mask hi}
-    static constexpr uint32_t kBars = kRows + 3 * 128 * 16;       // 4 mbarriers
+    static constexpr uint32_t kOwn = kRows + 3 * 128 * 16;        // 3 buffers x 128 own masks {lo, hi}
+    static constexpr uint32_t kBars = kOwn + 3 * 128 * 8;         // 4 mbarriers
     static constexpr uint32_t kTmemPtr = kBars + 4 * 8;
     static constexpr uint32_t kTotal = kTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kTotal + 1024;      // slack for the manual 1024-byte alignment
@@ -148,6 +150,9 @@ __device__ __forceinline__ void epi_barrier() {  // the 8 epilogue warps only
     asm volatile("bar.sync 1, %0;" ::"n"(kDenseEpiWarps * 32) : "memory");
 }
 
+// OWN = false: the tiles do not overlap (tiles on the 64-grid), every present nonzero is the tile's own and the own masks
+// are neither fetched nor looked at.
+template <bool OWN>
 __global__ void __launch_bounds__(kDenseThreads, kDenseCtasPerSm)
 sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b) {
@@ -159,6 +164,7 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     float *sAcc = reinterpret_cast<float *>(smem + DenseSmem::kAcc);
     float *sSval = reinterpret_cast<float *>(smem + DenseSmem::kSval);
     uint4 *sRows = reinterpret_cast<uint4 *>(smem + DenseSmem::kRows);
+    uint2 *sOwn = reinterpret_cast<uint2 *>(smem + DenseSmem::kOwn);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + DenseSmem::kBars);
     uint64_t *ops_full = &bars[0], *ops_free = &bars[1], *acc_full = &bars[2], *acc_free = &bars[3];
     uint32_t *tmem_ptr_smem = reinterpret_cast<uint32_t *>(smem + DenseSmem::kTmemPtr);
@@ -172,13 +178,13 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     // job at once; the epilogue warps request the row records of their first job; only then does the CTA meet at the
     // barrier behind which the tensor memory address is known.
     const bool is_producer = (tid == kDenseEpiWarps * 32);
-    int first0 = 0, first1 = 0;   // producer: tile ids of the CTA's first job
+    int2 first0 = make_int2(0, 0), first1 = make_int2(0, 0);   // producer: tile origins of the CTA's first job
     if (is_producer) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
         if (static_cast<int>(blockIdx.x) < n_jobs) {
-            first0 = args.tile_ids[2 * blockIdx.x];
-            first1 = (2 * static_cast<int>(blockIdx.x) + 1 < args.n_tiles) ? args.tile_ids[2 * blockIdx.x + 1] : first0;
+            first0 = args.origins[2 * blockIdx.x];
+            first1 = (2 * static_cast<int>(blockIdx.x) + 1 < args.n_tiles) ? args.origins[2 * blockIdx.x + 1] : first0;
         }
         mbar_init(ops_full, 1);
         mbar_init(ops_free, 1);
@@ -198,13 +204,13 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     const int kbs = args.k_blocks;
     const int my_jobs = (n_jobs - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     const uint32_t total = static_cast<uint32_t>(my_jobs) * static_cast<uint32_t>(kbs);
-    int cur0 = first0, cur1 = first1, nxt0 = 0, nxt1 = 0;   // ids of the job being requested / of the one after (read a job ahead of their use)
+    int2 cur0 = first0, cur1 = first1, nxt0 = first0, nxt1 = first0;   // origins of the job being requested / of the one after (read a job ahead of their use)
     bool prod_ok = true;
-    // tile ids of a job (the second tile of the last job may be missing: its operands repeat the first)
-    auto load_ids = [&](uint32_t j, int &t0, int &t1) {
+    // tile origins of a job (the second tile of the last job may be missing: its operands repeat the first)
+    auto load_ids = [&](uint32_t j, int2 &t0, int2 &t1) {
         const int job = static_cast<int>(blockIdx.x) + static_cast<int>(j) * static_cast<int>(gridDim.x);
-        t0 = args.tile_ids[2 * job];
-        t1 = ((2 * job + 1) < args.n_tiles) ? args.tile_ids[2 * job + 1] : t0;
+        t0 = args.origins[2 * job];
+        t1 = ((2 * job + 1) < args.n_tiles) ? args.origins[2 * job + 1] : t0;
     };
     // request operand k-block `it` (called once per it, in order)
     auto issue_tma = [&](uint32_t it) -> bool {
@@ -216,8 +222,8 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
             cur1 = nxt1;
             if (j + 1 < static_cast<uint32_t>(my_jobs)) load_ids(j + 1, nxt0, nxt1);
         }
-        const int r0 = (cur0 / args.tiles_per_row) * kDenseTile, c0 = (cur0 % args.tiles_per_row) * kDenseTile;
-        const int r1 = (cur1 / args.tiles_per_row) * kDenseTile, c1 = (cur1 % args.tiles_per_row) * kDenseTile;
+        // (TMA coordinates: x = k offset, a multiple of 32 floats = 128 bytes; y = any row index, rows past the end read as zero)
+        const int r0 = cur0.x, c0 = cur0.y, r1 = cur1.x, c1 = cur1.y;
         // operand buffer free again?  (read by the MMAs of k-block it - 1)
         if (!mbar_wait_bounded(ops_free, ph ^ 1u)) return false;
         unsigned char *sa = smem + DenseSmem::kStage0;
@@ -239,8 +245,10 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                 const DenseTileDesc *d = args.descs + t;
                 cp_async_4(&dst->x, &d->start[tid & 63]);
                 cp_async_8(&dst->z, &d->mask[tid & 63]);
+                if (OWN) cp_async_8(sOwn + buf * 128 + tid, &d->own[tid & 63]);
             } else {
                 *dst = make_uint4(0u, 0u, 0u, 0u);
+                if (OWN) sOwn[buf * 128 + tid] = make_uint2(0u, 0u);
             }
         }
     };
@@ -343,17 +351,21 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
             for (int u = 0; u < 8; ++u) {
                 const int r = (8 * half + u) * kDenseEpiWarps + warp;
                 const uint4 d = sRows[buf * 128 + r];
+                uint2 o = make_uint2(d.z, d.w);
+                if (OWN) o = sOwn[buf * 128 + r];
                 // lane l owns the adjacent columns 2l and 2l+1: one 8-byte read of the accumulator pair; the second
-                // column's nonzero (if any) directly follows the first one's in the run
+                // column's nonzero (if any) directly follows the first one's in the run.  Positions come from the
+                // PRESENCE mask, what is written from the OWN mask.
                 const int st = static_cast<int>(d.x);
                 const uint32_t w = upper ? d.w : d.z;                       // the mask word that holds this lane's two bits
-                const uint32_t pair = (w >> pshift) & 3u;
+                const uint32_t present = (w >> pshift) & 3u;
+                const uint32_t pair = ((upper ? o.y : o.x) >> pshift) & 3u;
                 const int k0 = (upper ? __popc(d.z) : 0) + __popc(w & pbelow);   // offset of column 2l inside the run
                 const float2 a = *reinterpret_cast<const float2 *>(sAcc + r * kDenseAccStride + 2 * lane);
                 const float *srow = sSval + r * kDenseSvalStride + (st & 3) + k0;
                 float *prow = args.p_val + st + k0;
                 if (pair & 1u) __stcs(prow, a.x * srow[0]);
-                if (pair & 2u) __stcs(prow + (pair & 1u), a.y * srow[pair & 1u]);
+                if (pair & 2u) __stcs(prow + (present & 1u), a.y * srow[present & 1u]);
             }
         };
 

@@ -21,8 +21,8 @@
 // hint, the streams evict_first).  col_idx, S.val and P.val stay in CSR order: a run is a
 // contiguous piece of its row.
 //
-// A "chunk" is 4 consecutive K elements.  CPL = chunks per lane, so K <= 32*CPL.
-// EXACT = (K == 32*CPL): no chunk-range predicates in the inner loop.
+// A "chunk" is 4 consecutive K elements (8 for wide bf16 chunks).  CPL = chunks per lane, so K <= 8 * CPL chunks.
+// EXACT = (K == 8 * CPL chunks): no chunk-range predicates in the inner loop.
 #pragma once
 
 #include "device_utils.cuh"
@@ -70,16 +70,22 @@ __device__ __forceinline__ uint2 ld_chunk_hint(const uint2 *p, uint64_t pol) {
     asm("ld.global.nc.L2::cache_hint.v2.u32 {%0, %1}, [%2], %3;" : "=r"(v.x), "=r"(v.y) : "l"(p), "l"(pol));
     return v;
 }
+__device__ __forceinline__ uint4 ld_chunk_hint(const uint4 *p, uint64_t pol) {
+    uint4 v;
+    asm("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
+    return v;
+}
 
 // HINT: the B gathers carry the L2 evict_last policy (one instantiation with, one without: no branch per load).
 template <int CPL, bool EXACT, typename ET, bool HINT>
 __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_MINB1 : SDDMM_ROWSEG_MINBN) sddmm_rowseg_kernel(const RowSegArgs args) {
     using chunk_t = typename ChunkOf<ET>::type;
+    using areg_t = typename ChunkOf<ET>::areg;
     const int lane = threadIdx.x & 31;
     const int gl = lane & 7;          // lane inside its 8-lane group = chunk of a 128-byte piece = nonzero of the segment
     const int gbase = lane & 24;      // first lane of the group
     const int grp = lane >> 3;        // which of the warp's 4 units
-    const int nchunks = EXACT ? 8 * CPL : (args.K >> 2);
+    const int nchunks = EXACT ? 8 * CPL : (args.K / ChunkOf<ET>::elems);
     const uint32_t row_bytes = static_cast<uint32_t>(nchunks) * sizeof(chunk_t);
     constexpr int QS = (CPL >= 2) ? 2 : 1;   // chunks gathered per nonzero per step
     // chunks of this lane that exist (K < 32 * CPL: the lane's last chunks lie past the row and are read as chunk 0, times zero)
@@ -125,13 +131,13 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
         const float s = s_own;
 
         // ---- this lane's chunk(s) of the segment's A row ----
-        float4 areg[CPL];
+        areg_t areg[CPL];
         {
             const unsigned char *arow = Ab + static_cast<uint64_t>(static_cast<uint32_t>(row)) * row_bytes;
 #pragma unroll
             for (int c = 0; c < CPL; ++c) {
-                areg[c] = chunk_to_f4(ldg_chunk(reinterpret_cast<const chunk_t *>(arow + ch_off[c])));
-                if (!EXACT) { areg[c].x *= ch_on[c]; areg[c].y *= ch_on[c]; areg[c].z *= ch_on[c]; areg[c].w *= ch_on[c]; }
+                areg[c] = unpack_chunk(ldg_chunk(reinterpret_cast<const chunk_t *>(arow + ch_off[c])));
+                if (!EXACT) scale_chunk(areg[c], ch_on[c]);
             }
         }
         // ---- the 8 column indices of the segment ----
@@ -160,8 +166,8 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int qq = 0; qq < QS; ++qq) acc[i] = dot4(areg[qq], chunk_to_f4(bq[i][qq]), acc[i]);
-        // K > 64: the remaining chunks of the same 8 rows
+            for (int qq = 0; qq < QS; ++qq) acc[i] = dot_chunk(areg[qq], unpack_chunk(bq[i][qq]), acc[i]);
+        // more than QS chunks per lane: the remaining chunks of the same 8 rows
 #pragma unroll
         for (int q0 = QS; q0 < CPL; q0 += QS) {
 #pragma unroll
@@ -174,7 +180,7 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int qq = 0; qq < QS; ++qq) acc[i] = dot4(areg[q0 + qq], chunk_to_f4(bq[i][qq]), acc[i]);
+                for (int qq = 0; qq < QS; ++qq) acc[i] = dot_chunk(areg[q0 + qq], unpack_chunk(bq[i][qq]), acc[i]);
         }
         const float dot = group8_transpose_reduce(acc, gl);   // lane gl: nonzero gl of the segment
         if (valid) __stcs(args.p_val + j, dot * s);
@@ -183,6 +189,152 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
         if (q >= n_quads) break;   // warp-uniform
         u_cur = u_nxt;
         u_nxt = u_nxt2;
+    }
+}
+
+// ---- row groups: segments shared by NR consecutive rows with identical column lists ---------------
+// Block-structured matrices (several unknowns per mesh node) repeat one column list over the G rows of a block row.
+// A unit of such a group covers 8 columns of the shared list for all G rows: each B row is gathered ONCE and dotted
+// with G rows of A, so the traffic between L2 and the SM -- what bounds the gather -- drops by the factor G.
+//   ghdr[u]  .x = CSR position of the segment in the group's first row, .y = first row * 8 + (count - 1),
+//            .z = row length L (row t of the group holds the segment at .x + t * L: equal lengths, consecutive rows),
+//            .w = rows that share the unit (1 for rows outside matching groups, else G)
+// fp32 storage, K = 32 * CPL, CPL in {1, 2}; NR = G.
+struct RowSegGroupArgs {
+    const int4 *ghdr;         // n_units (> 0)
+    const int32_t *col_idx;   // nnz
+    const float *s_val;       // nnz
+    float *p_val;             // nnz
+    const float *A;           // M x K
+    const float *B;           // N x K
+    int32_t n_units;
+    int32_t K;
+};
+
+// (K = 32: three resident CTAs per SM -- 207 against 273 us on the banded 3x3-block configuration at K = 32; K = 64 needs
+// the registers of two)
+template <int CPL, int NR>
+__global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? 3 : 2) sddmm_rowseg_group_kernel(const RowSegGroupArgs args) {
+    const int lane = threadIdx.x & 31;
+    const int gl = lane & 7;
+    const int gbase = lane & 24;
+    const int grp = lane >> 3;
+    constexpr uint32_t row_bytes = 8 * CPL * sizeof(float4);
+
+    const int64_t n_quads = (static_cast<int64_t>(args.n_units) + 3) >> 2;
+    const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kRowSegWarps;
+    int64_t q = static_cast<int64_t>(blockIdx.x) * kRowSegWarps + (threadIdx.x >> 5);
+    if (q >= n_quads) return;
+    const int last_unit = args.n_units - 1;
+    const unsigned char *Ab = reinterpret_cast<const unsigned char *>(args.A) + gl * sizeof(float4);
+    const unsigned char *Bb = reinterpret_cast<const unsigned char *>(args.B) + gl * sizeof(float4);
+
+    // every load is unconditional and in range (clamped unit, clamped slot, clamped row of the group); stores are predicated
+    auto load_unit = [&](int64_t qq) -> int4 {
+        const int64_t u = 4 * qq + grp;
+        return __ldcs(args.ghdr + (u < last_unit ? u : last_unit));
+    };
+    auto own_slot = [&](const int4 &u) -> int { return u.x + min(gl, u.y & 7); };
+
+    int4 u_cur = load_unit(q);
+    int4 u_nxt = load_unit(q + n_warps);
+    int c_own = __ldcs(args.col_idx + own_slot(u_cur));
+
+    while (true) {
+        const int row = u_cur.y >> 3;
+        const int rows = u_cur.w;      // 1 .. NR
+        const int L = u_cur.z;
+        const int slot = own_slot(u_cur);
+        const bool valid = (gl <= (u_cur.y & 7)) && (4 * q + grp <= last_unit);
+
+        // S values of this lane's nonzero in every row of the group (used after the dots)
+        float sv[NR];
+#pragma unroll
+        for (int t = 0; t < NR; ++t) sv[t] = __ldcs(args.s_val + slot + min(t, rows - 1) * L);
+        // this lane's chunks of the group's A rows
+        float4 areg[NR][CPL];
+#pragma unroll
+        for (int t = 0; t < NR; ++t) {
+            const unsigned char *arow = Ab + static_cast<uint64_t>(static_cast<uint32_t>(row + min(t, rows - 1))) * row_bytes;
+#pragma unroll
+            for (int c = 0; c < CPL; ++c) areg[t][c] = __ldg(reinterpret_cast<const float4 *>(arow) + 8 * c);
+        }
+        const unsigned char *brow[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            brow[i] = Bb + static_cast<uint64_t>(static_cast<uint32_t>(__shfl_sync(kFullMask, c_own, gbase + i))) * row_bytes;
+
+        float acc[NR][8];
+#pragma unroll
+        for (int t = 0; t < NR; ++t)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[t][i] = 0.f;
+
+        // one 128-byte piece of the 8 B rows at a time: gathered once, used by every row of the group
+        float4 bq[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bq[i] = __ldg(reinterpret_cast<const float4 *>(brow[i]));
+        const int64_t q_next = q + n_warps;
+        const int4 u_nxt2 = load_unit(q_next + n_warps);
+        c_own = __ldcs(args.col_idx + own_slot(u_nxt));
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) {
+#pragma unroll
+            for (int t = 0; t < NR; ++t)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[t][i] = dot4(areg[t][c], bq[i], acc[t][i]);
+            if (c + 1 < CPL) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) bq[i] = __ldg(reinterpret_cast<const float4 *>(brow[i]) + 8 * (c + 1));
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < NR; ++t) {
+            const float dot = group8_transpose_reduce(acc[t], gl);
+            if (valid && t < rows) __stcs(args.p_val + u_cur.x + gl + t * L, dot * sv[t]);
+        }
+
+        q = q_next;
+        if (q >= n_quads) break;   // warp-uniform
+        u_cur = u_nxt;
+        u_nxt = u_nxt2;
+    }
+}
+
+// rows of group g when groups of G rows start at row `first` (group 0 = the rows before it)
+__device__ __forceinline__ void unit_group_rows(int32_t g, int32_t G, int32_t first, int32_t M, int32_t &r0, int32_t &r1) {
+    r0 = g == 0 ? 0 : first + (g - 1) * G;
+    r1 = g == 0 ? first : min(r0 + G, M);
+}
+// one thread per row: units the row contributes -- the leader of a matching group speaks for its whole group
+__global__ void k_group_unit_count(const int32_t *__restrict__ rp, int32_t M, int32_t G, int32_t first, const uint8_t *__restrict__ group_ok,
+                                   int32_t *__restrict__ counts) {
+    for (int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; r < M; r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int32_t g = r < first ? 0 : 1 + static_cast<int32_t>((r - first) / G);
+        int32_t r0, r1;
+        unit_group_rows(g, G, first, M, r0, r1);
+        const int32_t len = rp[r + 1] - rp[r];
+        counts[r] = (group_ok[g] && r != r0) ? 0 : (len + 7) >> 3;
+    }
+}
+// one warp per row: write its units at the scanned offset
+__global__ void k_group_unit_fill(const int32_t *__restrict__ rp, int32_t M, int32_t G, int32_t first, const uint8_t *__restrict__ group_ok,
+                                  const int32_t *__restrict__ offsets, int4 *__restrict__ ghdr) {
+    const int lane = threadIdx.x & 31;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t r = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5; r < M; r += n_warps) {
+        const int32_t g = r < first ? 0 : 1 + static_cast<int32_t>((r - first) / G);
+        int32_t r0, r1;
+        unit_group_rows(g, G, first, M, r0, r1);
+        const bool matched = group_ok[g] != 0;
+        if (matched && r != r0) continue;
+        const int32_t s = rp[r], e = rp[r + 1];
+        const int32_t n_units = (e - s + 7) >> 3;
+        const int32_t off = offsets[r];
+        for (int32_t u = lane; u < n_units; u += 32) {
+            const int32_t start = s + 8 * u;
+            ghdr[off + u] = make_int4(start, static_cast<int32_t>(r) * 8 + (min(8, e - start) - 1), e - s, matched ? G : 1);
+        }
     }
 }
 
@@ -238,6 +390,44 @@ __global__ void k_unit_fill(const int32_t *__restrict__ rp, const int32_t *__res
             const int32_t first = s + 8 * u;
             const int32_t cnt = min(8, e - first);
             units[off + u] = make_int2(first, i * 8 + (cnt - 1));
+        }
+    }
+}
+
+// ---- units over what the dense tiles left: runs of nonzeros whose bit in `covered` is clear -----------------------
+// first position in [j, b) whose bit equals `want`, or b
+__device__ __forceinline__ int32_t next_bit(const uint32_t *__restrict__ bits, int32_t j, int32_t b, bool want) {
+    while (j < b) {
+        uint32_t word = bits[j >> 5];
+        if (!want) word = ~word;
+        word >>= (j & 31);
+        if (word) return min(b, j + __ffs(word) - 1);
+        j = (j | 31) + 1;
+    }
+    return b;
+}
+// one thread per row: units of its uncovered runs
+__global__ void k_residual_unit_count(const int32_t *__restrict__ rp, int32_t M, const uint32_t *__restrict__ covered, int32_t *__restrict__ counts) {
+    for (int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; r < M; r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int32_t b = rp[r + 1];
+        int32_t n = 0;
+        for (int32_t j = next_bit(covered, rp[r], b, false); j < b;) {
+            const int32_t e = next_bit(covered, j, b, true);
+            n += (e - j + 7) >> 3;
+            j = next_bit(covered, e, b, false);
+        }
+        counts[r] = n;
+    }
+}
+__global__ void k_residual_unit_fill(const int32_t *__restrict__ rp, int32_t M, const uint32_t *__restrict__ covered,
+                                     const int32_t *__restrict__ offsets, int2 *__restrict__ units) {
+    for (int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; r < M; r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int32_t b = rp[r + 1];
+        int32_t off = offsets[r];
+        for (int32_t j = next_bit(covered, rp[r], b, false); j < b;) {
+            const int32_t e = next_bit(covered, j, b, true);
+            for (int32_t first = j; first < e; first += 8) units[off++] = make_int2(first, static_cast<int32_t>(r) * 8 + (min(8, e - first) - 1));
+            j = next_bit(covered, e, b, false);
         }
     }
 }

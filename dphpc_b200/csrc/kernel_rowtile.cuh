@@ -37,8 +37,7 @@ struct RowTileArgs {
     const void *B;            // N x K, element type ET
     const int2 *item_rows;    // per item: {row of its first nonzero, row of its last nonzero}
     const int32_t *item_ids;  // optional indirection (items that still hold work), or nullptr
-    const uint32_t *skip_tile_bitmap;  // optional: nonzeros whose 64x64 tile bit is set are owned by another kernel
-    int32_t skip_tiles_per_row;        // number of 64-column tiles per tile row in the bitmap
+    const uint32_t *covered;           // optional, one bit per nonzero: set = owned by another kernel (the dense tiles)
     int32_t *err;             // device error word
     int64_t nnz;
     int32_t M, K;
@@ -243,12 +242,9 @@ __global__ void __launch_bounds__(kRowTileWarps * 32, (CPL == 1) ? SDDMM_ROWTILE
                         cached_end = sRp[rf + 1];
                     }
                 }
-                if (args.skip_tile_bitmap) {
-                    if (valid) {
-                        const int c_own = __ldg(args.col_idx + j);
-                        const int64_t bit = static_cast<int64_t>((r0 + lr) >> 6) * args.skip_tiles_per_row + (c_own >> 6);
-                        if ((args.skip_tile_bitmap[bit >> 5] >> (bit & 31)) & 1u) valid = false;
-                    }
+                if (args.covered) {   // the window is 32-aligned: its 32 ownership bits are one word
+                    const uint32_t word = __ldg(args.covered + (wb >> 5));
+                    if ((word >> lane) & 1u) valid = false;
                     if (__ballot_sync(kFullMask, valid) == 0u) continue;
                 }
 

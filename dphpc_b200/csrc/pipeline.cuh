@@ -54,21 +54,11 @@ void chunk_copies_enqueued(void *user) {
     s->enqueued->store(s->index + 1, std::memory_order_release);
 }
 
-// first row of every chunk: the row boundary closest to c * nnz / chunks (a multiple of 64 rows when the
-// matrix is large, so that every chunk keeps the 64 x 64 tile grid of the tensor-core path)
+// first row of every chunk: the nnz-balanced cuts every sharded path uses (sddmm_b200_row_cuts), a multiple of 64 rows
+// when the matrix is large, so that every chunk keeps the 64 x 64 tile grid of the tensor-core path
 std::vector<int64_t> chunk_cuts(const int32_t *row_ptr, int64_t M, int chunks) {
-    const int64_t nnz = row_ptr[M];
-    const int64_t align = M >= int64_t(64) * 8 * chunks ? 64 : 1;
     std::vector<int64_t> cuts(static_cast<size_t>(chunks) + 1, 0);
-    cuts[static_cast<size_t>(chunks)] = M;
-    for (int c = 1; c < chunks; ++c) {
-        const int64_t target = nnz * c / chunks;
-        int64_t r = std::lower_bound(row_ptr, row_ptr + M + 1, target) - row_ptr;
-        r = std::min<int64_t>(r, M);
-        if (r > 0 && target - row_ptr[r - 1] < row_ptr[r] - target) --r;
-        if (align > 1) r = (r + align / 2) / align * align;
-        cuts[static_cast<size_t>(c)] = std::max<int64_t>(cuts[static_cast<size_t>(c) - 1], std::min<int64_t>(r, M));
-    }
+    sddmm_b200_row_cuts(row_ptr, M, chunks, M >= int64_t(64) * 8 * chunks ? 64 : 1, cuts.data());
     return cuts;
 }
 

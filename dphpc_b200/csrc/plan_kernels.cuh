@@ -30,6 +30,8 @@ struct PlanCounters {
     int group_count[9];                  // matching row groups, same slots
     int residual_items;
     unsigned long long units;            // row segments of the row-segment path
+    unsigned long long window_nnz;       // nonzeros inside the selected 64x64 windows (summed per window)
+    int n_anchors;                       // candidate origins of the arbitrary-offset tile detection
 };
 
 __device__ __forceinline__ int len_bin(int len) {
@@ -165,64 +167,180 @@ __global__ void k_tile_count(const int32_t *__restrict__ rp, const int32_t *__re
     if (run) atomicAdd(&counts[base + cur], run);
 }
 
-// tiles with >= min_count nonzeros: set their bit, append them to the dense list
-__global__ void k_tile_select(const int32_t *__restrict__ counts, int64_t n_tiles, int32_t min_count, uint32_t *__restrict__ bitmap,
-                              int32_t *__restrict__ dense_ids, int32_t cap, PlanCounters *__restrict__ pc) {
+// aligned tiles with >= min_count nonzeros: append their origin (first row, first column) to the dense list
+__global__ void k_tile_select(const int32_t *__restrict__ counts, int64_t n_tiles, int32_t tiles_per_row, int32_t min_count,
+                              int2 *__restrict__ origins, int32_t cap, PlanCounters *__restrict__ pc) {
     for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < n_tiles;
          t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int c = counts[t];
-        if (c >= min_count) {
+        if (counts[t] >= min_count) {
             const int slot = atomicAdd(&pc->dense_tiles, 1);
             if (slot < cap) {
-                dense_ids[slot] = static_cast<int32_t>(t);
-                atomicOr(&bitmap[t >> 5], 1u << (t & 31));
-                atomicAdd(&pc->dense_nnz, static_cast<unsigned long long>(c));
+                origins[slot] = make_int2(static_cast<int32_t>(t / tiles_per_row) * 64, static_cast<int32_t>(t % tiles_per_row) * 64);
+                atomicAdd(&pc->window_nnz, static_cast<unsigned long long>(counts[t]));
             }
         }
     }
 }
 
-// one thread per (dense tile, row): first CSR position of the row inside the tile's column
-// range, presence mask of its 64 columns; also credits the covered nonzeros to their work items
+// first position of [lo, hi) whose column is >= c (columns sorted inside a row)
+__device__ __forceinline__ int32_t lower_col(const int32_t *__restrict__ col, int32_t lo, int32_t hi, int64_t c) {
+    while (lo < hi) {
+        const int32_t mid = (lo + hi) >> 1;
+        if (col[mid] < c) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+// ---- dense 64x64 windows at ARBITRARY offsets ("randomly placed blocks") ---------------------------------------------
+// Step 1, one warp per row: nonzero j is a CANDIDATE when at least `half` nonzeros of its row lie in the 64 columns
+// that start at its own column.  One bit per nonzero.
+__global__ void k_window_candidates(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t half,
+                                    uint32_t *__restrict__ cand) {
+    const int lane = threadIdx.x & 31;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t r = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5; r < M; r += n_warps) {
+        const int32_t a = rp[r], b = rp[r + 1];
+        if (b - a < half) continue;
+        for (int32_t j = a + lane; j < b; j += 32) {
+            if (j + half > b) continue;
+            // `half` nonzeros from j on fit into 64 columns <=> the (half-1)-th successor is closer than 64 columns
+            if (col[j + half - 1] - col[j] < 64) atomicOr(&cand[j >> 5], 1u << (j & 31));
+        }
+    }
+}
+
+// nonzeros of row r inside columns [c, c + 64)
+__device__ __forceinline__ int32_t window_count(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t r, int32_t c) {
+    const int32_t a = rp[r], b = rp[r + 1];
+    const int32_t lo = lower_col(col, a, b, c);
+    return lower_col(col, lo, min(b, lo + 64), static_cast<int64_t>(c) + 64) - lo;
+}
+
+// Step 2, one thread per row: the row's candidates are cut greedily, left to right, into 64-column windows (a window
+// starts at the first candidate at or after the end of the previous one), so every window of a row is visited once.  A
+// window whose row above is NOT dense in the same columns is the top edge of a block and anchors a tile there -- and
+// further tiles every 64 rows below it for as long as those rows stay dense in the same columns.
+__global__ void k_window_anchors(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t half,
+                                 const uint32_t *__restrict__ cand, int2 *__restrict__ anchors, int32_t cap, int *__restrict__ n_anchors) {
+    // first candidate position in [j, b), or b
+    auto next_cand = [&](int32_t j, int32_t b) -> int32_t {
+        while (j < b) {
+            const uint32_t word = cand[j >> 5] >> (j & 31);
+            if (word) return min(b, j + __ffs(word) - 1);
+            j = (j | 31) + 1;
+        }
+        return b;
+    };
+    for (int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; r < M; r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int32_t a = rp[r], b = rp[r + 1];
+        if (b - a < half) continue;
+        for (int32_t w = next_cand(a, b); w < b;) {
+            const int32_t c = col[w];
+            const bool top = (r == 0) || window_count(rp, col, static_cast<int32_t>(r) - 1, c) < half;
+            if (top) {
+                for (int32_t rr = static_cast<int32_t>(r); rr < M; rr += 64) {
+                    if (rr != r && window_count(rp, col, rr, c) < half) break;
+                    const int slot = atomicAdd(n_anchors, 1);
+                    if (slot < cap) anchors[slot] = make_int2(rr, c);
+                }
+            }
+            w = next_cand(lower_col(col, w, b, static_cast<int64_t>(c) + 64), b);
+        }
+    }
+}
+
+// Step 3, one thread per (anchor, row): nonzeros inside the anchored window, summed per anchor
+__global__ void k_anchor_counts(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, const int2 *__restrict__ anchors,
+                                int32_t n_anchors, int32_t *__restrict__ counts) {
+    const int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (g >= static_cast<int64_t>(n_anchors) * 64) return;
+    const int2 o = anchors[g >> 6];
+    const int32_t row = o.x + static_cast<int32_t>(g & 63);
+    int32_t n = row < M ? window_count(rp, col, row, o.y) : 0;
+    for (int off = 16; off > 0; off >>= 1) n += __shfl_xor_sync(kFullMask, n, off);   // (64 rows of an anchor = 2 warps)
+    if ((threadIdx.x & 31) == 0 && n) atomicAdd(&counts[g >> 6], n);
+}
+// Step 4: anchors whose window holds >= min_count nonzeros become dense tiles
+__global__ void k_anchor_select(const int2 *__restrict__ anchors, const int32_t *__restrict__ counts, int32_t n_anchors, int32_t min_count,
+                                int2 *__restrict__ origins, int32_t cap, PlanCounters *__restrict__ pc) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_anchors || counts[t] < min_count) return;
+    const int slot = atomicAdd(&pc->dense_tiles, 1);
+    if (slot < cap) {
+        origins[slot] = anchors[t];
+        atomicAdd(&pc->window_nnz, static_cast<unsigned long long>(counts[t]));
+    }
+}
+
+// one thread per (dense tile, row): first CSR position of the row inside the tile's column range, presence mask of its 64
+// columns, and the OWN mask -- the nonzeros this tile computes.  Tiles at arbitrary offsets may overlap: a nonzero belongs
+// to the tile that claims its bit in the `covered` bitmap first.  Owned nonzeros are credited to their work items.
 template <typename Desc>
-__global__ void k_tile_rows(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t tiles_per_row,
-                            const int32_t *__restrict__ dense_ids, int32_t n_dense, Desc *__restrict__ descs, int32_t item_nnz,
-                            int32_t *__restrict__ item_covered) {
+__global__ void k_tile_rows(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, const int2 *__restrict__ origins,
+                            int32_t n_dense, Desc *__restrict__ descs, uint32_t *__restrict__ covered, int32_t item_nnz,
+                            int32_t *__restrict__ item_covered, int32_t *__restrict__ tile_owned, PlanCounters *__restrict__ pc) {
     const int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (g >= static_cast<int64_t>(n_dense) * 64) return;
     const int t = static_cast<int>(g >> 6), r = static_cast<int>(g & 63);
-    const int id = dense_ids[t];
-    const int row = (id / tiles_per_row) * 64 + r;
-    const int c0 = (id % tiles_per_row) * 64;
+    const int2 o = origins[t];
+    const int row = o.x + r;
+    const int c0 = o.y;
     int start = 0;
-    unsigned long long mask = 0ull;
+    unsigned long long mask = 0ull, own = 0ull;
     if (row < M) {
-        int lo = rp[row], hi = rp[row + 1];
-        const int end = hi;
-        while (lo < hi) {  // first position with col >= c0
-            const int mid = (lo + hi) >> 1;
-            if (col[mid] < c0) lo = mid + 1; else hi = mid;
-        }
-        start = lo;
+        const int end = rp[row + 1];
+        start = lower_col(col, rp[row], end, c0);
         int n = 0;
-        for (int j = lo; j < end; ++j) {
+        for (int j = start; j < end; ++j) {
             const int c = col[j] - c0;
             if (c >= 64) break;
             mask |= 1ull << c;
             ++n;
         }
-        // credit [start, start+n) to the work items it overlaps
-        int j = start, left = n;
-        while (left > 0) {
-            const int item = j / item_nnz;
-            const int take = min(left, (item + 1) * item_nnz - j);
-            atomicAdd(&item_covered[item], take);
+        // claim [start, start + n) word by word; bit k of `got` = nonzero start + k is ours
+        unsigned long long got = 0ull;
+        for (int j = start; j < start + n;) {
+            const int w = j >> 5, first = j & 31;
+            const int take = min(32 - first, start + n - j);
+            const uint32_t bits = (take == 32 ? 0xffffffffu : ((1u << take) - 1u)) << first;
+            const uint32_t old = atomicOr(&covered[w], bits);
+            got |= static_cast<unsigned long long>((bits & ~old) >> first) << (j - start);
             j += take;
-            left -= take;
+        }
+        // rank k of the run -> its column bit
+        int k = 0, owned = 0;
+        for (unsigned long long m = mask; m; m &= m - 1, ++k)
+            if ((got >> k) & 1ull) {
+                own |= m & (~m + 1);
+                ++owned;
+            }
+        if (owned) {
+            atomicAdd(&pc->dense_nnz, static_cast<unsigned long long>(owned));
+            atomicAdd(&tile_owned[t], owned);
+        }
+        // credit the owned nonzeros to the work items they lie in
+        for (int kk = 0; kk < n;) {
+            const int j = start + kk;
+            const int item = j / item_nnz;
+            const int take = min(n - kk, (item + 1) * item_nnz - j);
+            const unsigned long long seg = (take == 64 ? ~0ull : ((1ull << take) - 1ull)) << kk;
+            const int c = __popcll(got & seg);
+            if (c) atomicAdd(&item_covered[item], c);
+            kk += take;
         }
     }
     descs[t].start[r] = start;
     descs[t].mask[r] = mask;
+    descs[t].own[r] = own;
+}
+
+// Overlapping windows: a tile that ended up owning too few nonzeros (most of its window went to its neighbours) is not
+// worth a job.  The tiles that own enough are copied to a second list, on which the ownership is then decided afresh.
+__global__ void k_tile_keep(const int2 *__restrict__ origins, const int32_t *__restrict__ tile_owned, int32_t n_dense, int32_t min_owned,
+                            int2 *__restrict__ kept, PlanCounters *__restrict__ pc) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_dense || tile_owned[t] < min_owned) return;
+    kept[atomicAdd(&pc->dense_tiles, 1)] = origins[t];
 }
 
 // work items that still hold nonzeros outside the dense tiles

@@ -14,23 +14,23 @@ import numpy as np
 
 
 def row_cuts(row_ptr: np.ndarray, parts: int, align: int = 1) -> np.ndarray:
-    """parts+1 row indices, cut[0] = 0, cut[parts] = M, non-decreasing.
+    """parts+1 row indices, cut[0] = 0, cut[parts] = M, non-decreasing (sddmm_b200_row_cuts of the C ABI: the one
+    definition the chunked call, the multi-device competitor and the one-process-per-GPU bench share).
 
     align > 1 moves every inner cut to the nearest multiple of `align` rows: with align = 64 the 64x64
     tiles of each shard coincide with those of the whole matrix, so a block that is dense globally is
     still one dense tile locally (the tensor-core path looks at aligned tiles of what it is given)."""
-    row_ptr = np.asarray(row_ptr)
-    M = row_ptr.size - 1
-    nnz = int(row_ptr[M])
-    targets = (np.arange(1, parts, dtype=np.int64) * nnz) // parts
-    hi = np.minimum(np.searchsorted(row_ptr, targets, side="left").astype(np.int64), M)   # first boundary at or past the target
-    lo = np.maximum(hi - 1, 0)
-    rp = row_ptr.astype(np.int64)
-    inner = np.where(targets - rp[lo] < rp[hi] - targets, lo, hi)                          # the closer row boundary wins
-    if align > 1:
-        inner = np.minimum((inner + align // 2) // align * align, M)
-    cuts = np.concatenate(([0], inner, [M]))
-    return np.maximum.accumulate(cuts)
+    import ctypes as C
+
+    from .capi import load_engine_lib
+
+    rp = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    cuts = np.zeros(parts + 1, dtype=np.int64)
+    st = load_engine_lib().sddmm_b200_row_cuts(C.c_void_p(rp.ctypes.data), C.c_int64(rp.size - 1), C.c_int(parts), C.c_int64(align),
+                                               C.c_void_p(cuts.ctypes.data))
+    if st:
+        raise ValueError(f"sddmm_b200_row_cuts: status {st}")
+    return cuts
 
 
 def shard(row_ptr, col_idx, s_val, A, rank: int, parts: int, align: int = 1):

@@ -11,8 +11,10 @@
 // into disjoint ranges of the host P.values.  The reference's dispatcher (`CSR::_dispatch`,
 // src/matrices/CSR.hpp:214-264) balances nonzeros over thread blocks the same way.
 //
-// One engine (include/sddmm_b200.h) per device.  Uploads and downloads of the devices run on one helper
-// thread each (they share PCIe but not a stream); the threads are joined before every member returns.
+// One engine (include/sddmm_b200.h) per device.  B crosses the host link once and is then copied device to
+// device (sddmm_b200_stage_b: NVLink between peers, log2(G) rounds); the shards of S and A go up on one helper
+// thread per device (they share the host but not a stream); the threads are joined before every member returns.
+// A listed device that does not exist is left out with a message: the competitor then runs on the devices that do.
 // run_* enqueues on every device, then waits for all of them; the caller's current device is left as it was.
 // A device may be listed more than once (two engines on one GPU): the sharding logic is then testable
 // on a single-GPU machine.
@@ -46,21 +48,10 @@ public:
     GPUB200Multi(const GPUB200Multi &) = delete;
     GPUB200Multi &operator=(const GPUB200Multi &) = delete;
 
-    // first row of every shard (size shards + 1): the row boundary closest to g * nnz / G, optionally a multiple of `align`
+    // first row of every shard (size shards + 1): sddmm_b200_row_cuts, the one definition every sharded path uses
     static std::vector<int64_t> row_cuts(const std::vector<int> &row_ptr, int parts, int64_t align = 1) {
-        const int64_t M = static_cast<int64_t>(row_ptr.size()) - 1;
-        const int64_t nnz = M > 0 ? row_ptr[static_cast<size_t>(M)] : 0;
         std::vector<int64_t> cuts(static_cast<size_t>(parts) + 1, 0);
-        cuts[static_cast<size_t>(parts)] = M;
-        for (int g = 1; g < parts; ++g) {
-            const int64_t target = nnz * g / parts;
-            int64_t r = std::lower_bound(row_ptr.begin(), row_ptr.end(), target) - row_ptr.begin();   // first boundary at or past the target
-            r = std::min<int64_t>(r, M);
-            if (r > 0 && target - row_ptr[static_cast<size_t>(r - 1)] < row_ptr[static_cast<size_t>(r)] - target) --r;   // the closer boundary wins
-            if (align > 1) r = (r + align / 2) / align * align;
-            r = std::max<int64_t>(cuts[static_cast<size_t>(g - 1)], std::min<int64_t>(r, M));
-            cuts[static_cast<size_t>(g)] = r;
-        }
+        sddmm_b200_row_cuts(row_ptr.data(), static_cast<int64_t>(row_ptr.size()) - 1, parts, align, cuts.data());
         return cuts;
     }
 
@@ -69,6 +60,7 @@ public:
         const int64_t M = A.getRows(), N = B.getRows(), K = A.getCols();
         const std::vector<int> &rp = S.getRowPositions();
         plan_shards(rp, M);
+        if (!stage_b(N, K, B.get_pointer())) return;
         std::vector<int> status(shards(), SDDMM_B200_OK);
         parallel([&](int g) {
             const int64_t r0 = cuts_[static_cast<size_t>(g)], r1 = cuts_[static_cast<size_t>(g) + 1];
@@ -78,7 +70,7 @@ public:
             if (r1 == r0) return;   // an empty shard keeps its engine idle
             status[static_cast<size_t>(g)] = sddmm_b200_upload_csr(engines_[static_cast<size_t>(g)], r1 - r0, N, K, local.data(),
                                                                     S.getColPositions().data() + off, S.getValues().data() + off,
-                                                                    A.get_pointer() + r0 * K, B.get_pointer());
+                                                                    A.get_pointer() + r0 * K, nullptr /* the staged B */);
         });
         after_upload(status);
     }
@@ -91,6 +83,7 @@ public:
         for (int r : rows) ++rp[static_cast<size_t>(r) + 1];
         for (int64_t i = 0; i < M; ++i) rp[static_cast<size_t>(i) + 1] += rp[static_cast<size_t>(i)];
         plan_shards(rp, M);
+        if (!stage_b(N, K, B.get_pointer())) return;
         std::vector<int> status(shards(), SDDMM_B200_OK);
         parallel([&](int g) {
             const int64_t r0 = cuts_[static_cast<size_t>(g)], r1 = cuts_[static_cast<size_t>(g) + 1];
@@ -100,7 +93,7 @@ public:
             for (int64_t j = 0; j < n; ++j) local[static_cast<size_t>(j)] = static_cast<int32_t>(rows[static_cast<size_t>(off + j)] - r0);
             status[static_cast<size_t>(g)] = sddmm_b200_upload_coo(engines_[static_cast<size_t>(g)], r1 - r0, N, K, n, local.data(),
                                                                     S.getColPositions().data() + off, S.getValues().data() + off,
-                                                                    A.get_pointer() + r0 * K, B.get_pointer());
+                                                                    A.get_pointer() + r0 * K, nullptr /* the staged B */);
         });
         after_upload(status);
     }
@@ -158,7 +151,12 @@ private:
             const int n = sddmm_b200_device_count();
             for (int d = 0; d < n; ++d) devices_.push_back(d);
         }
+        const int present = sddmm_b200_device_count();
         for (int d : devices_) {
+            if (d < 0 || d >= present) {   // fewer devices than asked for: go on with those that exist
+                std::cerr << "[" << name << "] device " << d << " does not exist (" << present << " visible): left out" << std::endl;
+                continue;
+            }
             sddmm_b200_engine *e = nullptr;
             const int st = sddmm_b200_create(&e, d, mode_, flags_);
             if (st != SDDMM_B200_OK) {
@@ -171,6 +169,17 @@ private:
         }
         if (engines_.empty()) std::cerr << "[" << name << "] no CUDA device" << std::endl;
         return !engines_.empty();
+    }
+
+    // B to every device: once over the host link, then device to device
+    bool stage_b(int64_t N, int64_t K, const T *B) {
+        const int st = sddmm_b200_stage_b(engines_.data(), shards(), N, K, B);
+        if (st == SDDMM_B200_OK) return true;
+        std::cerr << "[" << name << "] distributing B failed (status " << st << ")";
+        for (sddmm_b200_engine *e : engines_)
+            if (*sddmm_b200_last_error(e)) { std::cerr << ": " << sddmm_b200_last_error(e); break; }
+        std::cerr << std::endl;
+        return false;
     }
 
     void plan_shards(const std::vector<int> &rp, int64_t M) {

@@ -36,7 +36,7 @@ enum {
     SDDMM_B200_ERR_CUDA      = 4,  /* any other CUDA runtime failure              */
     SDDMM_B200_ERR_STATE     = 5,  /* call order violated (run before upload ...) */
     SDDMM_B200_ERR_UNSUPPORTED = 6,
-    SDDMM_B200_ERR_COMM      = 7,  /* NCCL could not be loaded or failed          */
+    SDDMM_B200_ERR_COMM      = 7,  /* a copy between devices failed (sddmm_b200_stage_b) */
     SDDMM_B200_ERR_DEVICE_WAIT = 8 /* a bounded device-side wait ran out          */
 };
 
@@ -141,6 +141,18 @@ int sddmm_b200_download(sddmm_b200_engine *e, float *p_val);
 /* device pointer to the nnz output values (valid until the next upload). */
 int sddmm_b200_p_device(sddmm_b200_engine *e, float **p_val_device);
 
+/* ---- consumer of P on the device ---------------------------------------------
+ * Y = P X for the P of the last run(), which stays on the GPU: X is dense N x K2, Y dense M x K2 (host pointers,
+ * row-major fp32; K2 % 4 == 0, 4 <= K2 <= 256).  X = NULL stands for X = B, the copy the engine already holds (K2 must
+ * equal K; in bf16 mode that copy carries the bf16-rounded values): nothing is uploaded.  No counterpart in the reference, whose competitors end by copying P
+ * back to the host (cleanup_csr, src/competitors/gpu/gpu_convert.hpp:58-64); its report names this product (SpMM after
+ * SDDMM, ALS-style updates) as what SDDMM results are used for.  A caller that only needs Y skips the download of
+ * P.val (4 bytes per nonzero) and copies M * K2 floats instead.  Synchronous.  Partial row sums are added to Y with
+ * floating-point reductions whose order is not fixed: Y is reproducible to fp32 rounding, not bit for bit.
+ * sddmm_b200_last_spmm_ms: device time of the consumer kernel (with the clearing of Y) of the last call. */
+int sddmm_b200_spmm(sddmm_b200_engine *e, int64_t K2, const float *X, float *Y);
+int sddmm_b200_last_spmm_ms(sddmm_b200_engine *e, float *ms);
+
 /* ---- introspection ----------------------------------------------------------
  * Device time of the last run() (CUDA events on the engine's stream), standing
  * in for the cudaEvent pair of Benchmark<T>::timing (src/benchmark/benchmark.hpp:160-164). */
@@ -159,7 +171,9 @@ int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info);
  *   "panel_mb"      target size of one panel of B in MiB
  *   "rowseg"        0: never take the row-segment kernel, 1: take it whenever it applies
  *   "b_evict_last"  0/1: gathers of B carry an L2 evict_last hint
- *   "b_fraction"    share of the B lines that hint applies to, (0, 1] */
+ *   "b_fraction"    share of the B lines that hint applies to, (0, 1]
+ *   "group_units"   0: rows with identical column lists run the warp-per-group kernel instead of shared segments
+ *   "offset_tiles"  0: dense tiles only on the 64-grid, 1: always also look for half-full 64x64 windows at arbitrary offsets */
 int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value);
 /* compulsory traffic e*K*(M+ + N+) + 12*nnz + 4*(M+1) with e = bytes per stored
  * element of A/B; extends the read-only model of plots/plot_roofline.py:30 */
@@ -233,6 +247,32 @@ int sddmm_b200_pipeline_update_csr(sddmm_b200_pipeline *p, const float *s_val, c
 int sddmm_b200_pipeline_last_chunks(sddmm_b200_pipeline *p); /* ranges the last call used */
 int sddmm_b200_pipeline_set_min_chunk_bytes(sddmm_b200_pipeline *p, int64_t bytes);
 const char *sddmm_b200_pipeline_last_error(sddmm_b200_pipeline *p);
+
+/* ---- several GPUs of one box from one process -----------------------------------------
+ * SDDMM shards by rows with no exchange in the compute step; what the devices share is B.
+ *
+ * sddmm_b200_row_cuts: parts + 1 row indices (cuts[0] = 0, cuts[parts] = M) that give every part an equal share of the
+ * nonzeros -- the row boundary closest to g * nnz / parts, moved to a multiple of `align` rows when align > 1 (64 keeps
+ * the 64 x 64 tile grid of the tensor-core path in every shard).  The goal of the reference's CSR<T>::_dispatch
+ * (src/matrices/CSR.hpp:196-264: equal nonzeros per worker), by one binary search per cut.  Host only.
+ *
+ * sddmm_b200_stage_b: B crosses the host link ONCE, to engines[0]'s device, and is then copied device to device in
+ * log2(n) rounds (every device that holds B serves one that does not; NVLink where the devices are peers).  After it
+ * every listed engine accepts B = NULL in its next sddmm_b200_upload_csr / _coo with the same N and K and takes its
+ * staged copy.  Engines may sit on the same device.  SDDMM_B200_ERR_COMM when a device-to-device copy fails (the reason
+ * is in the engine's last_error); no engine keeps a staged B then.  No reference counterpart (the reference is
+ * single-GPU: every competitor uploads B itself, e.g. src/competitors/gpu/gpu_basic.hpp:33-60). */
+int sddmm_b200_row_cuts(const int32_t *row_ptr, int64_t M, int parts, int64_t align, int64_t *cuts);
+int sddmm_b200_stage_b(sddmm_b200_engine **engines, int n, int64_t N, int64_t K, const float *B);
+
+/* ---- self-test of the failure path ------------------------------------------------------------
+ * Every wait inside the kernels (on an mbarrier fed by a TMA copy or by the tensor cores) gives up after a bounded
+ * number of probes, records that in a device error word and lets the kernel return; sync() then reports
+ * SDDMM_B200_ERR_DEVICE_WAIT.  This call exercises exactly that path without any fault: a one-thread kernel waits
+ * `probes` (1..65536) times on a barrier nothing completes.  Returns SDDMM_B200_ERR_DEVICE_WAIT when the mechanism
+ * works (the time-out was seen, recorded and read back), SDDMM_B200_OK if the wait unexpectedly succeeded.  The engine
+ * stays usable: the next run() clears the error word.  No reference counterpart (its kernels do not wait on anything). */
+int sddmm_b200_selftest_wait_timeout(sddmm_b200_engine *e, int probes);
 
 /* pinned host memory helpers (so callers without a CUDA toolchain can stage
  * inputs for full-rate copies) */

@@ -37,6 +37,8 @@ class Oracle:
         L.oracle_sddmm_coo.restype = None
         L.oracle_sddmm_csr_rows.argtypes = [C.c_int32, C.c_int32, C.c_int32] + [_vp] * 6
         L.oracle_sddmm_csr_rows.restype = None
+        L.oracle_spmm_csr_rows.argtypes = [C.c_int32, C.c_int32, C.c_int32] + [_vp] * 5
+        L.oracle_spmm_csr_rows.restype = None
         L.oracle_sort_unique_triplets.argtypes = [C.c_int64] + [_vp] * 6
         L.oracle_sort_unique_triplets.restype = C.c_int64
         L.oracle_coo_rows_to_row_ptr.argtypes = [C.c_int32, C.c_int64, _vp, _vp]
@@ -56,6 +58,13 @@ class Oracle:
 
     def sddmm_csr_rows(self, r0, r1, K, row_ptr, col_idx, s_val, A, B, out):
         self.lib.oracle_sddmm_csr_rows(r0, r1, K, _p(row_ptr), _p(col_idx), _p(s_val), _p(A), _p(B), _p(out))
+
+    def spmm_csr(self, M, K2, row_ptr, col_idx, p_val, X):
+        """Y = P X, the consumer of the SDDMM result (plain CSR loop, fp32)."""
+        row_ptr, col_idx, p_val, X = _i32(row_ptr), _i32(col_idx), _f32(p_val), _f32(X)
+        Y = np.empty((M, K2), dtype=np.float32)
+        self.lib.oracle_spmm_csr_rows(0, M, K2, _p(row_ptr), _p(col_idx), _p(p_val), _p(X), _p(Y))
+        return Y
 
     def sddmm_coo(self, K, row_idx, col_idx, s_val, A, B):
         row_idx, col_idx, s_val, A, B = _i32(row_idx), _i32(col_idx), _f32(s_val), _f32(A), _f32(B)

@@ -179,3 +179,20 @@ int oracle_values_equal_reference_rule(int64_t n, const float *lhs, const float 
     }
     return ok;
 }
+
+/* ---- the consumer of P: Y = P X (CSR SpMM) --------------------------------
+ * No counterpart in the reference's sources (its report names SpMM / ALS-style consumers of the SDDMM result as the
+ * motivation, but ships none): a plain row-by-row loop, y_i = sum_j p_ij * x_col(j), fp32, in CSR order.  Used to check
+ * the engine's device-side consumer; rows [row_begin, row_end). */
+void oracle_spmm_csr_rows(int32_t row_begin, int32_t row_end, int32_t K2, const int32_t *row_ptr, const int32_t *col_idx,
+                          const float *p_val, const float *X, float *Y) {
+    for (int32_t i = row_begin; i < row_end; i++) {
+        float *y = Y + (size_t)i * K2;
+        for (int32_t k = 0; k < K2; k++) y[k] = 0.0f;
+        for (int32_t j = row_ptr[i]; j < row_ptr[i + 1]; j++) {
+            const float *x = X + (size_t)col_idx[j] * K2;
+            const float p = p_val[j];
+            for (int32_t k = 0; k < K2; k++) y[k] += p * x[k];
+        }
+    }
+}

@@ -86,9 +86,53 @@ def test_synthetic_configs_small(engines, oracle, mode, cfg, scale, K):
 
 
 def test_config2_unaligned_blocks(engines, oracle):
+    # 64x64 blocks at arbitrary offsets: the tile detector anchors its tiles on the blocks, not on the 64-grid
     d = Dataset(2, 32, 0.1, variant=1)
-    for mode in ("fp32", "fp32_tc", "tf32"):
+    for mode in ("fp32", "fp32_tc", "tf32", "bf16"):
         check(engines[mode], mode, oracle, d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, what=f"{mode} unaligned")
+        plan = engines[mode].plan()
+        if mode != "fp32":
+            assert plan["dense_nnz"] >= 0.6 * d.nnz, f"{mode}: only {plan['dense_nnz']} of {d.nnz} nonzeros on the tensor path"
+            assert plan["dense_nnz"] + plan["rowseg_nnz"] + plan["rowtile_nnz"] == d.nnz
+        check(engines[mode], mode, oracle, d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, coo=True, what=f"{mode} unaligned coo")
+    # the grid-only detection on the same input catches far less, and gives the same values
+    with Engine(0, "fp32_tc") as e:
+        e.set_knob("offset_tiles", 0)
+        q = check(e, "fp32_tc", oracle, d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B, what="grid tiles only")
+        assert e.plan()["dense_nnz"] < engines["fp32_tc"].plan()["dense_nnz"]
+    d.close()
+
+
+def test_overlapping_dense_blocks_have_one_owner_per_nonzero(engines, oracle):
+    # two dense 64x64 blocks that overlap in rows and columns, a third stacked right below the first, one at the matrix
+    # corner (its window reaches past the last row and column): every nonzero is computed exactly once
+    rng = np.random.default_rng(21)
+    M = N = 400
+    dense = np.zeros((M, N), bool)
+    for r0, c0 in ((10, 20), (40, 50), (74, 20), (350, 350), (200, 100), (200, 164)):
+        dense[r0:r0 + 64, c0:c0 + 64] |= rng.random((min(64, M - r0), min(64, N - c0))) < 0.8
+    dense |= rng.random((M, N)) < 0.01      # thin background
+    rows, cols = np.nonzero(dense)
+    rp = np.concatenate([[0], np.cumsum(np.bincount(rows, minlength=M))]).astype(np.int32)
+    ci = cols.astype(np.int32)
+    sv = rng.uniform(-1, 1, ci.size).astype(np.float32)
+    A = rng.uniform(-1, 1, (M, 64)).astype(np.float32)
+    B = rng.uniform(-1, 1, (N, 64)).astype(np.float32)
+    for mode in ("fp32_tc", "tf32", "bf16"):
+        e = Engine(0, mode)
+        e.set_knob("offset_tiles", 1)
+        p = check(e, mode, oracle, M, N, 64, rp, ci, sv, A, B, what=f"overlapping blocks {mode}")
+        plan = e.plan()
+        assert plan["dense_tiles"] >= 4 and plan["dense_nnz"] + plan["rowseg_nnz"] + plan["rowtile_nnz"] == ci.size
+        # the same input with the residual on the row-tile kernel (flag: no row segments)
+        e2 = Engine(0, mode, flags=4)
+        e2.set_knob("offset_tiles", 1)
+        q = check(e2, mode, oracle, M, N, 64, rp, ci, sv, A, B, what=f"overlapping blocks {mode}, row-tile residual")
+        assert e2.plan()["rowseg_units"] == 0 and [n for n, _ in e2.kernel_times()][-1] == "sddmm_rowtile_kernel"
+        e2.close()
+        e.run()
+        assert np.array_equal(e.download(), p)   # same plan, same owners: bit-identical on a second run
+        e.close()
 
 
 @pytest.mark.parametrize("K", [1, 2, 3, 4, 8, 12, 20, 31, 32, 33, 36, 64, 96, 100, 128, 160, 256, 260])
@@ -445,11 +489,22 @@ def test_row_groups_share_the_gather(engines, oracle, G, K, extra_rows, break_ev
         p = check(engines[mode], mode, oracle, M, N, K, rp, ci, sv, A, B, what=f"row groups G={G} K={K} {mode}")
         plan = engines[mode].plan()
         assert plan["rowgroup_rows"] == G and plan["n_kernels"] == 1 and plan["rowtile_nnz"] == 0
-        assert [n for n, _ in engines[mode].kernel_times()] == ["sddmm_rowgroup_kernel"]
+        # the group's column list cut into shared segments of 8 columns: one unit serves all G rows
+        assert [n for n, _ in engines[mode].kernel_times()] == ["sddmm_rowseg_group_kernel"]
+        lens = np.diff(rp).astype(np.int64)
+        assert plan["rowseg_units"] <= int(((lens + 7) // 8).sum())
         if not break_every:
             assert plan["rowgroup_nnz"] == blocked_nnz
+            assert plan["rowseg_units"] == int(((lens + 7) // 8).sum()) - (G - 1) * 150 * ((int(lens[lead_rows]) + 7) // 8)
         else:
             assert 0 < plan["rowgroup_nnz"] < blocked_nnz
+    # the same groups through the warp-per-group kernel (knob "group_units" = 0)
+    with Engine(0, "fp32") as e0:
+        e0.set_knob("group_units", 0)
+        q0 = e0.sddmm_csr(M, N, K, rp, ci, sv, A, B)
+        assert [n for n, _ in e0.kernel_times()] == ["sddmm_rowgroup_kernel"] and e0.plan()["rowgroup_rows"] == G
+        bound0 = oracle_lib.abs_dot_bound(oracle.coo_rows(M, rp), ci, sv, A, B)
+        oracle_lib.assert_values_close(q0, p, bound0, 2e-5, "row-group kernel vs shared segments")
     # the same input with the path switched off goes through the row-tile kernel and agrees
     e = Engine(0, "fp32", flags=2)
     try:
@@ -476,7 +531,7 @@ def test_kernel_timing_is_opt_in():
     try:
         e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
         names = [n for n, _ in e.kernel_times()]
-        assert names == ["sddmm_dense_tile_kernel", "sddmm_rowtile_kernel"]
+        assert names == ["sddmm_dense_tile_kernel", "sddmm_rowseg_kernel"]   # the tiles, and what they left as row segments
         assert all(ms == -1.0 for _, ms in e.kernel_times())
         e.set_kernel_timing(True)
         e.run(); e.sync()
@@ -575,3 +630,76 @@ def test_pipeline_edges(oracle):
         oracle_lib.assert_values_close(p_up, 2 * p_ref, 2 * bound, 1e-5, "pipeline ragged update")
     with pytest.raises(SddmmError):
         Pipeline(0, "fp32", chunks=0)
+
+
+# ---- the consumer of P on the device: Y = P X ------------------------------------------------------------------
+@pytest.mark.parametrize("cfg,scale,K,mode,K2", [(5, 0.01, 32, "fp32", 32), (4, 0.01, 32, "fp32", 64), (2, 0.1, 32, "fp32_tc", 32),
+                                                  (3, 0.01, 64, "fp32", 16), (5, 0.005, 64, "bf16", 36), (1, 1.0, 32, "fp32", 256)])
+def test_consumer_spmm_on_the_device_resident_result(engines, oracle, cfg, scale, K, mode, K2):
+    import scipy.sparse as sp
+
+    d = Dataset(cfg, K, scale)
+    e = engines[mode]
+    p = e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    rng = np.random.default_rng(K2)
+    X = rng.uniform(-1, 1, (d.N, K2)).astype(np.float32)
+    Y = e.spmm(X)
+    assert Y.shape == (d.M, K2) and np.isfinite(Y).all()
+    # (a) the consumer alone: against a float64 product with the P the engine itself computed
+    P64 = sp.csr_matrix((p.astype(np.float64), d.col_idx, d.row_ptr), shape=(d.M, d.N))
+    want = P64 @ X.astype(np.float64)
+    bound = abs(P64) @ np.abs(X.astype(np.float64))
+    assert (np.abs(Y - want) <= 3e-5 * bound + 1e-30).all(), f"consumer off by up to {np.max(np.abs(Y - want) / (bound + 1e-30)):.2e} of the bound"
+    # (b) the chain SDDMM -> SpMM against the CPU oracle's chain
+    p_ref = oracle.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    y_ref = oracle.spmm_csr(d.M, K2, d.row_ptr, d.col_idx, p_ref, X)
+    rows = oracle.coo_rows(d.M, d.row_ptr)
+    pb = oracle_lib.abs_dot_bound(rows, d.col_idx, d.s_val, d.A, d.B)            # scale of each P entry
+    chain_bound = sp.csr_matrix((pb, d.col_idx, d.row_ptr), shape=(d.M, d.N)) @ np.abs(X.astype(np.float64))
+    tol = 4 * TOL[mode]
+    assert (np.abs(Y - y_ref) <= tol * chain_bound + 1e-30).all(), "SDDMM -> SpMM chain differs from the oracle's"
+    # a second call (other K2) reuses the unit list; the result of the first call is reproducible to rounding
+    Y2 = e.spmm(X[:, :8].copy())
+    assert (np.abs(Y2 - want[:, :8]) <= 3e-5 * bound[:, :8] + 1e-30).all()
+    if d.M == d.N or True:   # X = None: the engine's own copy of B is the right-hand side (nothing is uploaded)
+        Bq = d.B.astype(np.float32)
+        if mode == "bf16":   # the engine holds the bf16-rounded B
+            Bq = (Bq.view(np.uint32) + 0x7FFF + ((Bq.view(np.uint32) >> 16) & 1) & 0xFFFF0000).astype(np.uint32).view(np.float32)
+        YB = e.spmm(None)
+        wantB = P64 @ Bq.astype(np.float64)
+        boundB = abs(P64) @ np.abs(Bq.astype(np.float64))
+        assert YB.shape == (d.M, d.K) and (np.abs(YB - wantB) <= 3e-5 * boundB + 1e-30).all()
+    assert e.last_spmm_ms() > 0
+    d.close()
+
+
+def test_consumer_rejects_what_it_cannot_take(engines):
+    e = engines["fp32"]
+    A = np.ones((3, 4), np.float32)
+    e.sddmm_csr(3, 3, 4, [0, 1, 2, 3], [0, 1, 2], [1, 1, 1], A, A)
+    assert e.spmm(np.ones((3, 4), np.float32)).tolist() == [[4.0] * 4] * 3
+    for bad in (3, 6, 260):
+        with pytest.raises(SddmmError) as ei:
+            e.spmm(np.ones((3, bad), np.float32))
+        assert ei.value.code == 6
+    fresh = Engine(0, "fp32")
+    with pytest.raises(SddmmError) as ei:
+        fresh.spmm(np.ones((3, 4), np.float32), rows=3)
+    assert ei.value.code == 5
+    fresh.close()
+
+
+def test_bounded_wait_runs_out_and_is_reported(oracle):
+    # the failure path of every device-side wait, exercised without a fault: a one-thread kernel waits a bounded number of
+    # times on a barrier nothing completes, records the time-out and returns; sync reports it; the next run is clean again
+    d = Dataset(1, 32, 1.0)
+    with Engine(0, "fp32") as e:
+        p = e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        assert e.lib.sddmm_b200_selftest_wait_timeout(e.h, 64) == 8            # SDDMM_B200_ERR_DEVICE_WAIT
+        assert b"wait" in e.lib.sddmm_b200_last_error(e.h)
+        assert e.lib.sddmm_b200_selftest_wait_timeout(e.h, 0) == 1             # bad argument
+        e.run()                                                                  # clears the error word
+        assert np.array_equal(e.download(), p)
+    fresh = Engine(0, "fp32")
+    assert fresh.lib.sddmm_b200_selftest_wait_timeout(fresh.h, 64) == 5         # before any upload: call order
+    fresh.close()
