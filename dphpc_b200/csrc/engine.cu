@@ -127,6 +127,9 @@ struct sddmm_b200_engine {
 
     // row-segment path (short and power-law rows; column panels when B is much larger than L2)
     int2 *d_units = nullptr;
+    int32_t *d_unit_cols = nullptr;    // column panels: per-unit copies of column indices and S values (8 slots per unit)
+    float *d_unit_sval = nullptr;
+    bool seg_copies = false;           // ... in use by the current plan
     int32_t *d_unit_off = nullptr;     // per (panel, row): units before it (scan of the counts)
     int32_t *d_scan_tiles = nullptr;
     int64_t unit_cap = 0;
@@ -315,6 +318,8 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     e->unit_cap = static_cast<int64_t>(nnz / 8 + runs + 8);
     const size_t scan_n = M * static_cast<size_t>(e->panels);
     const size_t o_units = c.take(static_cast<size_t>(e->unit_cap) * sizeof(int4));   // (row groups use 16-byte headers)
+    const size_t o_ucols = e->panels > 1 ? c.take(static_cast<size_t>(e->unit_cap) * 32) : 0;
+    const size_t o_usval = e->panels > 1 ? c.take(static_cast<size_t>(e->unit_cap) * 32) : 0;
     const size_t o_uoff = c.take((scan_n + 1) * 4);
     const size_t o_stile = c.take((scan_n / kScanTile + 2) * 4);
     // dense-tile path: only carved when the mode, K and the size of the 64x64 tile grid allow it
@@ -359,6 +364,8 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     e->d_Ax = split ? reinterpret_cast<float *>(b + o_ax) : nullptr;
     e->d_Bx = split ? reinterpret_cast<float *>(b + o_bx) : nullptr;
     e->d_units = reinterpret_cast<int2 *>(b + o_units);
+    e->d_unit_cols = e->panels > 1 ? reinterpret_cast<int32_t *>(b + o_ucols) : nullptr;
+    e->d_unit_sval = e->panels > 1 ? reinterpret_cast<float *>(b + o_usval) : nullptr;
     e->d_unit_off = reinterpret_cast<int32_t *>(b + o_uoff);
     e->d_scan_tiles = reinterpret_cast<int32_t *>(b + o_stile);
     e->d_rp = reinterpret_cast<int32_t *>(b + o_rp);
@@ -393,7 +400,12 @@ int choose_item_nnz(const sddmm_b200_engine *e) {
 
 int convert_storage(sddmm_b200_engine *e) {
     const int cap = e->sm_count * 8;
-    if (e->d_Ax) {  // hi/lo-concatenated operands of the fp32-grade tensor-core mode
+    if (e->use_seg && e->seg_copies && e->n_units > 0) {   // the units' copies of S.val follow every change of S.val
+        k_unit_values<<<grid_for(8 * static_cast<int64_t>(e->n_units), kBlock, cap * 4), kBlock, 0, e->stream>>>(e->d_units, e->n_units, e->d_sval,
+                                                                                                           e->d_unit_sval);
+        CU_TRY(e, cudaGetLastError());
+    }
+    if (e->d_Ax && e->n_dense > 0) {  // hi/lo-concatenated operands of the fp32-grade tensor-core mode (only when tiles were found)
         k_split_concat_tf32<<<grid_for(e->M * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_A32, e->d_Ax, e->M, static_cast<int32_t>(e->K), 1);
         k_split_concat_tf32<<<grid_for(e->N * e->K, kBlock, cap), kBlock, 0, e->stream>>>(e->d_B32, e->d_Bx, e->N, static_cast<int32_t>(e->K), 0);
         CU_TRY(e, cudaGetLastError());
@@ -736,6 +748,7 @@ int build_residual_units(sddmm_b200_engine *e) {
 int build_rowseg_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     const int seg_env = e->knob_rowseg < 0 ? -1 : static_cast<int>(e->knob_rowseg);   // 0 never, 1 whenever possible
     e->use_seg = false;
+    e->seg_copies = false;
     e->n_units = 0;
     if ((e->flags & SDDMM_B200_FLAG_NO_ROW_SEGMENTS) || seg_env == 0 || e->M >= kUnitRowLimit) return SDDMM_B200_OK;
     const int32_t panels = base_pc.unsorted_cols ? 1 : e->panels;   // a panel run is a contiguous piece of a row only when its columns are sorted
@@ -748,7 +761,9 @@ int build_rowseg_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     k_scan_tile_sums<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, n, e->d_scan_tiles);
     k_scan_sums<<<1, kScanBlock, 0, s>>>(e->d_scan_tiles, n_tiles, &e->d_pc->units);
     k_scan_apply<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, n, e->d_scan_tiles);
-    k_unit_fill<<<grid_for(n * 32, kBlock, cap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, panels, e->panel_cols, e->d_unit_off, e->d_units);
+    e->seg_copies = panels > 1 && e->d_unit_cols != nullptr;
+    k_unit_fill<<<grid_for(n * 32, kBlock, cap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, panels, e->panel_cols, e->d_unit_off, e->d_units,
+                                                                  e->seg_copies ? e->d_unit_cols : nullptr);
     CU_TRY(e, cudaGetLastError());
     PlanCounters pc;
     if (int rc = read_counters(e, &pc)) return rc;
@@ -971,8 +986,10 @@ int launch_rowseg(sddmm_b200_engine *e, cudaStream_t stream) {
     g.units = e->d_units; g.col_idx = e->d_col; g.s_val = e->d_sval; g.p_val = e->d_pval;
     g.n_units = e->n_units; g.K = static_cast<int32_t>(e->K);
     // L2 is asked to keep the gathered B rows when they can stay: one column panel at a time
-    g.b_evict_last = e->knob_b_evict_last >= 0 ? static_cast<int32_t>(e->knob_b_evict_last) : (p.rowseg_panels > 1 ? 1 : 0);
+    g.b_evict_last = p.rowseg_panels > 1 ? 1 : 0;
     g.b_fraction = e->knob_b_fraction > 0 ? static_cast<float>(std::min(1.0, e->knob_b_fraction)) : 1.0f;
+    g.unit_cols = e->d_unit_cols; g.unit_sval = e->d_unit_sval;
+    if (!e->seg_copies) g.b_evict_last = 0;   // (the hinted instantiation reads the per-unit copies)
     if (int st = begin_kernel(e, stream)) return st;
     if (e->mode == SDDMM_B200_BF16) {
         g.A = e->d_A16; g.B = e->d_B16;
@@ -1214,6 +1231,11 @@ int sddmm_b200_update_values(sddmm_b200_engine *e, const float *s_val) {
     if (!s_val && e->nnz) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
     DeviceGuard g(e->device);
     if (e->nnz) CU_TRY(e, cudaMemcpyAsync(e->d_sval, s_val, static_cast<size_t>(e->nnz) * 4, cudaMemcpyHostToDevice, e->stream));
+    if (e->use_seg && e->seg_copies && e->n_units > 0) {
+        k_unit_values<<<grid_for(8 * static_cast<int64_t>(e->n_units), kBlock, e->sm_count * 32), kBlock, 0, e->stream>>>(e->d_units, e->n_units,
+                                                                                                                  e->d_sval, e->d_unit_sval);
+        CU_TRY(e, cudaGetLastError());
+    }
     CU_TRY(e, cudaStreamSynchronize(e->stream));
     return SDDMM_B200_OK;
 }
@@ -1471,7 +1493,7 @@ int spmm_prepare(sddmm_b200_engine *e, int64_t K2) {
         k_scan_tile_sums<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
         k_scan_sums<<<1, kScanBlock, 0, s>>>(e->d_scan_tiles, n_tiles, &e->d_pc->units);
         k_scan_apply<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
-        k_unit_fill<<<grid_for(e->M * 32, kBlock, capb), kBlock, 0, s>>>(e->d_rp, e->d_col, Mi, 1, 0, e->d_unit_off, e->d_spmm_units);
+        k_unit_fill<<<grid_for(e->M * 32, kBlock, capb), kBlock, 0, s>>>(e->d_rp, e->d_col, Mi, 1, 0, e->d_unit_off, e->d_spmm_units, nullptr);
         CU_TRY(e, cudaGetLastError());
         PlanCounters pc;
         if (int rc = read_counters(e, &pc)) return rc;

@@ -43,6 +43,11 @@ struct RowSegArgs {
     int32_t K;
     int32_t b_evict_last;     // B gathers ask L2 to keep their lines (column panels)
     float b_fraction;         // share of the B lines the hint applies to (1 = all)
+    // column panels: copies of the units' column indices and S values, 8 slots per unit in list order (slots past the
+    // segment's end repeat its last nonzero).  A panel run is a short piece of its row, so reading col_idx / S.val in
+    // place would touch one or two 32-byte sectors of a 128-byte line per unit; the copies are read front to back.
+    const int32_t *unit_cols;
+    const float *unit_sval;
 };
 
 constexpr int kRowSegWarps = 8;
@@ -76,7 +81,8 @@ __device__ __forceinline__ uint4 ld_chunk_hint(const uint4 *p, uint64_t pol) {
     return v;
 }
 
-// HINT: the B gathers carry the L2 evict_last policy (one instantiation with, one without: no branch per load).
+// HINT: column panels -- the B gathers carry the L2 evict_last policy and column indices / S values come from the
+// per-unit copies (one instantiation with, one without: no branch per load).
 template <int CPL, bool EXACT, typename ET, bool HINT>
 __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_MINB1 : SDDMM_ROWSEG_MINBN) sddmm_rowseg_kernel(const RowSegArgs args) {
     using chunk_t = typename ChunkOf<ET>::type;
@@ -113,16 +119,21 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
 
     // Every load below is unconditional and in range: a group past the end of the list repeats the last unit, a lane
     // past the end of its segment repeats the segment's last nonzero; only the final store is predicated.
-    auto load_unit = [&](int64_t qq) -> int2 {
-        const int64_t u = 4 * qq + grp;
-        return __ldcs(args.units + (u < last_unit ? u : last_unit));
-    };
+    auto unit_index = [&](int64_t qq) -> int64_t { const int64_t u = 4 * qq + grp; return u < last_unit ? u : last_unit; };
+    auto load_unit = [&](int64_t qq) -> int2 { return __ldcs(args.units + unit_index(qq)); };
     auto own_slot = [&](const int2 &u) -> int { return u.x + min(gl, u.y & 7); };
+    // column index / S value of this lane's nonzero of the unit of quad qq (u: that unit's header, if already loaded)
+    auto own_col = [&](int64_t qq, const int2 &u) -> int {
+        return HINT ? __ldcs(args.unit_cols + 8 * unit_index(qq) + gl) : __ldcs(args.col_idx + own_slot(u));
+    };
+    auto own_val = [&](int64_t qq, const int2 &u) -> float {
+        return HINT ? __ldcs(args.unit_sval + 8 * unit_index(qq) + gl) : __ldcs(args.s_val + own_slot(u));
+    };
 
     int2 u_cur = load_unit(q);
     int2 u_nxt = load_unit(q + n_warps);
-    int c_own = __ldcs(args.col_idx + own_slot(u_cur));
-    float s_own = __ldcs(args.s_val + own_slot(u_cur));
+    int c_own = own_col(q, u_cur);
+    float s_own = own_val(q, u_cur);
 
     while (true) {
         const int row = u_cur.y >> 3;
@@ -161,8 +172,8 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
             }
         const int64_t q_next = q + n_warps;
         const int2 u_nxt2 = load_unit(q_next + n_warps);
-        c_own = __ldcs(args.col_idx + own_slot(u_nxt));
-        s_own = __ldcs(args.s_val + own_slot(u_nxt));
+        c_own = own_col(q_next, u_nxt);
+        s_own = own_val(q_next, u_nxt);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
@@ -376,7 +387,7 @@ __global__ void k_unit_count(const int32_t *__restrict__ rp, const int32_t *__re
 
 // one warp per (panel, row): write its units at the scanned offset
 __global__ void k_unit_fill(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t panels,
-                            int32_t panel_cols, const int32_t *__restrict__ offsets, int2 *__restrict__ units) {
+                            int32_t panel_cols, const int32_t *__restrict__ offsets, int2 *__restrict__ units, int32_t *__restrict__ ucols) {
     const int lane = threadIdx.x & 31;
     const int64_t n = static_cast<int64_t>(panels) * M;
     const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
@@ -391,6 +402,17 @@ __global__ void k_unit_fill(const int32_t *__restrict__ rp, const int32_t *__res
             const int32_t cnt = min(8, e - first);
             units[off + u] = make_int2(first, i * 8 + (cnt - 1));
         }
+        if (ucols)   // per-unit copies of the column indices (slots past the end of the run repeat its last column)
+            for (int32_t t = lane; t < 8 * n_units; t += 32) ucols[8 * static_cast<int64_t>(off) + t] = col[min(s + t, e - 1)];
+    }
+}
+
+// per-unit copies of the S values (one thread per slot): refreshed whenever S.val changes
+__global__ void k_unit_values(const int2 *__restrict__ units, int32_t n_units, const float *__restrict__ s_val, float *__restrict__ usval) {
+    for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < 8 * static_cast<int64_t>(n_units);
+         t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int2 u = units[t >> 3];
+        usval[t] = s_val[u.x + min(static_cast<int>(t & 7), u.y & 7)];
     }
 }
 
