@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "../../include/sddmm_b200.h"
+#include "host_staging.cuh"
 #include "kernel_dense_tile.cuh"
 #include "kernel_rowgroup.cuh"
 #include "kernel_rowseg.cuh"
@@ -143,6 +144,8 @@ struct sddmm_b200_engine {
     double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_evict_last = -1, knob_b_fraction = -1, knob_group_units = -1,
            knob_offset_tiles = -1;
     bool rg_units = false;             // row groups run as shared segments (row-segment group kernel) instead of the warp-per-group kernel
+
+    HostStager stager, stager2;   // pageable host memory goes through pinned ring buffers filled by a pool of host threads (one per stream)
 
     // B received from another engine (sddmm_b200_stage_b): the next upload may pass B = NULL
     float *b_stage = nullptr;
@@ -919,15 +922,19 @@ int enqueue_copies(sddmm_b200_engine *e, const int32_t *row_ptr, const int32_t *
                    const float *A, const float *B, cudaMemcpyKind kind) {
     cudaStream_t s = e->stream, s2 = e->side_stream;
     const int64_t M = e->M, N = e->N, K = e->K, nnz = e->nnz;
-    if (row_ptr) CU_TRY(e, cudaMemcpyAsync(e->d_rp, row_ptr, static_cast<size_t>(M + 1) * 4, kind, s));
-    if (coo_rows && nnz) CU_TRY(e, cudaMemcpyAsync(e->d_coo_rows, coo_rows, static_cast<size_t>(nnz) * 4, kind, s));
-    if (nnz) CU_TRY(e, cudaMemcpyAsync(e->d_col, col_idx, static_cast<size_t>(nnz) * 4, kind, s));
+    // (host sources: pageable memory is staged through pinned buffers by a pool of host threads, see host_staging.cuh)
+    auto copy_in = [&](void *dst, const void *src, size_t bytes, cudaStream_t st, HostStager &stg) -> cudaError_t {
+        return kind == cudaMemcpyHostToDevice ? stg.upload(dst, src, bytes, st) : cudaMemcpyAsync(dst, src, bytes, kind, st);
+    };
+    if (row_ptr) CU_TRY(e, copy_in(e->d_rp, row_ptr, static_cast<size_t>(M + 1) * 4, s, e->stager));
+    if (coo_rows && nnz) CU_TRY(e, copy_in(e->d_coo_rows, coo_rows, static_cast<size_t>(nnz) * 4, s, e->stager));
+    if (nnz) CU_TRY(e, copy_in(e->d_col, col_idx, static_cast<size_t>(nnz) * 4, s, e->stager));
     CU_TRY(e, cudaEventRecord(e->ev_join, s));
     CU_TRY(e, cudaStreamWaitEvent(s2, e->ev_join, 0));   // keeps the link order: pattern first
-    if (nnz) CU_TRY(e, cudaMemcpyAsync(e->d_sval, s_val, static_cast<size_t>(nnz) * 4, kind, s2));
-    CU_TRY(e, cudaMemcpyAsync(e->d_A32, A, static_cast<size_t>(M * K) * 4, kind, s2));
+    if (nnz) CU_TRY(e, copy_in(e->d_sval, s_val, static_cast<size_t>(nnz) * 4, s2, e->stager2));
+    CU_TRY(e, copy_in(e->d_A32, A, static_cast<size_t>(M * K) * 4, s2, e->stager2));
     if (e->B_on_device) CU_TRY(e, cudaMemcpyAsync(e->d_B32, e->B_on_device, static_cast<size_t>(N * K) * 4, cudaMemcpyDeviceToDevice, s2));
-    else CU_TRY(e, cudaMemcpyAsync(e->d_B32, B, static_cast<size_t>(N * K) * 4, kind, s2));
+    else CU_TRY(e, copy_in(e->d_B32, B, static_cast<size_t>(N * K) * 4, s2, e->stager2));
     CU_TRY(e, cudaEventRecord(e->ev_h2d, s2));
     if (e->on_copies_enqueued) e->on_copies_enqueued(e->on_copies_user);
     return SDDMM_B200_OK;
@@ -1151,6 +1158,8 @@ int sddmm_b200_destroy(sddmm_b200_engine *e) {
         if (e->stream) cudaStreamSynchronize(e->stream);
         if (e->arena.base) cudaFree(e->arena.base);
         if (e->spmm_arena.base) cudaFree(e->spmm_arena.base);
+        e->stager.release();
+        e->stager2.release();
         if (e->b_stage) cudaFree(e->b_stage);
         if (e->ev_stage) cudaEventDestroy(e->ev_stage);
         if (e->ev_spmm0) cudaEventDestroy(e->ev_spmm0);
@@ -1217,8 +1226,8 @@ int sddmm_b200_update_dense(sddmm_b200_engine *e, const float *A, const float *B
     if (!e) return SDDMM_B200_ERR_ARG;
     if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "update_dense before upload");
     DeviceGuard g(e->device);
-    if (A) CU_TRY(e, cudaMemcpyAsync(e->d_A32, A, static_cast<size_t>(e->M * e->K) * 4, cudaMemcpyHostToDevice, e->stream));
-    if (B) CU_TRY(e, cudaMemcpyAsync(e->d_B32, B, static_cast<size_t>(e->N * e->K) * 4, cudaMemcpyHostToDevice, e->stream));
+    if (A) CU_TRY(e, e->stager.upload(e->d_A32, A, static_cast<size_t>(e->M * e->K) * 4, e->stream));
+    if (B) CU_TRY(e, e->stager.upload(e->d_B32, B, static_cast<size_t>(e->N * e->K) * 4, e->stream));
     int st = convert_storage(e);
     if (st) return st;
     CU_TRY(e, cudaStreamSynchronize(e->stream));
@@ -1230,7 +1239,7 @@ int sddmm_b200_update_values(sddmm_b200_engine *e, const float *s_val) {
     if (!e->uploaded) return fail(e, SDDMM_B200_ERR_STATE, "update_values before upload");
     if (!s_val && e->nnz) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
     DeviceGuard g(e->device);
-    if (e->nnz) CU_TRY(e, cudaMemcpyAsync(e->d_sval, s_val, static_cast<size_t>(e->nnz) * 4, cudaMemcpyHostToDevice, e->stream));
+    if (e->nnz) CU_TRY(e, e->stager.upload(e->d_sval, s_val, static_cast<size_t>(e->nnz) * 4, e->stream));
     if (e->use_seg && e->seg_copies && e->n_units > 0) {
         k_unit_values<<<grid_for(8 * static_cast<int64_t>(e->n_units), kBlock, e->sm_count * 32), kBlock, 0, e->stream>>>(e->d_units, e->n_units,
                                                                                                                   e->d_sval, e->d_unit_sval);
@@ -1270,7 +1279,7 @@ int sddmm_b200_download(sddmm_b200_engine *e, float *p_val) {
     if (!e->uploaded || !e->ran) return fail(e, SDDMM_B200_ERR_STATE, "download before run");
     if (!p_val && e->nnz) return fail(e, SDDMM_B200_ERR_ARG, "null pointer argument");
     DeviceGuard g(e->device);
-    if (e->nnz) CU_TRY(e, cudaMemcpyAsync(p_val, e->d_pval, static_cast<size_t>(e->nnz) * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (e->nnz) CU_TRY(e, e->stager.download(p_val, e->d_pval, static_cast<size_t>(e->nnz) * 4, e->stream));
     return sddmm_b200_sync(e);
 }
 
@@ -1368,7 +1377,9 @@ int sddmm_b200_stage_b(sddmm_b200_engine **engines, int n, int64_t N, int64_t K,
         if (!g.ok) return fail(e, SDDMM_B200_ERR_COMM, "device %d cannot be selected", e->device);
         e->b_stage_n = e->b_stage_k = 0;
         if (e->b_stage_cap < bytes) {
-            if (e->b_stage) cudaFree(e->b_stage);
+            e->stager.release();
+        e->stager2.release();
+        if (e->b_stage) cudaFree(e->b_stage);
             e->b_stage = nullptr;
             e->b_stage_cap = 0;
             void *p = nullptr;
@@ -1386,7 +1397,7 @@ int sddmm_b200_stage_b(sddmm_b200_engine **engines, int n, int64_t N, int64_t K,
     {
         sddmm_b200_engine *e0 = engines[0];
         DeviceGuard g(e0->device);
-        if (cudaMemcpyAsync(e0->b_stage, B, bytes, cudaMemcpyHostToDevice, e0->stream) != cudaSuccess ||
+        if (e0->stager.upload(e0->b_stage, B, bytes, e0->stream) != cudaSuccess ||
             cudaEventRecord(e0->ev_stage, e0->stream) != cudaSuccess)
             rc = fail(e0, SDDMM_B200_ERR_COMM, "upload of B to device %d: %s", e0->device, cudaGetErrorString(cudaGetLastError()));
     }
