@@ -141,7 +141,7 @@ struct sddmm_b200_engine {
     bool seg_residual = false;         // the row-segment kernel computes what the dense tiles left (units over the uncovered runs)
     int l2_bytes = 0;
     // tuning knobs (sddmm_b200_set_knob; defaults from the environment at create): < 0 = decide automatically
-    double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_evict_last = -1, knob_b_fraction = -1, knob_group_units = -1,
+    double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_fraction = -1, knob_group_units = -1,
            knob_offset_tiles = -1;
     bool rg_units = false;             // row groups run as shared segments (row-segment group kernel) instead of the warp-per-group kernel
 
@@ -1122,7 +1122,6 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     e->knob_panels = env_double("SDDMM_B200_PANELS", -1);
     e->knob_panel_mb = env_double("SDDMM_B200_PANEL_MB", -1);
     e->knob_rowseg = env_double("SDDMM_B200_ROWSEG", -1);
-    e->knob_b_evict_last = env_double("SDDMM_B200_B_EVICT_LAST", -1);
     e->knob_b_fraction = env_double("SDDMM_B200_B_FRACTION", -1);
     e->knob_group_units = env_double("SDDMM_B200_GROUP_UNITS", -1);
     e->knob_offset_tiles = env_double("SDDMM_B200_OFFSET_TILES", -1);
@@ -1445,7 +1444,7 @@ int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value) {
     if (!e || !name) return SDDMM_B200_ERR_ARG;
     struct { const char *name; double *slot; } knobs[] = {
         {"panels", &e->knob_panels}, {"panel_mb", &e->knob_panel_mb}, {"rowseg", &e->knob_rowseg},
-        {"b_evict_last", &e->knob_b_evict_last}, {"b_fraction", &e->knob_b_fraction}, {"group_units", &e->knob_group_units},
+        {"b_fraction", &e->knob_b_fraction}, {"group_units", &e->knob_group_units},
         {"offset_tiles", &e->knob_offset_tiles},
     };
     for (auto &k : knobs)

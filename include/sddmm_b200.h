@@ -165,13 +165,11 @@ int sddmm_b200_set_kernel_timing(sddmm_b200_engine *e, int enabled);
 int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info);
 /* Tuning knobs of the planner (the thread-grid command-line options of the reference's driver, src/main.cpp:326-348, and
  * the density threshold of GPUDynamic, src/competitors/gpu/gpu_dynamic.hpp:72-73, play this role there).  A negative
- * value hands the decision back to the planner; a knob takes effect at the next upload (the two cache knobs at the
- * next run).  Defaults come from the environment variables SDDMM_B200_<NAME IN CAPITALS> at create.
+ * value hands the decision back to the planner; a knob takes effect at the next upload ("b_fraction" at the next run).  Defaults come from the environment variables SDDMM_B200_<NAME IN CAPITALS> at create.
  *   "panels"        column panels of the row-segment path (1..64)
  *   "panel_mb"      target size of one panel of B in MiB
  *   "rowseg"        0: never take the row-segment kernel, 1: take it whenever it applies
- *   "b_evict_last"  0/1: gathers of B carry an L2 evict_last hint
- *   "b_fraction"    share of the B lines that hint applies to, (0, 1]
+ *   "b_fraction"    with column panels the gathers of B carry an L2 evict_last hint: share of the lines it applies to, (0, 1]
  *   "group_units"   0: rows with identical column lists run the warp-per-group kernel instead of shared segments
  *   "offset_tiles"  0: dense tiles only on the 64-grid, 1: always also look for half-full 64x64 windows at arbitrary offsets */
 int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value);
