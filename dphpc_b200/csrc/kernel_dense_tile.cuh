@@ -44,6 +44,10 @@
 
 #include "device_utils.cuh"
 
+#ifndef SDDMM_DENSE_BATCH
+#define SDDMM_DENSE_BATCH 4
+#endif
+
 namespace sddmm {
 
 constexpr int kDenseTile = 64;               // tile edge
@@ -325,8 +329,8 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
             if (tid < 128 && job < n_jobs) {
                 uint4 *dst = sRows + buf * 128 + tid;
                 const uint4 d = *dst;
-                const uint32_t cnt = __popc(d.z) + __popc(d.w);
-                dst->y = cnt ? ((d.x & 3u) + cnt + 3u) >> 2 : 0u;
+                const uint32_t lo = __popc(d.z), cnt = lo + __popc(d.w);
+                dst->y = (cnt ? ((d.x & 3u) + cnt + 3u) >> 2 : 0u) | (lo << 8);   // granules | nonzeros in columns 0..31
             }
         };
         // two rows per instruction: lanes 0..15 copy granules 0..15 of one row, lanes 16..31 those of the next;
@@ -337,7 +341,7 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
             for (int u = 0; u < 8; u += 2) {
                 const int r = (8 * half + u + side) * kDenseEpiWarps + warp;
                 const uint4 d = sRows[buf * 128 + r];
-                const int n = static_cast<int>(d.y);
+                const int n = static_cast<int>(d.y & 0xFFu);
                 float *dst = sSval + r * kDenseSvalStride;
                 const float *src = args.s_val + (d.x & ~3u);
                 if (g < n) cp_async_16(dst + 4 * g, src + 4 * g);
@@ -347,25 +351,47 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
             }
         };
         auto sample_half = [&](int buf, int half) {
+            // four rows at a time, every shared-memory read of the batch issued before the first store: the reads are
+            // unconditional (an absent nonzero reads a word of the row's own slot and drops it), so nothing orders them
+            // behind the predicated global stores of the previous row
+            constexpr int kBatch = SDDMM_DENSE_BATCH;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int r = (8 * half + u) * kDenseEpiWarps + warp;
-                const uint4 d = sRows[buf * 128 + r];
-                uint2 o = make_uint2(d.z, d.w);
-                if (OWN) o = sOwn[buf * 128 + r];
-                // lane l owns the adjacent columns 2l and 2l+1: one 8-byte read of the accumulator pair; the second
-                // column's nonzero (if any) directly follows the first one's in the run.  Positions come from the
-                // PRESENCE mask, what is written from the OWN mask.
-                const int st = static_cast<int>(d.x);
-                const uint32_t w = upper ? d.w : d.z;                       // the mask word that holds this lane's two bits
-                const uint32_t present = (w >> pshift) & 3u;
-                const uint32_t pair = ((upper ? o.y : o.x) >> pshift) & 3u;
-                const int k0 = (upper ? __popc(d.z) : 0) + __popc(w & pbelow);   // offset of column 2l inside the run
-                const float2 a = *reinterpret_cast<const float2 *>(sAcc + r * kDenseAccStride + 2 * lane);
-                const float *srow = sSval + r * kDenseSvalStride + (st & 3) + k0;
-                float *prow = args.p_val + st + k0;
-                if (pair & 1u) __stcs(prow, a.x * srow[0]);
-                if (pair & 2u) __stcs(prow + (present & 1u), a.y * srow[present & 1u]);
+            for (int u0 = 0; u0 < 8; u0 += kBatch) {
+                uint4 d[kBatch];
+                uint2 o[kBatch];
+                float2 a[kBatch];
+                float s0[kBatch], s1[kBatch];
+                int pos[kBatch];
+                uint32_t present[kBatch], pair[kBatch];
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    const int r = (8 * half + u0 + i) * kDenseEpiWarps + warp;
+                    d[i] = sRows[buf * 128 + r];
+                    o[i] = OWN ? sOwn[buf * 128 + r] : make_uint2(d[i].z, d[i].w);
+                }
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    // lane l owns the adjacent columns 2l and 2l+1: one 8-byte read of the accumulator pair; the second
+                    // column's nonzero (if any) directly follows the first one's in the run.  Positions come from the
+                    // PRESENCE mask, what is written from the OWN mask.
+                    const int r = (8 * half + u0 + i) * kDenseEpiWarps + warp;
+                    const int st = static_cast<int>(d[i].x);
+                    const uint32_t w = upper ? d[i].w : d[i].z;                       // the mask word that holds this lane's two bits
+                    present[i] = (w >> pshift) & 3u;
+                    pair[i] = ((upper ? o[i].y : o[i].x) >> pshift) & 3u;
+                    const int k0 = (upper ? static_cast<int>(d[i].y >> 8) : 0) + __popc(w & pbelow);   // offset of column 2l inside the run
+                    a[i] = *reinterpret_cast<const float2 *>(sAcc + r * kDenseAccStride + 2 * lane);
+                    const float *srow = sSval + r * kDenseSvalStride + (st & 3) + k0;
+                    s0[i] = srow[0];
+                    s1[i] = srow[present[i] & 1u];
+                    pos[i] = st + k0;
+                }
+#pragma unroll
+                for (int i = 0; i < kBatch; ++i) {
+                    float *prow = args.p_val + pos[i];
+                    if (pair[i] & 1u) __stcs(prow, a[i].x * s0[i]);
+                    if (pair[i] & 2u) __stcs(prow + (present[i] & 1u), a[i].y * s1[i]);
+                }
             }
         };
 

@@ -29,6 +29,7 @@
 #include "benchmark/competitor.hpp"
 #include "device_timed.hpp"
 #include "matrices/matrices.h"
+#include "pattern_copy.hpp"
 #include "sddmm_b200.h"
 
 namespace Competitors {
@@ -103,18 +104,12 @@ public:
 
     void cleanup_csr(Dense<T> &, Dense<T> &, CSR<T> &S, CSR<T> &P) override {
         if (!ready_) return;
-        if (P.getValues().size() != S.getValues().size()) P.setValues(S.getValues());
-        download(P.getValues().data());
-        P.setColPositions(S.getColPositions());
-        P.setRowPositions(S.getRowPositions());
+        SDDMM::finish_into(S, P, [&](T *values) { download(values); });
     }
 
     void cleanup_coo(Dense<T> &, Dense<T> &, COO<T> &S, COO<T> &P) override {
         if (!ready_) return;
-        if (P.getValues().size() != S.getValues().size()) P.setValues(S.getValues());
-        download(P.getValues().data());
-        P.setColPositions(S.getColPositions());
-        P.setRowPositions(S.getRowPositions());
+        SDDMM::finish_into(S, P, [&](T *values) { download(values); });
     }
 
     bool csr_supported() override { return true; }
