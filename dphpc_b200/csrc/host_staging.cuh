@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <atomic>
 #include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <mutex>
@@ -53,7 +54,12 @@ public:
 private:
     HostPool() {
         unsigned hw = std::thread::hardware_concurrency();
-        const int n = static_cast<int>(std::max(1u, std::min(hw ? hw / 2 : 2u, 8u))) - 1;
+        unsigned want = std::min(hw ? hw / 2 : 2u, 8u);
+        if (const char *env = std::getenv("SDDMM_B200_HOST_THREADS")) {   // override: 1 .. 64 threads including the caller
+            const int v = std::atoi(env);
+            if (v >= 1 && v <= 64) want = static_cast<unsigned>(v);
+        }
+        const int n = static_cast<int>(std::max(1u, want)) - 1;
         for (int i = 0; i < n; ++i) workers_.emplace_back([this] { loop(); });
     }
     ~HostPool() {
@@ -118,7 +124,15 @@ inline void parallel_memcpy(void *dst, const void *src, size_t bytes) {
 
 // two pinned buffers of one engine, used alternately
 struct HostStager {
-    static constexpr size_t kPiece = size_t(16) << 20;
+    // bytes per piece (= size of each pinned buffer); SDDMM_B200_STAGE_MB overrides the 16 MiB default (1 .. 256)
+    const size_t kPiece = [] {
+        size_t mb = 16;
+        if (const char *env = std::getenv("SDDMM_B200_STAGE_MB")) {
+            const int v = std::atoi(env);
+            if (v >= 1 && v <= 256) mb = static_cast<size_t>(v);
+        }
+        return mb << 20;
+    }();
     static constexpr size_t kMinStaged = size_t(4) << 20;   // smaller copies are left to the driver
     char *buf[2] = {nullptr, nullptr};
     cudaEvent_t ev[2] = {nullptr, nullptr};

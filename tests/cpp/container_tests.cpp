@@ -8,6 +8,7 @@
 
 #include "benchmark/dataset.hpp"
 #include "check.hpp"
+#include "competitors/gpu/pattern_copy.hpp"
 #include "matrices/matrices.h"
 
 TEST_CASE(coo_sizes) {
@@ -147,6 +148,28 @@ TEST_CASE(edge_list_reader) {
     CHECK(d.getS_CSR().getColPositions() == std::vector<int>({1, 0, 3}));
     CHECK(d.getS_CSR().getValues() == std::vector<float>({1.0f, 1.0f, 1.0f}));
     CHECK(throws([&] { SDDMM::EdgeListDataset x("small", path, 2, 2, 4); }));
+}
+
+// cleanup_* of the GPU competitors: P takes S's pattern on helper threads while the download fills the values
+// (the reference's convention for what P holds afterwards: src/competitors/gpu/gpu_convert.hpp:58-64)
+TEST_CASE(cleanup_hands_back_the_pattern_of_s_with_the_downloaded_values) {
+    std::vector<Triplet<float>> t = {{0, 1, 0.5f}, {0, 3, 1.5f}, {2, 0, 2.5f}, {3, 3, 3.5f}};
+    CSR<float> S(4, 4, t);
+    CSR<float> P;   // empty: values are sized, the pattern copied
+    SDDMM::finish_into(S, P, [](float *v) { for (int i = 0; i < 4; ++i) v[i] = 10.f * static_cast<float>(i); });
+    CHECK(P.getRowPositions() == S.getRowPositions());
+    CHECK(P.getColPositions() == S.getColPositions());
+    CHECK(P.getValues() == std::vector<float>({0.f, 10.f, 20.f, 30.f}));
+    CSR<float> stale(4, 4, t);   // same size, stale values: everything is overwritten, nothing reallocated
+    const float *before = stale.getValues().data();
+    SDDMM::finish_into(S, stale, [](float *v) { for (int i = 0; i < 4; ++i) v[i] = -1.f; });
+    CHECK(stale.getValues().data() == before);
+    CHECK(stale.getValues() == std::vector<float>(4, -1.f));
+    COO<float> Sc(S), Pc;
+    SDDMM::finish_into(Sc, Pc, [](float *v) { for (int i = 0; i < 4; ++i) v[i] = 1.f; });
+    CHECK(Pc.getRowPositions() == Sc.getRowPositions());
+    CHECK(Pc.getColPositions() == Sc.getColPositions());
+    CHECK(Pc.getValues() == std::vector<float>(4, 1.f));
 }
 
 int main(int argc, char **argv) { return tiny_test::run_all(argc > 1 ? argv[1] : nullptr); }
