@@ -2,7 +2,7 @@
 //
 // The driver stages such a copy through its own pinned buffer on one thread, which on this class of host moves about
 // 10 GB/s -- a fifth of what the link carries from pinned memory.  Here the staging is done by a small pool of host
-// threads: a copy is cut into pieces, the pool memcpy()s piece c+1 into one of two pinned ring buffers while the DMA
+// threads: a copy is cut into 8 MiB pieces, the pool memcpy()s piece c+1 into one of two pinned ring buffers while the DMA
 // engine moves piece c, and the other way round for downloads.  Pinned or registered host memory and device memory take
 // the direct cudaMemcpyAsync path.  Like a pageable cudaMemcpyAsync, a staged call returns when the caller's buffer is
 // free again (uploads) or filled (downloads).
@@ -124,9 +124,11 @@ inline void parallel_memcpy(void *dst, const void *src, size_t bytes) {
 
 // two pinned buffers of one engine, used alternately
 struct HostStager {
-    // bytes per piece (= size of each pinned buffer); SDDMM_B200_STAGE_MB overrides the 16 MiB default (1 .. 256)
+    // bytes per piece (= size of each pinned buffer); SDDMM_B200_STAGE_MB overrides the 8 MiB default (1 .. 256).
+    // Measured on a 16-core host with 8 pool threads, 678 MB up: 8 MiB 19-21 ms, 16 MiB 22-23 ms, 32 MiB 23-25 ms,
+    // 4 MiB and 2 MiB 43-75 ms (the per-piece hand-over dominates); 12 or 16 threads are no faster and at times far slower.
     const size_t kPiece = [] {
-        size_t mb = 16;
+        size_t mb = 8;
         if (const char *env = std::getenv("SDDMM_B200_STAGE_MB")) {
             const int v = std::atoi(env);
             if (v >= 1 && v <= 256) mb = static_cast<size_t>(v);
