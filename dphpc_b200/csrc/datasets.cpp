@@ -85,11 +85,31 @@ enum Stream : uint64_t { ST_A = 1, ST_B = 2, ST_VAL = 3, ST_LEN = 4, ST_COL = 5,
 
 }  // namespace
 
+// resize() without the value-initialising pass: the dense operands (gigabytes at K = 256) are first touched by the
+// threads that fill them
+template <class T>
+struct NoInit : std::allocator<T> {
+    template <class U>
+    struct rebind {
+        using other = NoInit<U>;
+    };
+    template <class U>
+    void construct(U *p) noexcept {
+        ::new (static_cast<void *>(p)) U;
+    }
+    template <class U, class... Args>
+    void construct(U *p, Args &&...args) {
+        ::new (static_cast<void *>(p)) U(std::forward<Args>(args)...);
+    }
+};
+using DenseVec = std::vector<float, NoInit<float>>;
+
 struct sddmm_dataset {
     std::string name;
     int64_t M = 0, N = 0, K = 0;
     std::vector<int32_t> row_ptr, col;
-    std::vector<float> val, A, B;
+    std::vector<float> val;
+    DenseVec A, B;
 };
 
 namespace {
@@ -97,7 +117,7 @@ namespace {
 void fill_dense(sddmm_dataset &d, uint64_t seed) {
     d.A.resize(static_cast<size_t>(d.M * d.K));
     d.B.resize(static_cast<size_t>(d.N * d.K));
-    auto fill = [&](std::vector<float> &v, uint64_t stream) {
+    auto fill = [&](DenseVec &v, uint64_t stream) {
         parallel_for(static_cast<int64_t>(v.size()), [&](int64_t a, int64_t b, int) {
             for (int64_t i = a; i < b; ++i) {
                 const uint64_t z = mix64(seed ^ mix64(stream * 0xD1B54A32D192ED03ull + static_cast<uint64_t>(i)));
