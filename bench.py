@@ -277,7 +277,7 @@ def run_reference_arm(args, rank, world):
 
 
 def kernel_only_stats(eng, steps, warmup, flush):
-    """(mean ms per step, {kernel: mean ms}) with L2 flushed before every step."""
+    """(median ms per step, {kernel: mean ms}) with L2 flushed before every step."""
     for _ in range(warmup):
         eng.run(); eng.sync()
     tot, per = [], {}
@@ -292,7 +292,7 @@ def kernel_only_stats(eng, steps, warmup, flush):
         for name, ms in eng.kernel_times():
             per.setdefault(name, []).append(ms)
     eng.set_kernel_timing(False)
-    return float(np.mean(tot)), {k: float(np.mean(v)) for k, v in per.items()}
+    return float(np.median(tot)), {k: float(np.mean(v)) for k, v in per.items()}
 
 
 def shard_of(d, rank, world):
@@ -674,16 +674,27 @@ def main():
                     e2 = Engine(local, m)
                     e2.upload_csr(s2["M"], dd.N, dd.K, s2["rp"], dd.col_idx[s2["j0"]:s2["j1"]], dd.s_val[s2["j0"]:s2["j1"]],
                                   dd.A[s2["r0"]:s2["r1"]], dd.B)
-                    ms_local, kern_c = kernel_only_stats(e2, 10, 3, flush)
-                    alg_local, plan_c = float(e2.algorithmic_bytes()), e2.plan()
                 else:
                     ms_local = 0.0
             except Exception as ex:  # report, never hide (the collectives below still run on every rank)
+                sys.stderr.write(f"rank {rank}: {key}: {ex}\n")
+                if e2 is not None:
+                    e2.close()
+                e2, ms_local = None, 1e30
+            # every rank has generated and uploaded before any rank times: a rank still generating its dataset on all host
+            # cores would delay the launches of the ranks that already time (the event pair spans the launches of a step)
+            barrier()
+            try:
+                if e2 is not None:
+                    ms_local, kern_c = kernel_only_stats(e2, 10, 3, flush)
+                    alg_local, plan_c = float(e2.algorithmic_bytes()), e2.plan()
+            except Exception as ex:
                 sys.stderr.write(f"rank {rank}: {key}: {ex}\n")
                 ms_local = 1e30
             finally:
                 if e2 is not None:
                     e2.close()
+            barrier()
             ms = max_over_ranks(ms_local)
             alg = sum_over_ranks(alg_local)
             if rank == 0:
