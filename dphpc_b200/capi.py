@@ -40,7 +40,7 @@ ENGINE_SYMBOLS = [
     "sddmm_b200_pipeline_create", "sddmm_b200_pipeline_destroy", "sddmm_b200_pipeline_sddmm_csr",
     "sddmm_b200_pipeline_last_chunks", "sddmm_b200_pipeline_last_error", "sddmm_b200_pipeline_set_min_chunk_bytes",
     "sddmm_b200_pipeline_update_csr", "sddmm_b200_pipeline_sddmm_coo", "sddmm_b200_set_knob",
-    "sddmm_b200_spmm", "sddmm_b200_last_spmm_ms", "sddmm_b200_row_cuts", "sddmm_b200_stage_b",
+    "sddmm_b200_spmm", "sddmm_b200_last_spmm_ms", "sddmm_b200_row_cuts", "sddmm_b200_coo_cuts", "sddmm_b200_upload_coo_rows", "sddmm_b200_stage_b",
     "sddmm_b200_selftest_wait_timeout",
 ]
 DATASET_SYMBOLS = [
@@ -120,6 +120,8 @@ def load_engine_lib() -> C.CDLL:
     lib.sddmm_b200_spmm.argtypes = [H, C.c_int64, C.c_void_p, C.c_void_p]
     lib.sddmm_b200_selftest_wait_timeout.argtypes = [H, C.c_int]
     lib.sddmm_b200_row_cuts.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_void_p]
+    lib.sddmm_b200_coo_cuts.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int64, C.c_void_p, C.c_void_p]
+    lib.sddmm_b200_upload_coo_rows.argtypes = [H, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 5
     lib.sddmm_b200_stage_b.argtypes = [C.POINTER(H), C.c_int, C.c_int64, C.c_int64, C.c_void_p]
     lib.sddmm_b200_last_spmm_ms.argtypes = [H, C.POINTER(C.c_float)]
     lib.sddmm_b200_algorithmic_bytes.argtypes = [H]
@@ -242,6 +244,15 @@ class Engine:
         assert row_idx.size == col_idx.size == s_val.size
         self._check(self.lib.sddmm_b200_upload_coo(self.h, M, N, K, row_idx.size, _ptr(row_idx), _ptr(col_idx), _ptr(s_val),
                                                    _ptr(A), _ptr(B)), "upload_coo")
+        self.nnz = int(row_idx.size)
+
+    def upload_coo_rows(self, M, N, K, row_base, row_idx, col_idx, s_val, A, B):
+        """Rows [row_base, row_base + M) of a larger COO matrix; row_idx keeps the matrix' own row numbers."""
+        row_idx, col_idx = _as(row_idx, np.int32), _as(col_idx, np.int32)
+        s_val, A, B = _as(s_val, np.float32), _as(A, np.float32), _as(B, np.float32)
+        assert row_idx.size == col_idx.size == s_val.size
+        self._check(self.lib.sddmm_b200_upload_coo_rows(self.h, M, N, K, row_idx.size, int(row_base), _ptr(row_idx), _ptr(col_idx),
+                                                        _ptr(s_val), _ptr(A), _ptr(B)), "upload_coo_rows")
         self.nnz = int(row_idx.size)
 
     def upload_csr_device(self, M, N, K, nnz, row_ptr, col_idx, s_val, A, B):

@@ -1206,6 +1206,16 @@ int sddmm_b200_upload_coo(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K,
     return upload_common(e, M, N, K, nnz, nullptr, nnz ? row_idx : &dummy, col_idx, s_val, A, B, cudaMemcpyHostToDevice);
 }
 
+int sddmm_b200_upload_coo_rows(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz, int64_t row_base, const int32_t *row_idx,
+                               const int32_t *col_idx, const float *s_val, const float *A, const float *B) {
+    if (!e) return SDDMM_B200_ERR_ARG;
+    if (row_base < 0 || row_base + M >= (int64_t(1) << 31)) return fail(e, SDDMM_B200_ERR_ARG, "row_base outside the int32 index range");
+    e->coo_row_base = static_cast<int32_t>(row_base);
+    const int st = sddmm_b200_upload_coo(e, M, N, K, nnz, row_idx, col_idx, s_val, A, B);
+    e->coo_row_base = 0;
+    return st;
+}
+
 int sddmm_b200_upload_csr_device(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, const int32_t *row_ptr,
                                  const int32_t *col_idx, const float *s_val, const float *A, const float *B) {
     if (!e) return SDDMM_B200_ERR_ARG;
@@ -1361,6 +1371,26 @@ int sddmm_b200_row_cuts(const int32_t *row_ptr, int64_t M, int parts, int64_t al
         if (align > 1) r = (r + align / 2) / align * align;
         cuts[g] = std::max<int64_t>(cuts[g - 1], std::min<int64_t>(r, M));
     }
+    return SDDMM_B200_OK;
+}
+
+int sddmm_b200_coo_cuts(const int32_t *row_idx, int64_t nnz, int64_t M, int parts, int64_t align, int64_t *cuts, int64_t *offsets) {
+    if (!cuts || !offsets || M < 0 || nnz < 0 || parts < 1 || (nnz > 0 && !row_idx)) return SDDMM_B200_ERR_ARG;
+    cuts[0] = 0;
+    offsets[0] = 0;
+    cuts[parts] = M;
+    offsets[parts] = nnz;
+    for (int g = 1; g < parts; ++g) {
+        int64_t r = nnz ? row_idx[std::min<int64_t>(nnz - 1, nnz * g / parts)] : 0;   // the row holding the part's first nonzero ...
+        if (r < 0 || r >= std::max<int64_t>(M, 1)) return SDDMM_B200_ERR_INDEX;
+        if (align > 1) r = std::min<int64_t>((r + align / 2) / align * align, M);
+        r = std::max<int64_t>(r, cuts[g - 1]);
+        const int64_t pos = std::lower_bound(row_idx, row_idx + nnz, static_cast<int32_t>(r)) - row_idx;   // ... taken whole
+        cuts[g] = r;
+        offsets[g] = std::max<int64_t>(pos, offsets[g - 1]);
+    }
+    for (int g = 0; g < parts; ++g)   // nonzeros in a part without rows: the rows cannot be sorted
+        if (cuts[g + 1] == cuts[g] && offsets[g + 1] != offsets[g]) return SDDMM_B200_ERR_INDEX;
     return SDDMM_B200_OK;
 }
 

@@ -99,9 +99,7 @@ int run_chunks(sddmm_b200_pipeline *p, int chunks, int64_t N, int64_t K, const i
             if (row_ptr) {
                 st = sddmm_b200_upload_csr(e, r1 - r0, N, K, local, col_idx + off, s_val + off, A + r0 * K, B);
             } else {
-                e->coo_row_base = static_cast<int32_t>(r0);
-                st = sddmm_b200_upload_coo(e, r1 - r0, N, K, n, row_idx + off, col_idx + off, s_val + off, A + r0 * K, B);
-                e->coo_row_base = 0;
+                st = sddmm_b200_upload_coo_rows(e, r1 - r0, N, K, n, r0, row_idx + off, col_idx + off, s_val + off, A + r0 * K, B);
             }
             e->h2d_after = nullptr;
             e->B_on_device = nullptr;
@@ -255,20 +253,8 @@ int sddmm_b200_pipeline_sddmm_coo(sddmm_b200_pipeline *p, int64_t M, int64_t N, 
     const int64_t align = M >= int64_t(64) * 8 * chunks ? 64 : 1;
     p->cuts.assign(static_cast<size_t>(chunks) + 1, 0);
     p->offsets.assign(static_cast<size_t>(chunks) + 1, 0);
-    p->cuts[static_cast<size_t>(chunks)] = M;
-    p->offsets[static_cast<size_t>(chunks)] = nnz;
-    for (int c = 1; c < chunks; ++c) {
-        int64_t r = nnz ? row_idx[std::min<int64_t>(nnz - 1, nnz * c / chunks)] : 0;   // the row holding the chunk's first nonzero ...
-        if (r < 0 || r >= M) return bad(SDDMM_B200_ERR_INDEX, "COO row indices must be sorted and inside [0, M)");
-        if (align > 1) r = std::min<int64_t>((r + align / 2) / align * align, M);
-        r = std::max<int64_t>(r, p->cuts[static_cast<size_t>(c) - 1]);
-        const int64_t pos = std::lower_bound(row_idx, row_idx + nnz, static_cast<int32_t>(r)) - row_idx;   // ... taken whole
-        p->cuts[static_cast<size_t>(c)] = r;
-        p->offsets[static_cast<size_t>(c)] = std::max<int64_t>(pos, p->offsets[static_cast<size_t>(c) - 1]);
-    }
-    for (int c = 0; c < chunks; ++c)   // nonzeros in a chunk without rows: the rows cannot be sorted
-        if (p->cuts[static_cast<size_t>(c) + 1] == p->cuts[static_cast<size_t>(c)] && p->offsets[static_cast<size_t>(c) + 1] != p->offsets[static_cast<size_t>(c)])
-            return bad(SDDMM_B200_ERR_INDEX, "COO row indices must be sorted and inside [0, M)");
+    if (sddmm_b200_coo_cuts(row_idx, nnz, M, chunks, align, p->cuts.data(), p->offsets.data()) != SDDMM_B200_OK)
+        return bad(SDDMM_B200_ERR_INDEX, "COO row indices must be sorted and inside [0, M)");
     return run_chunks(p, chunks, N, K, nullptr, row_idx, col_idx, s_val, A, B, p_val);
 }
 

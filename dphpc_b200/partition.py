@@ -33,6 +33,23 @@ def row_cuts(row_ptr: np.ndarray, parts: int, align: int = 1) -> np.ndarray:
     return cuts
 
 
+def coo_cuts(row_idx: np.ndarray, M: int, parts: int, align: int = 1):
+    """(cuts, offsets) of a COO row array sorted by row (sddmm_b200_coo_cuts): part g holds rows [cuts[g], cuts[g+1]) =
+    entries [offsets[g], offsets[g+1]); no row_ptr is built."""
+    import ctypes as C
+
+    from .capi import load_engine_lib
+
+    rows = np.ascontiguousarray(row_idx, dtype=np.int32)
+    cuts = np.zeros(parts + 1, dtype=np.int64)
+    offs = np.zeros(parts + 1, dtype=np.int64)
+    st = load_engine_lib().sddmm_b200_coo_cuts(C.c_void_p(rows.ctypes.data), C.c_int64(rows.size), C.c_int64(M), C.c_int(parts),
+                                               C.c_int64(align), C.c_void_p(cuts.ctypes.data), C.c_void_p(offs.ctypes.data))
+    if st:
+        raise ValueError(f"sddmm_b200_coo_cuts: status {st}")
+    return cuts, offs
+
+
 def shard(row_ptr, col_idx, s_val, A, rank: int, parts: int, align: int = 1):
     """(row0, row1, rebased row_ptr, col slice, val slice, A slice) of one rank; views where possible."""
     cuts = row_cuts(row_ptr, parts, align)

@@ -80,21 +80,25 @@ public:
         if (!ensure_engines()) return;
         const int64_t M = A.getRows(), N = B.getRows(), K = A.getCols();
         const std::vector<int> &rows = S.getRowPositions();   // sorted by row (src/matrices/COO.hpp:39)
-        std::vector<int> rp(static_cast<size_t>(M) + 1, 0);
-        for (int r : rows) ++rp[static_cast<size_t>(r) + 1];
-        for (int64_t i = 0; i < M; ++i) rp[static_cast<size_t>(i) + 1] += rp[static_cast<size_t>(i)];
-        plan_shards(rp, M);
+        const int64_t nnz = static_cast<int64_t>(rows.size());
+        // cuts and slice offsets straight from the sorted row array; every shard uploads its slice of the caller's arrays
+        // as they are and its device subtracts the shard's first row (no row_ptr, no rewritten copy on the host)
+        offsets_.assign(static_cast<size_t>(shards()) + 1, 0);
+        cuts_.assign(static_cast<size_t>(shards()) + 1, 0);
+        const int64_t align = M >= int64_t(64) * 8 * shards() ? 64 : 1;
+        if (sddmm_b200_coo_cuts(rows.data(), nnz, M, shards(), align, cuts_.data(), offsets_.data()) != SDDMM_B200_OK) {
+            std::cerr << "[" << name << "] COO row indices must be sorted and inside [0, M)" << std::endl;
+            return;
+        }
         if (!stage_b(N, K, B.get_pointer())) return;
         std::vector<int> status(shards(), SDDMM_B200_OK);
         parallel([&](int g) {
             const int64_t r0 = cuts_[static_cast<size_t>(g)], r1 = cuts_[static_cast<size_t>(g) + 1];
-            const int64_t off = rp[static_cast<size_t>(r0)], n = rp[static_cast<size_t>(r1)] - off;
+            const int64_t off = offsets_[static_cast<size_t>(g)], n = offsets_[static_cast<size_t>(g) + 1] - off;
             if (r1 == r0) return;
-            std::vector<int32_t> local(static_cast<size_t>(n));
-            for (int64_t j = 0; j < n; ++j) local[static_cast<size_t>(j)] = static_cast<int32_t>(rows[static_cast<size_t>(off + j)] - r0);
-            status[static_cast<size_t>(g)] = sddmm_b200_upload_coo(engines_[static_cast<size_t>(g)], r1 - r0, N, K, n, local.data(),
-                                                                    S.getColPositions().data() + off, S.getValues().data() + off,
-                                                                    A.get_pointer() + r0 * K, nullptr /* the staged B */);
+            status[static_cast<size_t>(g)] = sddmm_b200_upload_coo_rows(engines_[static_cast<size_t>(g)], r1 - r0, N, K, n, r0, rows.data() + off,
+                                                                         S.getColPositions().data() + off, S.getValues().data() + off,
+                                                                         A.get_pointer() + r0 * K, nullptr /* the staged B */);
         });
         after_upload(status);
     }

@@ -113,6 +113,13 @@ int sddmm_b200_upload_csr(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K,
 int sddmm_b200_upload_coo(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz,
                           const int32_t *row_idx, const int32_t *col_idx, const float *s_val,
                           const float *A, const float *B);
+/* A row slice of a larger COO matrix: the slice holds rows [row_base, row_base + M) of it, row_idx keeps the
+ * matrix' own (global) row numbers and the device subtracts row_base while it derives row_ptr -- the host neither
+ * copies nor rewrites the index array (row shards of one matrix on several engines).  A must point at the slice's
+ * first row.  SDDMM_B200_ERR_INDEX when a row index lies outside the slice. */
+int sddmm_b200_upload_coo_rows(sddmm_b200_engine *e, int64_t M, int64_t N, int64_t K, int64_t nnz, int64_t row_base,
+                               const int32_t *row_idx, const int32_t *col_idx, const float *s_val,
+                               const float *A, const float *B);
 /* Same as upload_csr but every pointer is a DEVICE pointer on the engine's
  * device (e.g. B received by an NCCL broadcast). The data is copied into the
  * engine's own aligned arena.  No reference counterpart (the reference keeps
@@ -253,6 +260,9 @@ const char *sddmm_b200_pipeline_last_error(sddmm_b200_pipeline *p);
  * nonzeros -- the row boundary closest to g * nnz / parts, moved to a multiple of `align` rows when align > 1 (64 keeps
  * the 64 x 64 tile grid of the tensor-core path in every shard).  The goal of the reference's CSR<T>::_dispatch
  * (src/matrices/CSR.hpp:196-264: equal nonzeros per worker), by one binary search per cut.  Host only.
+ * sddmm_b200_coo_cuts does the same from a COO row array sorted by row (no row_ptr is built): cuts[g] is the row and
+ * offsets[g] the position in row_idx where part g starts (offsets[parts] = nnz).  SDDMM_B200_ERR_INDEX when the
+ * entries it looks at are out of range or not sorted (the upload of every part validates its whole slice).
  *
  * sddmm_b200_stage_b: B crosses the host link ONCE, to engines[0]'s device, and is then copied device to device in
  * log2(n) rounds (every device that holds B serves one that does not; NVLink where the devices are peers).  After it
@@ -261,6 +271,8 @@ const char *sddmm_b200_pipeline_last_error(sddmm_b200_pipeline *p);
  * is in the engine's last_error); no engine keeps a staged B then.  No reference counterpart (the reference is
  * single-GPU: every competitor uploads B itself, e.g. src/competitors/gpu/gpu_basic.hpp:33-60). */
 int sddmm_b200_row_cuts(const int32_t *row_ptr, int64_t M, int parts, int64_t align, int64_t *cuts);
+int sddmm_b200_coo_cuts(const int32_t *row_idx, int64_t nnz, int64_t M, int parts, int64_t align, int64_t *cuts,
+                        int64_t *offsets);
 int sddmm_b200_stage_b(sddmm_b200_engine **engines, int n, int64_t N, int64_t K, const float *B);
 
 /* ---- self-test of the failure path ------------------------------------------------------------

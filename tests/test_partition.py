@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from dphpc_b200 import Dataset
-from dphpc_b200.partition import row_cuts, shard
+from dphpc_b200.partition import coo_cuts, row_cuts, shard
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -43,6 +43,27 @@ def test_cuts_on_degenerate_patterns():
     cuts = row_cuts(np.arange(9, dtype=np.int32), 8)                                     # diagonal: one row each
     assert cuts.tolist() == list(range(9))
     assert row_cuts(np.zeros(5, np.int32), 2)[[0, -1]].tolist() == [0, 4]                # empty matrix
+
+
+@pytest.mark.parametrize("parts", [1, 2, 3, 8])
+def test_coo_cuts_find_row_boundaries_without_a_row_ptr(parts):
+    d = Dataset(5, 4, 0.01)
+    rows = d.row_idx()
+    cuts, offs = coo_cuts(rows, d.M, parts)
+    assert cuts[0] == 0 and cuts[-1] == d.M and offs[0] == 0 and offs[-1] == d.nnz
+    assert (np.diff(cuts) >= 0).all() and (np.diff(offs) >= 0).all()
+    assert np.array_equal(offs, d.row_ptr[cuts])                       # every part starts at the first entry of its first row
+    longest = int(np.diff(d.row_ptr).max())
+    assert np.diff(offs).max() <= d.nnz / parts + longest
+    # aligned cuts, degenerate inputs, unsorted rows
+    cuts64, offs64 = coo_cuts(rows, d.M, parts, align=64)
+    assert all(int(c) % 64 == 0 for c in cuts64[1:-1]) and np.array_equal(offs64, d.row_ptr[cuts64])
+    c, o = coo_cuts(np.array([2, 2, 2, 2, 2], np.int32), 3, 2)
+    assert c.tolist() == [0, 2, 3] and o.tolist() == [0, 0, 5]          # all entries in the last row
+    c, o = coo_cuts(np.zeros(0, np.int32), 4, 2)
+    assert c[[0, -1]].tolist() == [0, 4] and o.tolist() == [0, 0, 0]   # empty matrix
+    with pytest.raises(ValueError):
+        coo_cuts(np.array([0, 1, 2, 9, 3, 3], np.int32), 4, 2)          # the entry a cut looks at lies outside [0, M)
 
 
 def test_shard_slices_rebase_row_ptr():

@@ -703,3 +703,29 @@ def test_bounded_wait_runs_out_and_is_reported(oracle):
     fresh = Engine(0, "fp32")
     assert fresh.lib.sddmm_b200_selftest_wait_timeout(fresh.h, 64) == 5         # before any upload: call order
     fresh.close()
+@pytest.mark.gpu
+def test_coo_row_slices_keep_the_global_row_numbers(oracle):
+    """Row shards of one COO matrix (sddmm_b200_coo_cuts + sddmm_b200_upload_coo_rows): each engine gets its slice of the
+    caller's arrays as they are, the device subtracts the slice's first row; together the slices give the whole result."""
+    from dphpc_b200.partition import coo_cuts
+    d = Dataset(5, 32, 0.02)
+    rows = d.row_idx()
+    want = oracle.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    bound = oracle_lib.abs_dot_bound(rows, d.col_idx, d.s_val, d.A, d.B)
+    cuts, offs = coo_cuts(rows, d.M, 3, align=64)
+    got = np.empty(d.nnz, np.float32)
+    for g in range(3):
+        r0, r1, j0, j1 = int(cuts[g]), int(cuts[g + 1]), int(offs[g]), int(offs[g + 1])
+        with Engine(0, "fp32") as e:
+            e.upload_coo_rows(r1 - r0, d.N, d.K, r0, rows[j0:j1], d.col_idx[j0:j1], d.s_val[j0:j1], d.A[r0:r1], d.B)
+            e.run(); e.sync()
+            got[j0:j1] = e.download()
+    oracle_lib.assert_values_close(got, want, bound, 1e-5, "COO row slices")
+    with Engine(0, "fp32") as e:   # a slice that holds a row of its neighbour is refused, not misread
+        r0, r1, j0, j1 = int(cuts[1]), int(cuts[2]), int(offs[1]), int(offs[2])
+        with pytest.raises(SddmmError) as err:
+            e.upload_coo_rows(r1 - r0, d.N, d.K, r0, rows[j0 - 1:j1], d.col_idx[j0 - 1:j1], d.s_val[j0 - 1:j1], d.A[r0:r1], d.B)
+        assert err.value.code == 2   # SDDMM_B200_ERR_INDEX
+    d.close()
+
+
