@@ -107,6 +107,7 @@ struct sddmm_b200_engine {
     int2 *d_dense_origin2 = nullptr;    // ... (arbitrary-offset detection); `dense_origin` points at the list in use
     const int2 *dense_origin = nullptr;
     bool dense_own = false;             // the tiles in use may overlap: the kernel looks at their own masks
+    bool dense_split3 = false;          // fp32-grade mode: operands through three slots, accumulator parked a tile at a time
     uint32_t *d_covered = nullptr;      // one bit per nonzero: owned by a dense tile
     uint32_t *d_cand = nullptr;         // one bit per nonzero: starts a half-full 64-column window of its row
     int2 *d_anchors = nullptr;          // candidate tile origins of the arbitrary-offset detection
@@ -142,7 +143,7 @@ struct sddmm_b200_engine {
     int l2_bytes = 0;
     // tuning knobs (sddmm_b200_set_knob; defaults from the environment at create): < 0 = decide automatically
     double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_fraction = -1, knob_group_units = -1,
-           knob_offset_tiles = -1;
+           knob_offset_tiles = -1, knob_dense_split3 = -1;
     bool rg_units = false;             // row groups run as shared segments (row-segment group kernel) instead of the warp-per-group kernel
 
     HostStager stager, stager2;   // pageable host memory goes through pinned ring buffers filled by a pool of host threads (one per stream)
@@ -458,6 +459,12 @@ int read_counters(sddmm_b200_engine *e, PlanCounters *out) {
 
 int cuda_status(sddmm_b200_engine *e, cudaError_t err);
 
+// the instantiation of the dense-tile kernel for (own masks looked at, three-slot operand scheme)
+const void *dense_function(bool own, bool split3) {
+    if (split3) return own ? reinterpret_cast<const void *>(sddmm_dense_tile_kernel<true, true>) : reinterpret_cast<const void *>(sddmm_dense_tile_kernel<false, true>);
+    return own ? reinterpret_cast<const void *>(sddmm_dense_tile_kernel<true, false>) : reinterpret_cast<const void *>(sddmm_dense_tile_kernel<false, false>);
+}
+
 int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item_nnz, int n_items) {
     e->n_dense = 0;
     e->n_residual_items = n_items;
@@ -556,8 +563,13 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     if (st) return st;
     const bool own_masks = offsets_used;   // tiles off the grid may overlap
     e->dense_own = own_masks;
-    const void *dense_fn = own_masks ? reinterpret_cast<const void *>(sddmm_dense_tile_kernel<true>) : reinterpret_cast<const void *>(sddmm_dense_tile_kernel<false>);
-    if (ensure_dynamic_smem_limit(dense_fn, e->device, DenseSmem::kDynamicBytes))
+    // fp32-grade mode, K >= 64: the three-slot operand scheme (measured on the 64 x 64-block configuration, K = 64 / 128:
+    // 74 / 114 us against 93 / 160 us with one A block + one B block; K = 32: 63-66 us either way, the shared-memory data
+    // pipe that the epilogue and the operand reads share is the limit there).  Knob "dense_split3": 0 = never, 1 = always.
+    e->dense_split3 = split && (e->knob_dense_split3 > 0 || (e->knob_dense_split3 < 0 && e->K >= 64));
+    const void *dense_fn = dense_function(e->dense_own, e->dense_split3);
+    const uint32_t dense_smem = e->dense_split3 ? DenseSmemT<true>::kDynamicBytes : DenseSmemT<false>::kDynamicBytes;
+    if (ensure_dynamic_smem_limit(dense_fn, e->device, dense_smem))
         return fail(e, SDDMM_B200_ERR_CUDA, "dense-tile kernel: cannot raise the dynamic shared memory limit");
     CU_TRY(e, cudaFuncSetAttribute(dense_fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     e->n_dense = n_dense;
@@ -567,7 +579,7 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     p.dense_nnz = static_cast<int64_t>(pc.dense_nnz);
     p.dense_tile_rows = p.dense_tile_cols = kDenseTile;
     p.dense_block = kDenseThreads;
-    p.dense_smem_bytes = static_cast<int32_t>(DenseSmem::kDynamicBytes);
+    p.dense_smem_bytes = static_cast<int32_t>(dense_smem);
     // Resident CTAs per SM, from the kernel's own resources (the runtime's occupancy query answers 1 for this kernel):
     // shared memory (+1 KB the driver reserves per CTA), registers (allocated per warp in units of 256), tensor memory columns.
     cudaFuncAttributes fa;
@@ -575,10 +587,10 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     int smem_per_sm = 0, regs_per_sm = 0;   // (single attributes: the full property query takes milliseconds)
     CU_TRY(e, cudaDeviceGetAttribute(&smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, e->device));
     CU_TRY(e, cudaDeviceGetAttribute(&regs_per_sm, cudaDevAttrMaxRegistersPerMultiprocessor, e->device));
-    const int by_smem = static_cast<int>(static_cast<size_t>(smem_per_sm) / (DenseSmem::kDynamicBytes + fa.sharedSizeBytes + 1024));
+    const int by_smem = static_cast<int>(static_cast<size_t>(smem_per_sm) / (dense_smem + fa.sharedSizeBytes + 1024));
     const int regs_per_warp = ((fa.numRegs * 32 + 255) / 256) * 256;
     const int by_regs = regs_per_sm / (regs_per_warp * (kDenseThreads / 32));
-    const int by_tmem = 512 / kTmemCols;
+    const int by_tmem = 512 / static_cast<int>(e->dense_split3 ? DenseSmemT<true>::kTmemColumns : DenseSmemT<false>::kTmemColumns);
     int dense_ctas_per_sm = std::min(std::min(by_smem, by_regs), std::min(by_tmem, kDenseCtasPerSm));
     if (dense_ctas_per_sm < 1) return fail(e, SDDMM_B200_ERR_CUDA, "dense-tile kernel does not fit on an SM");
     if (const char *env = getenv("SDDMM_B200_DENSE_CTAS_PER_SM")) {   // tuning knob: fewer resident CTAs per SM
@@ -1047,8 +1059,8 @@ int launch_all(sddmm_b200_engine *e) {
         d.k_blocks = static_cast<int32_t>((e->mode == SDDMM_B200_FP32_TC ? 3 * e->K : e->K) / 32);
         d.nnz = e->nnz;
         if ((st = begin_kernel(e, e->stream))) return st;
-        if (e->dense_own) sddmm_dense_tile_kernel<true><<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a, e->map_b);
-        else sddmm_dense_tile_kernel<false><<<p.dense_grid, kDenseThreads, DenseSmem::kDynamicBytes, e->stream>>>(d, e->map_a, e->map_b);
+        using DenseFn = void (*)(const DenseArgs, const CUtensorMap, const CUtensorMap);
+        reinterpret_cast<DenseFn>(const_cast<void *>(dense_function(e->dense_own, e->dense_split3)))<<<p.dense_grid, kDenseThreads, p.dense_smem_bytes, e->stream>>>(d, e->map_a, e->map_b);
         if ((st = mark_kernel(e, "sddmm_dense_tile_kernel", e->stream))) return st;
         if (e->n_residual_items == 0) return SDDMM_B200_OK;
     }
@@ -1125,6 +1137,7 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     e->knob_b_fraction = env_double("SDDMM_B200_B_FRACTION", -1);
     e->knob_group_units = env_double("SDDMM_B200_GROUP_UNITS", -1);
     e->knob_offset_tiles = env_double("SDDMM_B200_OFFSET_TILES", -1);
+    e->knob_dense_split3 = env_double("SDDMM_B200_DENSE_SPLIT3", -1);
     DeviceGuard g(device);
     bool ok = g.ok;
     ok = ok && cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -1475,7 +1488,7 @@ int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value) {
     struct { const char *name; double *slot; } knobs[] = {
         {"panels", &e->knob_panels}, {"panel_mb", &e->knob_panel_mb}, {"rowseg", &e->knob_rowseg},
         {"b_fraction", &e->knob_b_fraction}, {"group_units", &e->knob_group_units},
-        {"offset_tiles", &e->knob_offset_tiles},
+        {"offset_tiles", &e->knob_offset_tiles}, {"dense_split3", &e->knob_dense_split3},
     };
     for (auto &k : knobs)
         if (std::strcmp(name, k.name) == 0) {

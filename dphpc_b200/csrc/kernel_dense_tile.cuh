@@ -81,21 +81,27 @@ struct DenseArgs {
     int64_t nnz;                    // bound of every S.val / P.val position (checked builds only)
 };
 
-// shared memory carve-up (dynamic, 1024-byte aligned by hand)
-struct DenseSmem {
-    static constexpr uint32_t kStageBytes = 2 * kOperandBytes;   // A block + B block
-    static constexpr uint32_t kStage0 = 0;                        // one operand buffer: A block, B block right after it
+// shared memory carve-up (dynamic, 1024-byte aligned by hand).
+// SPLIT3 (the fp32-grade mode, three tf32 products per 32 columns of K): three 16 KB operand slots instead of one
+// A block + one B block, and room for the accumulator of ONE tile of the pair at a time -- see the kernel.
+template <bool SPLIT3>
+struct DenseSmemT {
+    static constexpr uint32_t kStageBytes = (SPLIT3 ? 3 : 2) * kOperandBytes;   // A block + B block (+ a third slot)
+    static constexpr uint32_t kStage0 = 0;                        // operand slots, 16 KB each, back to back
     static constexpr uint32_t kAcc = kStageBytes;
-    static constexpr uint32_t kAccBytes = 128 * kDenseAccStride * 4;
+    static constexpr uint32_t kAccRows = SPLIT3 ? 64 : 128;
+    static constexpr uint32_t kAccBytes = kAccRows * kDenseAccStride * 4;
     static constexpr uint32_t kSval = kAcc + kAccBytes;           // 128 rows x kDenseSvalStride floats: the S.val run of each tile row, as it lies in memory
     static constexpr uint32_t kSvalBytes = 128 * kDenseSvalStride * 4;
     static constexpr uint32_t kRows = kSval + kSvalBytes;         // 3 buffers x 128 row records {first CSR position, 16-byte granules of the run, mask lo, mask hi}
     static constexpr uint32_t kOwn = kRows + 3 * 128 * 16;        // 3 buffers x 128 own masks {lo, hi}
-    static constexpr uint32_t kBars = kOwn + 3 * 128 * 8;         // 4 mbarriers
-    static constexpr uint32_t kTmemPtr = kBars + 4 * 8;
+    static constexpr uint32_t kBars = kOwn + 3 * 128 * 8;         // 10 mbarriers (4 used without SPLIT3)
+    static constexpr uint32_t kTmemPtr = kBars + 10 * 8;
+    static constexpr uint32_t kTmemColumns = SPLIT3 ? 2 * kTmemCols : kTmemCols;   // SPLIT3: two accumulators, used alternately
     static constexpr uint32_t kTotal = kTmemPtr + 16;
     static constexpr uint32_t kDynamicBytes = kTotal + 1024;      // slack for the manual 1024-byte alignment
 };
+using DenseSmem = DenseSmemT<false>;
 
 __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *map, int x, int y, uint64_t *bar) {
     asm volatile(
@@ -156,10 +162,20 @@ __device__ __forceinline__ void epi_barrier() {  // the 8 epilogue warps only
 
 // OWN = false: the tiles do not overlap (tiles on the 64-grid), every present nonzero is the tile's own and the own masks
 // are neither fetched nor looked at.
-template <bool OWN>
+//
+// SPLIT3 = true (fp32-grade mode; operand rows [A_lo | A_hi | A_hi] and [B_hi | B_lo | B_hi], each part K wide): per
+// 32 columns of K the accumulator takes A_hi.B_lo + A_hi.B_hi + A_lo.B_hi.  With one A block + one B block in shared
+// memory that is three TMA round trips in a row per job, which -- not the epilogue -- then sets the pace.  Here the
+// four distinct 16 KB operand blocks go through THREE slots: X <- A_hi, Y <- B_lo, Z <- B_hi are requested together,
+// MMA(X, Y) and MMA(X, Z) run as they land, Y is refilled with A_lo as soon as MMA(X, Y) has read it, then MMA(Y, Z):
+// two round trips per job, and X of the next job is requested while Y is on its way.  The third slot is paid for by
+// parking the accumulator of one tile of the pair at a time (64 rows instead of 128): tile 0 is moved out of tensor
+// memory and sampled, then tile 1 -- the epilogue has the time, the tensor memory is released after the second move.
+template <bool OWN, bool SPLIT3>
 __global__ void __launch_bounds__(kDenseThreads, kDenseCtasPerSm)
 sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b) {
+    using DenseSmem = DenseSmemT<SPLIT3>;
     extern __shared__ unsigned char dense_smem_raw[];
     // 1024-byte alignment by an OFFSET into the shared array (not by rounding a generic address): every pointer below
     // stays a shared-memory pointer for the compiler, so its loads and stores are shared-space instructions that it may
@@ -171,6 +187,12 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     uint2 *sOwn = reinterpret_cast<uint2 *>(smem + DenseSmem::kOwn);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + DenseSmem::kBars);
     uint64_t *ops_full = &bars[0], *ops_free = &bars[1], *acc_full = &bars[2], *acc_free = &bars[3];
+    uint64_t *slot_full = &bars[4];   // SPLIT3: [4..6] = slot X, Y, Z filled (bars[0], [1], [7] = slot released)
+    auto slot_free = [&](int sl) -> uint64_t * { return sl == 0 ? &bars[0] : sl == 1 ? &bars[1] : &bars[7]; };
+    // SPLIT3 keeps two accumulators in tensor memory (job n in buffer n & 1: bars[2], [3] for buffer 0, bars[8], [9] for buffer 1),
+    // so the MMAs of the next job never wait for the epilogue of this one
+    auto acc_full_of = [&](uint32_t b) -> uint64_t * { return b ? &bars[8] : acc_full; };
+    auto acc_free_of = [&](uint32_t b) -> uint64_t * { return b ? &bars[9] : acc_free; };
     uint32_t *tmem_ptr_smem = reinterpret_cast<uint32_t *>(smem + DenseSmem::kTmemPtr);
 
     const int tid = threadIdx.x;
@@ -194,11 +216,19 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
         mbar_init(ops_free, 1);
         mbar_init(acc_full, 1);
         mbar_init(acc_free, kDenseEpiWarps);
+        if (SPLIT3) {
+            mbar_init(&bars[4], 1);
+            mbar_init(&bars[5], 1);
+            mbar_init(&bars[6], 1);
+            mbar_init(&bars[7], 1);
+            mbar_init(&bars[8], 1);
+            mbar_init(&bars[9], kDenseEpiWarps);
+        }
         fence_mbar_init();
         fence_proxy_async_smem();
     }
     if (warp == 0) {  // one warp allocates the tensor memory for the CTA
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)), "r"(DenseSmem::kTmemColumns) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
 
@@ -257,10 +287,39 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
         }
     };
 
+    // ---- SPLIT3 producer: three operand slots (0 = X, 1 = Y, 2 = Z), iterations = (job, 32 columns of K) ----
+    const int kk_per_job = kbs / 3;                     // 32-column pieces of K
+    const int k_cols = kk_per_job * 32;                 // K: the width of each of the three parts of an operand row
+    const uint32_t total3 = static_cast<uint32_t>(my_jobs) * static_cast<uint32_t>(kk_per_job);
+    uint32_t n_rel[3] = {0u, 0u, 0u};                   // fills requested per slot (the k-th waits for the (k-1)-th release)
+    uint32_t n_fill[3] = {0u, 0u, 0u};                  // fills consumed per slot
+    auto slot_ptr = [&](int sl) -> unsigned char * { return smem + DenseSmem::kStage0 + static_cast<uint32_t>(sl) * kOperandBytes; };
+    // request 128 operand rows (64 of each tile of the pair) x 32 columns starting at column x into a slot
+    auto fill_slot = [&](int sl, const CUtensorMap *map, int x, int row_a, int row_b) -> bool {
+        if (!mbar_wait_bounded(slot_free(sl), (n_rel[sl] & 1u) ^ 1u)) return false;   // read by the MMAs that used it last?
+        ++n_rel[sl];
+        unsigned char *dst = slot_ptr(sl);
+        mbar_expect_tx(&slot_full[sl], kOperandBytes);
+        tma_load_2d(dst, map, x, row_a, &slot_full[sl]);
+        tma_load_2d(dst + kHalfOperandBytes, map, x, row_b, &slot_full[sl]);
+        return true;
+    };
+    auto slot_landed = [&](int sl) -> bool {
+        const bool landed = mbar_wait_bounded(&slot_full[sl], n_fill[sl] & 1u);
+        ++n_fill[sl];
+        return landed;
+    };
+
     // ---- before the CTA barrier: first operand request (producer), first row records (epilogue warps) ----
     if (is_producer) {
         if (my_jobs > 1) load_ids(1, nxt0, nxt1);
-        if (total > 0) prod_ok = issue_tma(0);
+        if (SPLIT3) {
+            if (total3 > 0)   // A_hi, B_lo, B_hi of the first 32 columns of the first job
+                prod_ok = fill_slot(0, &map_a, k_cols, cur0.x, cur1.x) && fill_slot(1, &map_b, k_cols, cur0.y, cur1.y) &&
+                          fill_slot(2, &map_b, 0, cur0.y, cur1.y);
+        } else if (total > 0) {
+            prod_ok = issue_tma(0);
+        }
     } else if (warp < kDenseEpiWarps && static_cast<int>(blockIdx.x) < n_jobs) {
         fetch_rows(blockIdx.x, 0);
         cp_async_commit();
@@ -272,7 +331,56 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
 
     if (warp == kDenseEpiWarps) {
         // ===================== producer + MMA issuer (one thread) =====================
-        if (lane == 0) {
+        if (lane == 0 && SPLIT3) {
+            bool ok = prod_ok;
+            uint32_t jb = 0;  // jobs whose MMAs have been issued (phase of acc_free / acc_full)
+            auto mma4 = [&](int sa, int sb, bool fresh) {   // 4 k-steps of 8 tf32 = 32 bytes inside the swizzle atom
+                const uint32_t a_s = smem_u32(slot_ptr(sa)), b_s = smem_u32(slot_ptr(sb));
+                const uint32_t d_tmem = tmem_base + (jb & 1u) * static_cast<uint32_t>(kTmemCols);   // this job's accumulator
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint32_t adv = static_cast<uint32_t>(ks) * 32u;
+                    umma_tf32(d_tmem, umma_smem_desc(a_s + adv), umma_smem_desc(b_s + adv), (fresh && ks == 0) ? 0u : 1u);
+                }
+            };
+            for (uint32_t it = 0; it < total3 && ok; ++it) {
+                const int kk = static_cast<int>(it % static_cast<uint32_t>(kk_per_job));
+                const bool last_kk = kk == kk_per_job - 1;
+                const bool more = it + 1 < total3;
+                // the iteration after this one: same job, next 32 columns -- or the first 32 columns of the next job
+                const int kk_n = last_kk ? 0 : kk + 1;
+                const int2 n0 = last_kk ? nxt0 : cur0, n1 = last_kk ? nxt1 : cur1;
+                if (!slot_landed(0) || !slot_landed(1)) { ok = false; break; }           // A_hi, B_lo
+                // this job's accumulator drained by the epilogue of the job before last?
+                if (kk == 0 && !mbar_wait_bounded(acc_free_of(jb & 1u), ((jb >> 1) & 1u) ^ 1u)) { ok = false; break; }
+                tcgen05_fence_after();
+                mma4(0, 1, kk == 0);                                                     // A_hi . B_lo
+                umma_commit(slot_free(1));
+                if (!slot_landed(2)) { ok = false; break; }                              // B_hi
+                tcgen05_fence_after();
+                mma4(0, 2, false);                                                       // A_hi . B_hi
+                umma_commit(slot_free(0));
+                if (!fill_slot(1, &map_a, 32 * kk, cur0.x, cur1.x)) { ok = false; break; }                     // Y <- A_lo (once A_hi . B_lo has read it)
+                if (more && !fill_slot(0, &map_a, k_cols + 32 * kk_n, n0.x, n1.x)) { ok = false; break; }      // X <- A_hi of the next iteration, on its way meanwhile
+                if (!slot_landed(1)) { ok = false; break; }
+                tcgen05_fence_after();
+                mma4(1, 2, false);                                                       // A_lo . B_hi
+                umma_commit(slot_free(1));
+                umma_commit(slot_free(2));
+                if (last_kk) {
+                    umma_commit(acc_full_of(jb & 1u));   // arrives once the accumulator of this job is complete
+                    ++jb;
+                }
+                if (more && !(fill_slot(1, &map_b, k_cols + 32 * kk_n, n0.y, n1.y) && fill_slot(2, &map_b, 32 * kk_n, n0.y, n1.y))) { ok = false; break; }
+                if (last_kk && more) {
+                    cur0 = nxt0;
+                    cur1 = nxt1;
+                    const uint32_t j = it / static_cast<uint32_t>(kk_per_job);
+                    if (j + 2 < static_cast<uint32_t>(my_jobs)) load_ids(j + 2, nxt0, nxt1);
+                }
+            }
+            if (!ok) atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
+        } else if (lane == 0) {
             bool ok = prod_ok;
             uint32_t jb = 0;  // jobs whose MMAs have been issued (phase of acc_free / acc_full)
             for (uint32_t it = 0; it < total && ok; ++it) {
@@ -380,7 +488,7 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
                     present[i] = (w >> pshift) & 3u;
                     pair[i] = ((upper ? o[i].y : o[i].x) >> pshift) & 3u;
                     const int k0 = (upper ? static_cast<int>(d[i].y >> 8) : 0) + __popc(w & pbelow);   // offset of column 2l inside the run
-                    a[i] = *reinterpret_cast<const float2 *>(sAcc + r * kDenseAccStride + 2 * lane);
+                    a[i] = *reinterpret_cast<const float2 *>(sAcc + (SPLIT3 ? (r & 63) : r) * kDenseAccStride + 2 * lane);
                     const float *srow = sSval + r * kDenseSvalStride + (st & 3) + k0;
                     s0[i] = srow[0];
                     s1[i] = srow[present[i] & 1u];
@@ -414,32 +522,46 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
             if (ok) {   // one lane polls, then the warp re-converges before the warp-wide tcgen05.ld
                 int got = 1;
                 if (lane == 0) {
-                    got = mbar_wait_bounded(acc_full, jb & 1u) ? 1 : 0;
+                    got = (SPLIT3 ? mbar_wait_bounded(acc_full_of(jb & 1u), (jb >> 1) & 1u) : mbar_wait_bounded(acc_full, jb & 1u)) ? 1 : 0;
                     if (!got) atomicCAS(args.err, kDevOk, kDevMbarrierTimeout);
                 }
                 __syncwarp();
                 ok = __shfl_sync(kFullMask, got, 0) != 0;
             }
-            if (ok) {
-                tcgen05_fence_after();
-                uint32_t v[32];
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + static_cast<uint32_t>(64 * tile_of_q + 32 * h);
-                tmem_ld_32x32b_x32(taddr, v);
-                tcgen05_fence_before();
-                float *row = sAcc + (32 * q + lane) * kDenseAccStride + 32 * h;
+            // accumulator rows of this warp's tensor-memory lanes -> shared memory (thread = row), then release the tensor memory
+            auto park = [&]() {
+                if (ok) {
+                    tcgen05_fence_after();
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * q) << 16) + static_cast<uint32_t>(64 * tile_of_q + 32 * h) +
+                                           (SPLIT3 ? (jb & 1u) * static_cast<uint32_t>(kTmemCols) : 0u);
+                    tmem_ld_32x32b_x32(taddr, v);
+                    tcgen05_fence_before();
+                    float *row = sAcc + (32 * (SPLIT3 ? (q & 1) : q) + lane) * kDenseAccStride + 32 * h;
 #pragma unroll
-                for (int c = 0; c < 32; c += 2)
-                    *reinterpret_cast<float2 *>(row + c) = make_float2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
-            }
+                    for (int c = 0; c < 32; c += 2)
+                        *reinterpret_cast<float2 *>(row + c) = make_float2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+                }
+            };
+            if (!SPLIT3 || tile_of_q == 0) park();
             cp_async_wait_group<2>();               // this thread's share of the next job's records
             finish_rows(job + stride_jobs, buf1);
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_free);   // tensor memory may be overwritten by the next job
+            if ((!SPLIT3 || tile_of_q == 0) && lane == 0) mbar_arrive(SPLIT3 ? acc_free_of(jb & 1u) : acc_free);   // (all 8 warps have arrived: that accumulator may be overwritten)
             epi_barrier();                          // accumulator + next job's records visible to all epilogue warps
             fetch_rows(job + 2 * stride_jobs, buf2);
             cp_async_commit();
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
+                if (SPLIT3 && half == 1) {          // the second tile of the pair takes the place of the first
+                    epi_barrier();                  // every warp is done with the first tile's accumulator
+                    if (tile_of_q == 1) {
+                        park();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_free_of(jb & 1u));
+                    }
+                    epi_barrier();
+                }
                 cp_async_wait_group<2>();   // this lane's granules of this half ...
                 __syncwarp();               // ... and every other lane's
                 if (ok) sample_half(buf, half);
@@ -455,7 +577,7 @@ sddmm_dense_tile_kernel(const DenseArgs args, const __grid_constant__ CUtensorMa
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(DenseSmem::kTmemColumns) : "memory");
     }
 }
 

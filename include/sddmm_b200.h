@@ -178,7 +178,9 @@ int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info);
  *   "rowseg"        0: never take the row-segment kernel, 1: take it whenever it applies
  *   "b_fraction"    with column panels the gathers of B carry an L2 evict_last hint: share of the lines it applies to, (0, 1]
  *   "group_units"   0: rows with identical column lists run the warp-per-group kernel instead of shared segments
- *   "offset_tiles"  0: dense tiles only on the 64-grid, 1: always also look for half-full 64x64 windows at arbitrary offsets */
+ *   "offset_tiles"  0: dense tiles only on the 64-grid, 1: always also look for half-full 64x64 windows at arbitrary offsets
+ *   "dense_split3"  fp32-grade mode on dense tiles: 1 = operands through three shared-memory slots and two accumulators in
+ *                   tensor memory (default for K >= 64), 0 = one A block + one B block like the other modes */
 int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value);
 /* compulsory traffic e*K*(M+ + N+) + 12*nnz + 4*(M+1) with e = bytes per stored
  * element of A/B; extends the read-only model of plots/plot_roofline.py:30 */

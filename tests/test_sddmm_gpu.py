@@ -729,3 +729,23 @@ def test_coo_row_slices_keep_the_global_row_numbers(oracle):
     d.close()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("K", [32, 64, 96])
+@pytest.mark.parametrize("variant", [0, 1])
+def test_fp32_grade_dense_tiles_three_slot_operands(oracle, K, variant):
+    """fp32-grade mode on dense tiles with the operands going through three shared-memory slots and two accumulators in
+    tensor memory (the default for K >= 64) against the one-buffer form: both within the fp32 bar of the oracle, for one,
+    two and three 32-column pieces of K, tiles on the grid and at arbitrary offsets (overlapping tiles: own masks)."""
+    d = Dataset(2, K, 0.15, variant=variant)
+    want = oracle.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    bound = oracle_lib.abs_dot_bound(oracle.coo_rows(d.M, d.row_ptr), d.col_idx, d.s_val, d.A, d.B)
+    for split3 in (1, 0):
+        with Engine(0, "fp32_tc") as e:
+            e.set_knob("dense_split3", split3)
+            p = e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+            plan = e.plan()
+            assert plan["dense_tiles"] > 0 and plan["dense_nnz"] > 0.9 * d.nnz
+        oracle_lib.assert_values_close(p, want, bound, 1e-5, f"fp32_tc K={K} variant {variant} split3={split3}")
+    d.close()
+
+
