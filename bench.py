@@ -639,7 +639,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": {"fp32": "f32", "fp32_tc": "f32 (tf32x3 on dense tiles)", "tf32": "tf32", "bf16": "bf16"}[args.mode],
             "data": "synthetic", "config": workload_config(cfg, K, args.mode, world),
-            "e2e": e2e, "gpu_launches": int(args.steps * plan["n_kernels"]), "roofline": roofline, "clocks": clocks,
+            "e2e": e2e, "gpu_launches": int(args.steps * (plan["n_kernels"] + max(0, plan.get("rowseg_passes", 1) - 1))), "roofline": roofline, "clocks": clocks,
             "wall_s_timed_region": wall, "per_rank": per_rank, "parity": parity,
             "plan": {k: plan[k] for k in ("nnz", "rows_nonempty", "cols_touched", "max_row_nnz", "rowtile_nnz", "rowtile_items",
                                           "rowtile_rows_per_stage", "rowtile_grid", "rowtile_smem_bytes", "dense_nnz", "dense_tiles",

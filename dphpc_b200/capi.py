@@ -68,7 +68,7 @@ class PlanInfo(C.Structure):
         ("rowgroup_grid", C.c_int32),
         ("n_kernels", C.c_int32), ("n_devices", C.c_int32),
         ("rowseg_nnz", C.c_int64),
-        ("rowseg_units", C.c_int32), ("rowseg_panels", C.c_int32), ("rowseg_grid", C.c_int32), ("reserved0", C.c_int32),
+        ("rowseg_units", C.c_int32), ("rowseg_panels", C.c_int32), ("rowseg_grid", C.c_int32), ("rowseg_passes", C.c_int32),
     ]
 
     def as_dict(self) -> dict:

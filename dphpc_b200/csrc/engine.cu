@@ -107,6 +107,7 @@ struct sddmm_b200_engine {
     int2 *d_dense_origin2 = nullptr;    // ... (arbitrary-offset detection); `dense_origin` points at the list in use
     const int2 *dense_origin = nullptr;
     bool dense_own = false;             // the tiles in use may overlap: the kernel looks at their own masks
+    int seg_slices = 1;                 // row-segment path: K is taken in this many slices of 64 columns, one launch each
     bool dense_split3 = false;          // fp32-grade mode: operands through three slots, accumulator parked a tile at a time
     uint32_t *d_covered = nullptr;      // one bit per nonzero: owned by a dense tile
     uint32_t *d_cand = nullptr;         // one bit per nonzero: starts a half-full 64-column window of its row
@@ -143,7 +144,7 @@ struct sddmm_b200_engine {
     int l2_bytes = 0;
     // tuning knobs (sddmm_b200_set_knob; defaults from the environment at create): < 0 = decide automatically
     double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_fraction = -1, knob_group_units = -1,
-           knob_offset_tiles = -1, knob_dense_split3 = -1;
+           knob_offset_tiles = -1, knob_dense_split3 = -1, knob_k_slices = -1;
     bool rg_units = false;             // row groups run as shared segments (row-segment group kernel) instead of the warp-per-group kernel
 
     HostStager stager, stager2;   // pageable host memory goes through pinned ring buffers filled by a pool of host threads (one per stream)
@@ -279,10 +280,20 @@ double env_double(const char *name, double fallback) {
 // Column panels of the row-segment path.  B is cut into panels when it is much larger than the L2 cache, so that the
 // gathers of one panel hit in L2; every panel pass reads the A rows it touches again and shortens the runs a row
 // contributes (a run of fewer than ~6 nonzeros leaves most of a segment's 8 slots empty), which bounds the count.
+// Large K, fp32 storage, B far larger than L2: K is taken in slices of 64 columns, one launch of the K = 64 kernel per
+// slice over the same unit list, each adding to P.val -- a slice of B is small enough for column panels to keep it in
+// L2, where the whole rows are not (knob "k_slices": 0 = never, 1 = whenever K allows).
+int choose_k_slices(const sddmm_b200_engine *e) {
+    if (e->mode == SDDMM_B200_BF16 || e->K < 128 || e->K % 64 != 0 || e->knob_k_slices == 0) return 1;
+    const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
+    if (e->knob_k_slices < 0 && static_cast<double>(e->N) * e->K * 4.0 <= 4.0 * l2) return 1;
+    return static_cast<int>(e->K / 64);
+}
+
 int choose_panels(const sddmm_b200_engine *e) {
     if (e->knob_panels >= 1 && e->knob_panels <= 64) return static_cast<int>(e->knob_panels);
     const double eb = static_cast<double>(elem_bytes(e));
-    const double b_bytes = static_cast<double>(e->N) * e->K * eb;
+    const double b_bytes = static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) * eb;
     const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
     if (b_bytes <= l2) return 1;
     if (e->mode == SDDMM_B200_BF16) return 1;   // measured: with bf16 storage the extra segments cost more than the saved DRAM reads
@@ -316,6 +327,7 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     const size_t o_err = c.take(sizeof(int32_t));
     const size_t o_gok = c.take(M / 2 + 4);   // one byte per row group (groups of >= 2 rows, plus the leading partial group)
     // row-segment path: unit list (upper bound: one unit per 8 nonzeros plus one ragged unit per row and panel), scan scratch
+    e->seg_slices = choose_k_slices(e);
     e->panels = choose_panels(e);
     e->panel_cols = static_cast<int32_t>((N + e->panels - 1) / e->panels);
     const size_t runs = std::min(M * static_cast<size_t>(e->panels), nnz);
@@ -721,6 +733,9 @@ const void *seg_function(const sddmm_b200_engine *e, bool hint) {
         const int cpl = round_up_cpl((e->K + 1) / 2);   // chunks of 8: K / 64 lanes-rounds
         return reinterpret_cast<const void *>(pick_rowseg<Bf16x8>(cpl, e->K == 64 * cpl, hint));
     }
+    if (e->seg_slices > 1)   // a 64-column slice of fp32 rows
+        return hint ? reinterpret_cast<const void *>(sddmm_rowseg_kernel<2, true, float, true, true>)
+                    : reinterpret_cast<const void *>(sddmm_rowseg_kernel<2, true, float, false, true>);
     const bool exact = e->K == 32 * e->cpl;
     return e->mode == SDDMM_B200_BF16 ? reinterpret_cast<const void *>(pick_rowseg<__nv_bfloat16>(e->cpl, exact, hint))
                                       : reinterpret_cast<const void *>(pick_rowseg<float>(e->cpl, exact, hint));
@@ -795,6 +810,7 @@ int build_rowseg_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     p.rowseg_nnz = e->nnz;
     p.rowseg_units = e->n_units;
     p.rowseg_panels = panels;
+    p.rowseg_passes = e->seg_slices;
     p.rowseg_grid = static_cast<int32_t>(std::min<int64_t>((n_quads + kRowSegWarps - 1) / kRowSegWarps, static_cast<int64_t>(e->sm_count) * occ));
     p.rowtile_nnz = 0;
     p.rowtile_items = 0;
@@ -1009,14 +1025,28 @@ int launch_rowseg(sddmm_b200_engine *e, cudaStream_t stream) {
     g.b_fraction = e->knob_b_fraction > 0 ? static_cast<float>(std::min(1.0, e->knob_b_fraction)) : 1.0f;
     g.unit_cols = e->d_unit_cols; g.unit_sval = e->d_unit_sval;
     if (!e->seg_copies) g.b_evict_last = 0;   // (the hinted instantiation reads the per-unit copies)
+    g.row_stride = 0;
+    g.accumulate = 0;
     if (int st = begin_kernel(e, stream)) return st;
     if (e->mode == SDDMM_B200_BF16) {
         g.A = e->d_A16; g.B = e->d_B16;
     } else {
         g.A = e->d_A32; g.B = e->d_B32;
     }
-    reinterpret_cast<RowSegFn<float>>(const_cast<void *>(seg_function(e, g.b_evict_last != 0)))<<<p.rowseg_grid, kRowSegWarps * 32, 0, stream>>>(g);
-    return mark_kernel(e, "sddmm_rowseg_kernel", stream);
+    const auto fn = reinterpret_cast<RowSegFn<float>>(const_cast<void *>(seg_function(e, g.b_evict_last != 0)));
+    if (e->seg_slices > 1) {   // one launch per 64-column slice of K, in stream order: each adds to what the earlier ones wrote
+        g.K = 64;
+        g.row_stride = static_cast<uint32_t>(e->K * 4);
+        for (int sl = 0; sl < e->seg_slices; ++sl) {
+            g.A = e->d_A32 + 64 * sl;
+            g.B = e->d_B32 + 64 * sl;
+            g.accumulate = sl > 0 ? 1 : 0;
+            fn<<<p.rowseg_grid, kRowSegWarps * 32, 0, stream>>>(g);
+        }
+    } else {
+        fn<<<p.rowseg_grid, kRowSegWarps * 32, 0, stream>>>(g);
+    }
+    return mark_kernel(e, "sddmm_rowseg_kernel", stream);   // (the slices of one step count as one kernel in the timing table)
 }
 
 int launch_all(sddmm_b200_engine *e) {
@@ -1138,6 +1168,7 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     e->knob_group_units = env_double("SDDMM_B200_GROUP_UNITS", -1);
     e->knob_offset_tiles = env_double("SDDMM_B200_OFFSET_TILES", -1);
     e->knob_dense_split3 = env_double("SDDMM_B200_DENSE_SPLIT3", -1);
+    e->knob_k_slices = env_double("SDDMM_B200_K_SLICES", -1);
     DeviceGuard g(device);
     bool ok = g.ok;
     ok = ok && cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -1488,7 +1519,7 @@ int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value) {
     struct { const char *name; double *slot; } knobs[] = {
         {"panels", &e->knob_panels}, {"panel_mb", &e->knob_panel_mb}, {"rowseg", &e->knob_rowseg},
         {"b_fraction", &e->knob_b_fraction}, {"group_units", &e->knob_group_units},
-        {"offset_tiles", &e->knob_offset_tiles}, {"dense_split3", &e->knob_dense_split3},
+        {"offset_tiles", &e->knob_offset_tiles}, {"dense_split3", &e->knob_dense_split3}, {"k_slices", &e->knob_k_slices},
     };
     for (auto &k : knobs)
         if (std::strcmp(name, k.name) == 0) {

@@ -48,6 +48,10 @@ struct RowSegArgs {
     // place would touch one or two 32-byte sectors of a 128-byte line per unit; the copies are read front to back.
     const int32_t *unit_cols;
     const float *unit_sval;
+    // K in slices (large K, B far larger than L2): the launch covers columns [k0, k0 + K) of rows that are row_stride bytes
+    // apart (A and B point at column k0; 0 = rows of exactly K elements) and, from the second slice on, adds to P.val
+    uint32_t row_stride;
+    int32_t accumulate;
 };
 
 constexpr int kRowSegWarps = 8;
@@ -83,7 +87,13 @@ __device__ __forceinline__ uint4 ld_chunk_hint(const uint4 *p, uint64_t pol) {
 
 // HINT: column panels -- the B gathers carry the L2 evict_last policy and column indices / S values come from the
 // per-unit copies (one instantiation with, one without: no branch per load).
-template <int CPL, bool EXACT, typename ET, bool HINT>
+// SLICED: the launch covers a 64-column slice of longer rows (args.row_stride apart) and may add to P.val.
+// The add-to-P.val path (a predicated load of the old value at the top of a step, used by the final multiply-add) is
+// also compiled into the HINT instantiations although only slices switch it on: measured on the Poisson-rows
+// configuration with two column panels, K = 32, 575 -> 525 us per launch with it (the load is never issued; it changes
+// how the compiler groups the step's gathers into waits), while the instantiations without panels lose 6 % with it
+// (power-law rows 569 -> 604 us) and therefore do not carry it.
+template <int CPL, bool EXACT, typename ET, bool HINT, bool SLICED = false>
 __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_MINB1 : SDDMM_ROWSEG_MINBN) sddmm_rowseg_kernel(const RowSegArgs args) {
     using chunk_t = typename ChunkOf<ET>::type;
     using areg_t = typename ChunkOf<ET>::areg;
@@ -92,7 +102,8 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
     const int gbase = lane & 24;      // first lane of the group
     const int grp = lane >> 3;        // which of the warp's 4 units
     const int nchunks = EXACT ? 8 * CPL : (args.K / ChunkOf<ET>::elems);
-    const uint32_t row_bytes = static_cast<uint32_t>(nchunks) * sizeof(chunk_t);
+    const uint32_t row_bytes = SLICED ? args.row_stride : static_cast<uint32_t>(nchunks) * sizeof(chunk_t);   // distance between rows
+    constexpr bool kAccumulates = HINT || SLICED;
     constexpr int QS = (CPL >= 2) ? 2 : 1;   // chunks gathered per nonzero per step
     // chunks of this lane that exist (K < 32 * CPL: the lane's last chunks lie past the row and are read as chunk 0, times zero)
     uint64_t pol_b = 0;
@@ -140,6 +151,8 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
         const int j = u_cur.x + gl;
         const bool valid = (gl <= (u_cur.y & 7)) && (4 * q + grp <= last_unit);
         const float s = s_own;
+        float p_old = 0.f;   // (a later K slice: what the earlier slices left, requested before the gathers)
+        if (kAccumulates && args.accumulate && valid) p_old = __ldcs(args.p_val + j);
 
         // ---- this lane's chunk(s) of the segment's A row ----
         areg_t areg[CPL];
@@ -194,7 +207,7 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
                 for (int qq = 0; qq < QS; ++qq) acc[i] = dot_chunk(areg[q0 + qq], unpack_chunk(bq[i][qq]), acc[i]);
         }
         const float dot = group8_transpose_reduce(acc, gl);   // lane gl: nonzero gl of the segment
-        if (valid) __stcs(args.p_val + j, dot * s);
+        if (valid) __stcs(args.p_val + j, kAccumulates ? fmaf(dot, s, p_old) : dot * s);
 
         q = q_next;
         if (q >= n_quads) break;   // warp-uniform

@@ -88,7 +88,7 @@ typedef struct sddmm_b200_plan_info {
     int32_t rowseg_units;          /* segments                                        */
     int32_t rowseg_panels;         /* column panels the segment list is ordered by (1: none) */
     int32_t rowseg_grid;
-    int32_t reserved0;
+    int32_t rowseg_passes;      /* launches of the row-segment kernel per run: K taken in slices of 64 columns (else 1, or 0) */
 } sddmm_b200_plan_info;
 
 /* ---- life cycle ---------------------------------------------------------
@@ -179,6 +179,8 @@ int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info);
  *   "b_fraction"    with column panels the gathers of B carry an L2 evict_last hint: share of the lines it applies to, (0, 1]
  *   "group_units"   0: rows with identical column lists run the warp-per-group kernel instead of shared segments
  *   "offset_tiles"  0: dense tiles only on the 64-grid, 1: always also look for half-full 64x64 windows at arbitrary offsets
+ *   "k_slices"      fp32 storage, K >= 128 and a multiple of 64: 1 = take K in slices of 64 columns (one launch each over the same
+ *                   segment list, adding to P.val; default when B is larger than four times the L2), 0 = never
  *   "dense_split3"  fp32-grade mode on dense tiles: 1 = operands through three shared-memory slots and two accumulators in
  *                   tensor memory (default for K >= 64), 0 = one A block + one B block like the other modes */
 int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value);

@@ -749,3 +749,30 @@ def test_fp32_grade_dense_tiles_three_slot_operands(oracle, K, variant):
     d.close()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("K,panels", [(128, 1), (192, 2), (256, 3)])
+@pytest.mark.parametrize("mode", ["fp32", "fp32_tc"])
+def test_k_in_slices_of_64_columns(oracle, K, panels, mode):
+    """Large K on the row-segment path: one launch per 64-column slice of K over the same segment list, every later slice
+    adding to P.val (what the planner does when B is far larger than L2); forced here on a small input, with and without
+    column panels, and run twice (the first slice of a run must overwrite what the previous run left)."""
+    d = Dataset(5, K, 0.01)
+    want = oracle.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    bound = oracle_lib.abs_dot_bound(oracle.coo_rows(d.M, d.row_ptr), d.col_idx, d.s_val, d.A, d.B)
+    with Engine(0, mode) as e:
+        e.set_knob("k_slices", 1)
+        e.set_knob("panels", panels)
+        e.upload_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        plan = e.plan()
+        assert plan["rowseg_passes"] == K // 64 and plan["rowseg_panels"] == panels
+        for _ in range(2):
+            e.run(); e.sync()
+            oracle_lib.assert_values_close(e.download(), want, bound, 1e-5, f"{mode} K={K} in {K // 64} slices, {panels} panels")
+    with Engine(0, mode) as e:   # and the whole rows at once agree with it
+        e.set_knob("k_slices", 0)
+        p1 = e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        assert e.plan()["rowseg_passes"] == 1
+    oracle_lib.assert_values_close(p1, want, bound, 1e-5, f"{mode} K={K} whole rows")
+    d.close()
+
+
