@@ -130,8 +130,8 @@ struct sddmm_b200_engine {
 
     // row-segment path (short and power-law rows; column panels when B is much larger than L2)
     int2 *d_units = nullptr;
-    int32_t *d_unit_cols = nullptr;    // column panels: per-unit copies of column indices and S values (8 slots per unit)
-    float *d_unit_sval = nullptr;
+    int32_t *d_unit_cols = nullptr;    // column panels: per-unit copies of column indices and S values, 8 slots of {column, value} per unit
+    float *d_unit_sval = nullptr;      // (the same array: the values are its odd words)
     bool seg_copies = false;           // ... in use by the current plan
     int32_t *d_unit_off = nullptr;     // per (panel, row): units before it (scan of the counts)
     int32_t *d_scan_tiles = nullptr;
@@ -334,8 +334,7 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     e->unit_cap = static_cast<int64_t>(nnz / 8 + runs + 8);
     const size_t scan_n = M * static_cast<size_t>(e->panels);
     const size_t o_units = c.take(static_cast<size_t>(e->unit_cap) * sizeof(int4));   // (row groups use 16-byte headers)
-    const size_t o_ucols = e->panels > 1 ? c.take(static_cast<size_t>(e->unit_cap) * 32) : 0;
-    const size_t o_usval = e->panels > 1 ? c.take(static_cast<size_t>(e->unit_cap) * 32) : 0;
+    const size_t o_ucols = e->panels > 1 ? c.take(static_cast<size_t>(e->unit_cap) * 64) : 0;
     const size_t o_uoff = c.take((scan_n + 1) * 4);
     const size_t o_stile = c.take((scan_n / kScanTile + 2) * 4);
     // dense-tile path: only carved when the mode, K and the size of the 64x64 tile grid allow it
@@ -381,7 +380,7 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     e->d_Bx = split ? reinterpret_cast<float *>(b + o_bx) : nullptr;
     e->d_units = reinterpret_cast<int2 *>(b + o_units);
     e->d_unit_cols = e->panels > 1 ? reinterpret_cast<int32_t *>(b + o_ucols) : nullptr;
-    e->d_unit_sval = e->panels > 1 ? reinterpret_cast<float *>(b + o_usval) : nullptr;
+    e->d_unit_sval = e->panels > 1 ? reinterpret_cast<float *>(b + o_ucols) : nullptr;
     e->d_unit_off = reinterpret_cast<int32_t *>(b + o_uoff);
     e->d_scan_tiles = reinterpret_cast<int32_t *>(b + o_stile);
     e->d_rp = reinterpret_cast<int32_t *>(b + o_rp);

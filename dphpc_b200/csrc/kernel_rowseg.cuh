@@ -43,9 +43,10 @@ struct RowSegArgs {
     int32_t K;
     int32_t b_evict_last;     // B gathers ask L2 to keep their lines (column panels)
     float b_fraction;         // share of the B lines the hint applies to (1 = all)
-    // column panels: copies of the units' column indices and S values, 8 slots per unit in list order (slots past the
-    // segment's end repeat its last nonzero).  A panel run is a short piece of its row, so reading col_idx / S.val in
-    // place would touch one or two 32-byte sectors of a 128-byte line per unit; the copies are read front to back.
+    // column panels: copies of the units' column indices and S values, 8 slots of {column, value} per unit in list order
+    // (slots past the segment's end repeat its last nonzero): one 8-byte load per lane.  A panel run is a short piece of its
+    // row, so reading col_idx / S.val in place would touch one or two 32-byte sectors of a 128-byte line per unit; the
+    // copies are read front to back.  unit_sval is the same array (the values are its odd words).
     const int32_t *unit_cols;
     const float *unit_sval;
     // K in slices (large K, B far larger than L2): the launch covers columns [k0, k0 + K) of rows that are row_stride bytes
@@ -133,18 +134,24 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
     auto unit_index = [&](int64_t qq) -> int64_t { const int64_t u = 4 * qq + grp; return u < last_unit ? u : last_unit; };
     auto load_unit = [&](int64_t qq) -> int2 { return __ldcs(args.units + unit_index(qq)); };
     auto own_slot = [&](const int2 &u) -> int { return u.x + min(gl, u.y & 7); };
-    // column index / S value of this lane's nonzero of the unit of quad qq (u: that unit's header, if already loaded)
-    auto own_col = [&](int64_t qq, const int2 &u) -> int {
-        return HINT ? __ldcs(args.unit_cols + 8 * unit_index(qq) + gl) : __ldcs(args.col_idx + own_slot(u));
-    };
-    auto own_val = [&](int64_t qq, const int2 &u) -> float {
-        return HINT ? __ldcs(args.unit_sval + 8 * unit_index(qq) + gl) : __ldcs(args.s_val + own_slot(u));
-    };
+    // column index / S value of this lane's nonzero of a unit, read in place (u: that unit's header)
+    auto own_col = [&](int64_t, const int2 &u) -> int { return __ldcs(args.col_idx + own_slot(u)); };
+    auto own_val = [&](int64_t, const int2 &u) -> float { return __ldcs(args.s_val + own_slot(u)); };
 
+    // (HINT: column index and S value of a slot lie side by side in the per-unit copies: one 8-byte load)
+    auto own_pair = [&](int64_t qq) -> int2 { return __ldcs(reinterpret_cast<const int2 *>(args.unit_cols) + 8 * unit_index(qq) + gl); };
     int2 u_cur = load_unit(q);
     int2 u_nxt = load_unit(q + n_warps);
-    int c_own = own_col(q, u_cur);
-    float s_own = own_val(q, u_cur);
+    int c_own;
+    float s_own;
+    if (HINT) {
+        const int2 cs = own_pair(q);
+        c_own = cs.x;
+        s_own = __int_as_float(cs.y);
+    } else {
+        c_own = own_col(q, u_cur);
+        s_own = own_val(q, u_cur);
+    }
 
     while (true) {
         const int row = u_cur.y >> 3;
@@ -185,8 +192,14 @@ __global__ void __launch_bounds__(kRowSegWarps * 32, (CPL == 1) ? SDDMM_ROWSEG_M
             }
         const int64_t q_next = q + n_warps;
         const int2 u_nxt2 = load_unit(q_next + n_warps);
-        c_own = own_col(q_next, u_nxt);
-        s_own = own_val(q_next, u_nxt);
+        if (HINT) {
+            const int2 cs = own_pair(q_next);
+            c_own = cs.x;
+            s_own = __int_as_float(cs.y);
+        } else {
+            c_own = own_col(q_next, u_nxt);
+            s_own = own_val(q_next, u_nxt);
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
@@ -416,16 +429,16 @@ __global__ void k_unit_fill(const int32_t *__restrict__ rp, const int32_t *__res
             units[off + u] = make_int2(first, i * 8 + (cnt - 1));
         }
         if (ucols)   // per-unit copies of the column indices (slots past the end of the run repeat its last column)
-            for (int32_t t = lane; t < 8 * n_units; t += 32) ucols[8 * static_cast<int64_t>(off) + t] = col[min(s + t, e - 1)];
+            for (int32_t t = lane; t < 8 * n_units; t += 32) ucols[2 * (8 * static_cast<int64_t>(off) + t)] = col[min(s + t, e - 1)];
     }
 }
 
 // per-unit copies of the S values (one thread per slot): refreshed whenever S.val changes
-__global__ void k_unit_values(const int2 *__restrict__ units, int32_t n_units, const float *__restrict__ s_val, float *__restrict__ usval) {
+__global__ void k_unit_values(const int2 *__restrict__ units, int32_t n_units, const float *__restrict__ s_val, float *__restrict__ usval) {   // usval: the {column, value} slots
     for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < 8 * static_cast<int64_t>(n_units);
          t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int2 u = units[t >> 3];
-        usval[t] = s_val[u.x + min(static_cast<int>(t & 7), u.y & 7)];
+        usval[2 * t + 1] = s_val[u.x + min(static_cast<int>(t & 7), u.y & 7)];
     }
 }
 
