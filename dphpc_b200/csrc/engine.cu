@@ -767,6 +767,7 @@ int build_residual_units(sddmm_b200_engine *e) {
     const int64_t n_quads = (static_cast<int64_t>(e->n_units) + 3) / 4;
     e->plan.rowseg_units = e->n_units;
     e->plan.rowseg_panels = 1;
+    e->plan.rowseg_passes = e->seg_slices;
     e->plan.rowseg_grid = static_cast<int32_t>(std::min<int64_t>((n_quads + kRowSegWarps - 1) / kRowSegWarps, static_cast<int64_t>(e->sm_count) * occ));
     return SDDMM_B200_OK;
 }

@@ -776,3 +776,21 @@ def test_k_in_slices_of_64_columns(oracle, K, panels, mode):
     d.close()
 
 
+@pytest.mark.gpu
+def test_k_slices_beside_dense_tiles(oracle):
+    """K in slices on what the dense tiles leave: the residual row segments run once per slice on the side stream and add to
+    their own nonzeros only, the tensor-core kernel writes the rest (fp32-grade mode, K = 128, blocks at arbitrary offsets)."""
+    d = Dataset(2, 128, 0.1, variant=1)
+    want = oracle.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    bound = oracle_lib.abs_dot_bound(oracle.coo_rows(d.M, d.row_ptr), d.col_idx, d.s_val, d.A, d.B)
+    with Engine(0, "fp32_tc") as e:
+        e.set_knob("k_slices", 1)
+        e.upload_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        plan = e.plan()
+        assert plan["dense_tiles"] > 0 and 0 < plan["dense_nnz"] < d.nnz
+        for _ in range(2):
+            e.run(); e.sync()
+            oracle_lib.assert_values_close(e.download(), want, bound, 1e-5, "fp32_tc K=128: dense tiles + sliced residual")
+    d.close()
+
+
