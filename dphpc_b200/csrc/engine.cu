@@ -138,13 +138,14 @@ struct sddmm_b200_engine {
     int64_t unit_cap = 0;
     int32_t panels = 1;                // column panels the unit list is ordered by
     int32_t panel_cols = 0;            // columns per panel
+    int32_t long_rows = 0;             // > 0: only rows of at least this many nonzeros are cut into panels, the others follow whole (as one more "panel")
     int32_t n_units = 0;
     bool use_seg = false;
     bool seg_residual = false;         // the row-segment kernel computes what the dense tiles left (units over the uncovered runs)
     int l2_bytes = 0;
     // tuning knobs (sddmm_b200_set_knob; defaults from the environment at create): < 0 = decide automatically
     double knob_panels = -1, knob_panel_mb = -1, knob_rowseg = -1, knob_b_fraction = -1, knob_group_units = -1,
-           knob_offset_tiles = -1, knob_dense_split3 = -1, knob_k_slices = -1;
+           knob_offset_tiles = -1, knob_dense_split3 = -1, knob_k_slices = -1, knob_long_rows = -1;
     bool rg_units = false;             // row groups run as shared segments (row-segment group kernel) instead of the warp-per-group kernel
 
     HostStager stager, stager2;   // pageable host memory goes through pinned ring buffers filled by a pool of host threads (one per stream)
@@ -288,13 +289,33 @@ int choose_k_slices(const sddmm_b200_engine *e) {
     const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
     if (e->knob_k_slices < 0 && static_cast<double>(e->N) * e->K * 4.0 <= 4.0 * l2) return 1;
     // slices pay through the column panels they make room for; rows too short for panels are better off read whole
-    // (power-law rows, mean length 14, K = 128: 2.04 ms whole against 2.12 ms in slices)
-    if (e->knob_k_slices < 0 && e->nnz / std::max<int64_t>(1, 8 * e->M) < 2) return 1;
+    // (power-law rows, mean length 14, K = 128: 2.04 ms whole against 2.12 ms in slices) -- unless the long rows get panels
+    if (e->knob_k_slices < 0 && e->nnz / std::max<int64_t>(1, 8 * e->M) < 2 && e->knob_long_rows == 0) return 1;
     return static_cast<int>(e->K / 64);
+}
+
+// Rows too short for column panels on average, but B far larger than L2 (power-law row lengths: a few percent of the rows
+// hold most of the nonzeros): column panels for the rows of at least `long_rows` nonzeros only, the shorter rows follow
+// whole as one more entry of the panel-major list.  Returns the candidate threshold (0: not a candidate); e->panels is
+// then the number of real panels.  The plan confirms it once the row-length statistics are known (build_rowseg_plan).
+// Knob "long_rows": 0 = never, T >= 1 = threshold T with the panels the "panels" knob or the rule below gives.
+bool long_rows_candidate(const sddmm_b200_engine *e) {
+    if (e->knob_long_rows == 0 || e->mode == SDDMM_B200_BF16) return false;
+    const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
+    return static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) * 4.0 > l2 && e->nnz / std::max<int64_t>(1, 8 * e->M) < 2;
+}
+int choose_long_rows(const sddmm_b200_engine *e) {
+    if (e->knob_long_rows >= 1) return e->panels > 1 ? static_cast<int>(e->knob_long_rows) : 0;
+    if (!long_rows_candidate(e) || e->panels < 2) return 0;
+    return e->panels <= 4 ? 64 : 128;    // runs of 16 nonzeros or more on average (powers of two: the histogram's bins)
 }
 
 int choose_panels(const sddmm_b200_engine *e) {
     if (e->knob_panels >= 1 && e->knob_panels <= 64) return static_cast<int>(e->knob_panels);
+    if (long_rows_candidate(e)) {   // measured on the power-law configuration (B 333 MB): 4 panels 458 us, 6 446 us, 8 442-447 us
+        const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
+        return static_cast<int>(std::max(2.0, std::min(8.0, std::ceil(static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) * 4.0 / (0.5 * l2)))));
+    }
     const double eb = static_cast<double>(elem_bytes(e));
     const double b_bytes = static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) * eb;
     const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
@@ -332,8 +353,14 @@ int carve_arena(sddmm_b200_engine *e, bool coo, int n_items) {
     // row-segment path: unit list (upper bound: one unit per 8 nonzeros plus one ragged unit per row and panel), scan scratch
     e->seg_slices = choose_k_slices(e);
     e->panels = choose_panels(e);
+    e->long_rows = choose_long_rows(e);              // > 0: e->panels column panels for the long rows (still to be confirmed by the row statistics)
     e->panel_cols = static_cast<int32_t>((N + e->panels - 1) / e->panels);
-    const size_t runs = std::min(M * static_cast<size_t>(e->panels), nnz);
+    size_t runs = std::min(M * static_cast<size_t>(e->panels), nnz);
+    if (e->long_rows > 0) {
+        // a run per short row, and per panel for at most nnz / long_rows long rows
+        runs = std::min(M + std::min(nnz / static_cast<size_t>(e->long_rows), M) * static_cast<size_t>(e->panels), nnz);
+        e->panels += 1;                              // the short rows, whole, as the last entry of the list
+    }
     e->unit_cap = static_cast<int64_t>(nnz / 8 + runs + 8);
     const size_t scan_n = M * static_cast<size_t>(e->panels);
     const size_t o_units = c.take(static_cast<size_t>(e->unit_cap) * sizeof(int4));   // (row groups use 16-byte headers)
@@ -784,18 +811,30 @@ int build_rowseg_plan(sddmm_b200_engine *e, const PlanCounters &base_pc) {
     e->seg_copies = false;
     e->n_units = 0;
     if ((e->flags & SDDMM_B200_FLAG_NO_ROW_SEGMENTS) || seg_env == 0 || e->M >= kUnitRowLimit) return SDDMM_B200_OK;
-    const int32_t panels = base_pc.unsorted_cols ? 1 : e->panels;   // a panel run is a contiguous piece of a row only when its columns are sorted
+    int32_t panels = base_pc.unsorted_cols ? 1 : e->panels;   // a panel run is a contiguous piece of a row only when its columns are sorted
+    if (panels == 1) e->long_rows = 0;
+    if (e->long_rows > 0 && e->knob_long_rows < 0) {
+        // panels for the long rows only pay when those rows hold a good share of the nonzeros
+        unsigned long long in_long = 0;
+        for (int b = 0; b < SDDMM_B200_HIST_BINS; ++b)
+            if (b >= 1 && (1ll << (b - 1)) >= e->long_rows) in_long += base_pc.hist_nnz[b];
+        if (5 * in_long < 2 * static_cast<unsigned long long>(e->nnz)) {   // < 40 %: every row whole, one pass
+            e->long_rows = 0;
+            panels = 1;
+            if (e->knob_k_slices < 0) e->seg_slices = 1;
+        }
+    }
     const int32_t M = static_cast<int32_t>(e->M);
     const int64_t n = static_cast<int64_t>(panels) * M;
     const int n_tiles = static_cast<int>((n + kScanTile - 1) / kScanTile);
     const int cap = e->sm_count * 32;
     cudaStream_t s = e->stream;
-    k_unit_count<<<grid_for(n, kBlock, cap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, panels, e->panel_cols, e->d_unit_off);
+    k_unit_count<<<grid_for(n, kBlock, cap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, panels, e->panel_cols, e->long_rows, e->d_unit_off);
     k_scan_tile_sums<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, n, e->d_scan_tiles);
     k_scan_sums<<<1, kScanBlock, 0, s>>>(e->d_scan_tiles, n_tiles, &e->d_pc->units);
     k_scan_apply<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, n, e->d_scan_tiles);
     e->seg_copies = panels > 1 && e->d_unit_cols != nullptr;
-    k_unit_fill<<<grid_for(n * 32, kBlock, cap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, panels, e->panel_cols, e->d_unit_off, e->d_units,
+    k_unit_fill<<<grid_for(n * 32, kBlock, cap), kBlock, 0, s>>>(e->d_rp, e->d_col, M, panels, e->panel_cols, e->long_rows, e->d_unit_off, e->d_units,
                                                                   e->seg_copies ? e->d_unit_cols : nullptr);
     CU_TRY(e, cudaGetLastError());
     PlanCounters pc;
@@ -1172,6 +1211,7 @@ int sddmm_b200_create(sddmm_b200_engine **out, int device, int mode, uint32_t fl
     e->knob_offset_tiles = env_double("SDDMM_B200_OFFSET_TILES", -1);
     e->knob_dense_split3 = env_double("SDDMM_B200_DENSE_SPLIT3", -1);
     e->knob_k_slices = env_double("SDDMM_B200_K_SLICES", -1);
+    e->knob_long_rows = env_double("SDDMM_B200_LONG_ROWS", -1);
     DeviceGuard g(device);
     bool ok = g.ok;
     ok = ok && cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -1522,7 +1562,7 @@ int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value) {
     struct { const char *name; double *slot; } knobs[] = {
         {"panels", &e->knob_panels}, {"panel_mb", &e->knob_panel_mb}, {"rowseg", &e->knob_rowseg},
         {"b_fraction", &e->knob_b_fraction}, {"group_units", &e->knob_group_units},
-        {"offset_tiles", &e->knob_offset_tiles}, {"dense_split3", &e->knob_dense_split3}, {"k_slices", &e->knob_k_slices},
+        {"offset_tiles", &e->knob_offset_tiles}, {"dense_split3", &e->knob_dense_split3}, {"k_slices", &e->knob_k_slices}, {"long_rows", &e->knob_long_rows},
     };
     for (auto &k : knobs)
         if (std::strcmp(name, k.name) == 0) {
@@ -1576,11 +1616,11 @@ int spmm_prepare(sddmm_b200_engine *e, int64_t K2) {
         const int n_tiles = static_cast<int>((e->M + kScanTile - 1) / kScanTile);
         const int capb = e->sm_count * 32;
         cudaStream_t s = e->stream;
-        k_unit_count<<<grid_for(e->M, kBlock, capb), kBlock, 0, s>>>(e->d_rp, e->d_col, Mi, 1, 0, e->d_unit_off);
+        k_unit_count<<<grid_for(e->M, kBlock, capb), kBlock, 0, s>>>(e->d_rp, e->d_col, Mi, 1, 0, 0, e->d_unit_off);
         k_scan_tile_sums<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
         k_scan_sums<<<1, kScanBlock, 0, s>>>(e->d_scan_tiles, n_tiles, &e->d_pc->units);
         k_scan_apply<<<n_tiles, kScanBlock, 0, s>>>(e->d_unit_off, e->M, e->d_scan_tiles);
-        k_unit_fill<<<grid_for(e->M * 32, kBlock, capb), kBlock, 0, s>>>(e->d_rp, e->d_col, Mi, 1, 0, e->d_unit_off, e->d_spmm_units, nullptr);
+        k_unit_fill<<<grid_for(e->M * 32, kBlock, capb), kBlock, 0, s>>>(e->d_rp, e->d_col, Mi, 1, 0, 0, e->d_unit_off, e->d_spmm_units, nullptr);
         CU_TRY(e, cudaGetLastError());
         PlanCounters pc;
         if (int rc = read_counters(e, &pc)) return rc;

@@ -378,13 +378,29 @@ __global__ void k_group_unit_fill(const int32_t *__restrict__ rp, int32_t M, int
 // ---- building the unit list (once per upload) -------------------------------------------
 // Run of row i inside column panel p: [s, e) in CSR positions.  One panel: the whole row.
 // Needs non-decreasing column indices inside a row when there is more than one panel.
+// long_rows > 0: only rows of at least that many nonzeros are cut into column panels (panels 0 .. panels-2, panel_cols
+// columns each); the shorter rows follow whole, as the last "panel" of the list -- a run of one or two nonzeros would
+// leave most of a segment's slots empty.
 __device__ __forceinline__ void panel_run(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t i, int32_t p,
-                                          int32_t panels, int32_t panel_cols, int32_t &s, int32_t &e) {
+                                          int32_t panels, int32_t panel_cols, int32_t long_rows, int32_t &s, int32_t &e) {
     const int32_t a = rp[i], b = rp[i + 1];
     if (panels == 1) {
         s = a;
         e = b;
         return;
+    }
+    if (long_rows > 0) {
+        const bool is_long = b - a >= long_rows;
+        if (p == panels - 1) {           // the short rows, whole
+            s = a;
+            e = is_long ? a : b;
+            return;
+        }
+        if (!is_long) {
+            s = e = a;
+            return;
+        }
+        --panels;                        // the real column panels
     }
     auto lower = [&](int64_t c) {   // first position whose column is >= c
         int32_t lo = a, hi = b;
@@ -400,27 +416,28 @@ __device__ __forceinline__ void panel_run(const int32_t *__restrict__ rp, const 
 
 // one thread per (panel, row), panel-major: number of units of that run
 __global__ void k_unit_count(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t panels,
-                             int32_t panel_cols, int32_t *__restrict__ counts) {
+                             int32_t panel_cols, int32_t long_rows, int32_t *__restrict__ counts) {
     const int64_t n = static_cast<int64_t>(panels) * M;
     for (int64_t qi = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; qi < n;
          qi += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int32_t p = static_cast<int32_t>(qi / M), i = static_cast<int32_t>(qi - static_cast<int64_t>(p) * M);
         int32_t s, e;
-        panel_run(rp, col, i, p, panels, panel_cols, s, e);
+        panel_run(rp, col, i, p, panels, panel_cols, long_rows, s, e);
         counts[qi] = (e - s + 7) >> 3;
     }
 }
 
 // one warp per (panel, row): write its units at the scanned offset
 __global__ void k_unit_fill(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, int32_t panels,
-                            int32_t panel_cols, const int32_t *__restrict__ offsets, int2 *__restrict__ units, int32_t *__restrict__ ucols) {
+                            int32_t panel_cols, int32_t long_rows, const int32_t *__restrict__ offsets, int2 *__restrict__ units,
+                            int32_t *__restrict__ ucols) {
     const int lane = threadIdx.x & 31;
     const int64_t n = static_cast<int64_t>(panels) * M;
     const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
     for (int64_t qi = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5; qi < n; qi += n_warps) {
         const int32_t p = static_cast<int32_t>(qi / M), i = static_cast<int32_t>(qi - static_cast<int64_t>(p) * M);
         int32_t s, e;
-        panel_run(rp, col, i, p, panels, panel_cols, s, e);
+        panel_run(rp, col, i, p, panels, panel_cols, long_rows, s, e);
         const int32_t n_units = (e - s + 7) >> 3;
         const int32_t off = offsets[qi];
         for (int32_t u = lane; u < n_units; u += 32) {

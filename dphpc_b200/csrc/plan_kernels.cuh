@@ -14,6 +14,7 @@ namespace sddmm {
 
 struct PlanCounters {
     unsigned long long hist[SDDMM_B200_HIST_BINS];
+    unsigned long long hist_nnz[SDDMM_B200_HIST_BINS];   // nonzeros held by the rows of each length bin
     unsigned long long rows_nonempty;
     unsigned long long cols_touched;
     unsigned long long dense_nnz;
@@ -44,9 +45,10 @@ __device__ __forceinline__ int len_bin(int len) {
 __global__ void k_row_stats(const int32_t *__restrict__ rp, int32_t M, int64_t nnz, uint32_t *__restrict__ row_start_bits,
                             PlanCounters *__restrict__ pc) {
     __shared__ unsigned int sh[SDDMM_B200_HIST_BINS];
+    __shared__ unsigned long long sh_nnz[SDDMM_B200_HIST_BINS];
     __shared__ unsigned int s_nonempty;
     __shared__ int s_max;
-    if (threadIdx.x < SDDMM_B200_HIST_BINS) sh[threadIdx.x] = 0;
+    if (threadIdx.x < SDDMM_B200_HIST_BINS) { sh[threadIdx.x] = 0; sh_nnz[threadIdx.x] = 0; }
     if (threadIdx.x == 0) { s_nonempty = 0; s_max = 0; }
     __syncthreads();
     const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
@@ -58,6 +60,7 @@ __global__ void k_row_stats(const int32_t *__restrict__ rp, int32_t M, int64_t n
         } else {
             atomicAdd(&sh[len_bin(len)], 1u);
             if (len > 0) {
+                atomicAdd(&sh_nnz[len_bin(len)], static_cast<unsigned long long>(len));
                 atomicAdd(&s_nonempty, 1u);
                 atomicMax(&s_max, len);
                 atomicOr(&row_start_bits[a >> 5], 1u << (a & 31));
@@ -67,7 +70,10 @@ __global__ void k_row_stats(const int32_t *__restrict__ rp, int32_t M, int64_t n
         if (i == M - 1 && b != nnz) pc->bad_row_ptr = 1;
     }
     __syncthreads();
-    if (threadIdx.x < SDDMM_B200_HIST_BINS && sh[threadIdx.x]) atomicAdd(&pc->hist[threadIdx.x], (unsigned long long)sh[threadIdx.x]);
+    if (threadIdx.x < SDDMM_B200_HIST_BINS && sh[threadIdx.x]) {
+        atomicAdd(&pc->hist[threadIdx.x], (unsigned long long)sh[threadIdx.x]);
+        if (sh_nnz[threadIdx.x]) atomicAdd(&pc->hist_nnz[threadIdx.x], sh_nnz[threadIdx.x]);
+    }
     if (threadIdx.x == 0) {
         if (s_nonempty) atomicAdd(&pc->rows_nonempty, (unsigned long long)s_nonempty);
         if (s_max) atomicMax(&pc->max_row_nnz, s_max);

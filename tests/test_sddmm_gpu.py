@@ -280,7 +280,7 @@ def full_compare(p, d, oracle, tol, what):
 
 @pytest.mark.parametrize("cfg,K,mode", [(2, 32, "fp32"), (2, 32, "fp32_tc"), (2, 32, "tf32"), (2, 32, "bf16"), (3, 64, "fp32"),
                                         (4, 32, "fp32"), (4, 32, "bf16"), (5, 32, "fp32"), (5, 32, "bf16"), (2, 64, "fp32_tc"),
-                                        (3, 32, "fp32_tc"), (5, 128, "bf16"), (5, 64, "fp32")])
+                                        (3, 32, "fp32_tc"), (5, 128, "bf16"), (5, 64, "fp32"), (5, 128, "fp32")])
 def test_full_size_all_nonzeros(engines, oracle, cfg, K, mode):
     d = Dataset(cfg, K, 1.0)
     e = engines[mode]
@@ -561,10 +561,17 @@ def test_pipeline_matches_oracle_and_engine(engines, oracle, cfg, scale, K, mode
         A2, B2 = rng.uniform(-1, 1, (d.M, K)).astype(np.float32), rng.uniform(-1, 1, (d.N, K)).astype(np.float32)
         p2 = np.full(d.s_val.size, np.nan, np.float32)
         pl.update_csr_raw(sv2, A2, B2, p2)
-    np.testing.assert_array_equal(p, p_again)
     p_ref = oracle.sddmm_csr(d.M, K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
     rows = oracle.coo_rows(d.M, d.row_ptr)
     bound = oracle_lib.abs_dot_bound(rows, d.col_idx, d.s_val, d.A, d.B)
+    if mode in ("tf32", "bf16"):
+        # Row ranges that do not start on the 64-row grid see the blocks at arbitrary offsets: overlapping 64x64 windows claim
+        # their nonzeros with atomics, and a window left with too few is dropped -- its nonzeros then take the fp32 path.
+        # Which of two overlapping windows loses can differ between two runs, so the reduced-precision modes repeat a result
+        # within their bar, not bit for bit.
+        oracle_lib.assert_values_close(p_again, p_ref, bound, TOL[mode], f"pipeline {mode} cfg{cfg}, second call")
+    else:
+        np.testing.assert_array_equal(p, p_again)
     oracle_lib.assert_values_close(p, p_ref, bound, TOL[mode], f"pipeline {mode} cfg{cfg}")
     oracle_lib.assert_values_close(p_coo, p_ref, bound, TOL[mode], f"pipeline coo {mode} cfg{cfg}")   # (its cuts may differ by a row)
     p_one = engines[mode].sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
@@ -791,6 +798,30 @@ def test_k_slices_beside_dense_tiles(oracle):
         for _ in range(2):
             e.run(); e.sync()
             oracle_lib.assert_values_close(e.download(), want, bound, 1e-5, "fp32_tc K=128: dense tiles + sliced residual")
+    d.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg,scale", [(4, 0.02), (5, 0.01)])
+@pytest.mark.parametrize("panels,threshold", [(2, 16), (3, 8), (4, 64)])
+def test_column_panels_for_the_long_rows_only(oracle, cfg, scale, panels, threshold):
+    """Power-law row lengths: the rows of at least `threshold` nonzeros are cut into column panels, the shorter rows follow
+    whole as one more entry of the panel-major segment list (what the planner does on the full-size power-law
+    configuration, where B is far larger than L2; forced here on small inputs, also on one whose rows are all alike)."""
+    d = Dataset(cfg, 32, scale)
+    want = oracle.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    bound = oracle_lib.abs_dot_bound(oracle.coo_rows(d.M, d.row_ptr), d.col_idx, d.s_val, d.A, d.B)
+    with Engine(0, "fp32") as e:
+        e.set_knob("panels", panels)
+        e.set_knob("long_rows", threshold)
+        p = e.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        plan = e.plan()
+        assert plan["rowseg_panels"] == panels + 1 and plan["rowseg_nnz"] == d.nnz
+        e.update_values(d.s_val * 2.0)   # the per-unit copies of S follow the new values
+        e.run(); e.sync()
+        p2 = e.download()
+    oracle_lib.assert_values_close(p, want, bound, 1e-5, f"cfg{cfg}: {panels} panels for rows >= {threshold}")
+    oracle_lib.assert_values_close(p2, 2.0 * want, 2.0 * bound, 1e-5, f"cfg{cfg}: the same after update_values")
     d.close()
 
 
