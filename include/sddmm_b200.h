@@ -181,6 +181,9 @@ int sddmm_b200_get_plan(sddmm_b200_engine *e, sddmm_b200_plan_info *info);
  *   "offset_tiles"  0: dense tiles only on the 64-grid, 1: always also look for half-full 64x64 windows at arbitrary offsets
  *   "k_slices"      fp32 storage, K >= 128 and a multiple of 64: 1 = take K in slices of 64 columns (one launch each over the same
  *                   segment list, adding to P.val; default when B is larger than four times the L2), 0 = never
+ *   "long_rows"     rows too short for column panels on average but B far larger than L2: column panels for the rows of at
+ *                   least this many nonzeros only, the shorter rows follow whole (default: 64 or 128, chosen with the number
+ *                   of panels, when such rows hold at least 40 % of the nonzeros); 0 = never
  *   "dense_split3"  fp32-grade mode on dense tiles: 1 = operands through three shared-memory slots and two accumulators in
  *                   tensor memory (default for K >= 64), 0 = one A block + one B block like the other modes */
 int sddmm_b200_set_knob(sddmm_b200_engine *e, const char *name, double value);
