@@ -300,9 +300,10 @@ int choose_k_slices(const sddmm_b200_engine *e) {
 // then the number of real panels.  The plan confirms it once the row-length statistics are known (build_rowseg_plan).
 // Knob "long_rows": 0 = never, T >= 1 = threshold T with the panels the "panels" knob or the rule below gives.
 bool long_rows_candidate(const sddmm_b200_engine *e) {
-    if (e->knob_long_rows == 0 || e->mode == SDDMM_B200_BF16) return false;
+    if (e->knob_long_rows == 0) return false;
     const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
-    return static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) * 4.0 > l2 && e->nnz / std::max<int64_t>(1, 8 * e->M) < 2;
+    return static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) * static_cast<double>(elem_bytes(e)) > l2 &&
+           e->nnz / std::max<int64_t>(1, 8 * e->M) < 2;
 }
 int choose_long_rows(const sddmm_b200_engine *e) {
     if (e->knob_long_rows >= 1) return e->panels > 1 ? static_cast<int>(e->knob_long_rows) : 0;
@@ -314,7 +315,8 @@ int choose_panels(const sddmm_b200_engine *e) {
     if (e->knob_panels >= 1 && e->knob_panels <= 64) return static_cast<int>(e->knob_panels);
     if (long_rows_candidate(e)) {   // measured on the power-law configuration (B 333 MB): 4 panels 458 us, 6 446 us, 8 442-447 us
         const double l2 = e->l2_bytes > 0 ? e->l2_bytes : 96.0 * (1 << 20);
-        return static_cast<int>(std::max(2.0, std::min(8.0, std::ceil(static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) * 4.0 / (0.5 * l2)))));
+        return static_cast<int>(std::max(2.0, std::min(8.0, std::ceil(static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) *
+                                                                      static_cast<double>(elem_bytes(e)) / (0.5 * l2)))));
     }
     const double eb = static_cast<double>(elem_bytes(e));
     const double b_bytes = static_cast<double>(e->N) * (e->seg_slices > 1 ? 64 : e->K) * eb;
