@@ -86,7 +86,7 @@ typedef struct sddmm_b200_plan_info {
     /* row segments (rows cut into pieces of at most 8 nonzeros; the path for short and power-law rows) */
     int64_t rowseg_nnz;            /* nonzeros handled by the row-segment kernel      */
     int32_t rowseg_units;          /* segments                                        */
-    int32_t rowseg_panels;         /* column panels the segment list is ordered by (1: none) */
+    int32_t rowseg_panels;         /* column panels the segment list is ordered by (1: none); with panels for the long rows only, the short rows count as one more */
     int32_t rowseg_grid;
     int32_t rowseg_passes;      /* launches of the row-segment kernel per run: K taken in slices of 64 columns (else 1, or 0) */
 } sddmm_b200_plan_info;
