@@ -6,9 +6,11 @@
     python bench.py --impl reference ...      (the reference's own CPU SDDMM on the host cores)
 
 One step = one SDDMM over the whole sparse matrix.  For N > 1 the matrix is cut into
-nnz-balanced row ranges (one per rank), A is row-sliced, B is broadcast once over NCCL
-before the timed region, and no collective runs inside a step (strong scaling: the
-total work is fixed).  Rank 0 prints one JSON line.
+blocks, one per rank (dphpc_b200.partition.block_grid): nnz-balanced row ranges and, when B is
+far larger than L2 and the rows are long enough, equal column ranges as well, so that each
+rank gathers from a slice of B that stays in its L2.  A is row-sliced, B is broadcast once
+over NCCL before the timed region, and no collective runs inside a step (strong scaling:
+the total work is fixed).  Rank 0 prints one JSON line.
 
   value     GFLOP/s = 2*nnz*K / t with all operands resident in HBM; t = mean device time of a
             step (CUDA events on the engine's stream around its kernels), max over ranks;
@@ -234,9 +236,11 @@ class CpuRowShards:
             destroy()
 
 
-def workload_config(cfg, K, mode, world):
+def workload_config(cfg, K, mode, world, grid=None):
+    part = (f"{world} nnz-balanced row range(s), B replicated" if grid is None or grid[1] == 1 else
+            f"{grid[0]} nnz-balanced row range(s) x {grid[1]} equal column range(s): each rank one block with its rows of A and of B")
     return {"workload": f"{CONFIG_NAME[cfg]}, K={K}, A/B uniform [-1,1), seeded synthetic", "config_id": cfg, "k": K,
-            "mode": mode, "partition": f"{world} nnz-balanced row range(s), B replicated", "l2": "flushed between steps (512 MiB write)"}
+            "mode": mode, "partition": part, "l2": "flushed between steps (512 MiB write)"}
 
 
 def run_reference_arm(args, rank, world):
@@ -261,11 +265,13 @@ def run_reference_arm(args, rank, world):
     destroy()
     tm = float(np.mean(ts))
     val = 2.0 * nnz_s * K / tm / 1e9
+    from dphpc_b200.partition import block_grid
+    ref_grid = block_grid(max(1, args.gpus), d.M, d.N, K, d.nnz, elem_bytes=2 if args.mode == "bf16" else 4)
     line = {
         "impl": "reference", "metric": "SDDMM GFLOP/s (2*nnz*K/t)", "value": val, "unit": "GFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": tm * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(cfg, K, args.mode, max(1, args.gpus)),   # the same workload description as the GPU arm prints
+        "config": workload_config(cfg, K, args.mode, max(1, args.gpus), ref_grid),   # the same workload description as the GPU arm prints
         "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": shards.threads, "kind": shards.kind,
                          "sample": f"each step = CPUBasic::run_csr over rows [0,{r_end}) = {nnz_s} of {d.nnz} nnz, cut into "
                                    f"{shards.threads} nnz-balanced row ranges that run concurrently (one host thread each)",
@@ -295,14 +301,13 @@ def kernel_only_stats(eng, steps, warmup, flush):
     return float(np.median(tot)), {k: float(np.mean(v)) for k, v in per.items()}
 
 
-def shard_of(d, rank, world):
-    """This rank's nnz-balanced row range of a dataset (64-row aligned cuts keep the global tile grid)."""
-    from dphpc_b200.partition import row_cuts
-    cuts = row_cuts(d.row_ptr, world, align=64 if d.M >= 64 * 8 * world else 1)
-    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
-    j0, j1 = int(d.row_ptr[r0]), int(d.row_ptr[r1])
-    rp = (d.row_ptr[r0:r1 + 1].astype(np.int64) - j0).astype(np.int32)
-    return {"r0": r0, "r1": r1, "j0": j0, "j1": j1, "rp": rp, "M": r1 - r0, "nnz": j1 - j0}
+def shard_of(d, rank, world, mode="fp32"):
+    """This rank's block of a dataset as a problem of its own (dphpc_b200.partition.block_shard): nnz-balanced row ranges
+    (64-row aligned cuts keep the global tile grid) and, where B is far larger than L2 and the rows are long enough, equal
+    column ranges as well, so that every device gathers from a slice of B that stays in its L2."""
+    from dphpc_b200.partition import block_grid, block_shard
+    grid = block_grid(world, d.M, d.N, d.K, d.nnz, elem_bytes=2 if mode == "bf16" else 4)
+    return block_shard(d.row_ptr, d.col_idx, d.s_val, d.A, d.B, rank, grid, align=64 if d.M >= 64 * 8 * grid[0] else 1)
 
 
 def dominant_kernel(kern, plan):
@@ -343,34 +348,36 @@ def roofline_block(eng, plan, kern, mode, K, cfg, world, peak, peak_src):
     return out
 
 
-def parity_sample(p, d, sh, mode, sample=200000, edge_rows=2000):
-    """Outside the timed region: this rank's downloaded P shard against the CPU oracle -- `sample` random nonzeros plus the
-    first and last `edge_rows` rows of the shard.  Returns (checked nonzeros, max |err| / (tol * |s| sum|ab|))."""
+def parity_sample(p, sh, K, mode, sample=200000, edge_rows=2000):
+    """Outside the timed region: this rank's downloaded P block against the CPU oracle -- `sample` random nonzeros plus the
+    first and last `edge_rows` rows of the block (the block is a problem of its own: local row_ptr, re-based columns, its
+    rows of A and of B).  Returns (checked nonzeros, max |err| / (tol * |s| sum|ab|))."""
     import oracle_lib
     tol = 1e-5 if mode in ("fp32", "fp32_tc") else 1e-2
     orc = oracle_lib.Oracle()
-    r0, r1, j0, nnz = sh["r0"], sh["r1"], sh["j0"], sh["nnz"]
+    M, nnz = sh["M"], sh["nnz"]
     if nnz == 0:
         return 0, 0.0
-    A, B = np.ascontiguousarray(d.A), np.ascontiguousarray(d.B)
+    rp, col, val = np.ascontiguousarray(sh["rp"]), np.ascontiguousarray(sh["col"]), np.ascontiguousarray(sh["val"])
+    A, B = np.ascontiguousarray(sh["A"]), np.ascontiguousarray(sh["B"])
     worst, checked = 0.0, 0
-    for a, b in {(r0, min(r1, r0 + edge_rows)), (max(r0, r1 - edge_rows), r1)}:
-        ja, jb = int(d.row_ptr[a]), int(d.row_ptr[b])
+    for a, b in {(0, min(M, edge_rows)), (max(0, M - edge_rows), M)}:
+        ja, jb = int(rp[a]), int(rp[b])
         if jb <= ja:
             continue
-        ref = np.zeros(d.nnz, np.float32)
-        orc.sddmm_csr_rows(a, b, d.K, d.row_ptr, d.col_idx, d.s_val, A, B, ref)
-        rows = np.repeat(np.arange(a, b), np.diff(d.row_ptr[a:b + 1]))
-        bound = oracle_lib.abs_dot_bound(rows, d.col_idx[ja:jb], d.s_val[ja:jb], A, B)
-        err = np.abs(p[ja - j0:jb - j0].astype(np.float64) - ref[ja:jb])
+        ref = np.zeros(nnz, np.float32)
+        orc.sddmm_csr_rows(a, b, K, rp, col, val, A, B, ref)
+        rows = np.repeat(np.arange(a, b), np.diff(rp[a:b + 1]))
+        bound = oracle_lib.abs_dot_bound(rows, col[ja:jb], val[ja:jb], A, B)
+        err = np.abs(p[ja:jb].astype(np.float64) - ref[ja:jb])
         worst = max(worst, float(np.max(err / (tol * bound + 1e-30))))
         checked += jb - ja
-    rng = np.random.default_rng(1234 + r0)
-    idx = np.sort(rng.choice(nnz, min(sample, nnz), replace=False)) + j0
-    rows = (np.searchsorted(d.row_ptr, idx, side="right") - 1).astype(np.int64)
-    want = oracle_lib.dot_f64(rows, d.col_idx[idx], d.s_val[idx], A, B)
-    bound = oracle_lib.abs_dot_bound(rows, d.col_idx[idx], d.s_val[idx], A, B)
-    err = np.abs(p[idx - j0].astype(np.float64) - want)
+    rng = np.random.default_rng(1234 + sh["r0"] + 7 * sh["c0"])
+    idx = np.sort(rng.choice(nnz, min(sample, nnz), replace=False))
+    rows = (np.searchsorted(rp, idx, side="right") - 1).astype(np.int64)
+    want = oracle_lib.dot_f64(rows, col[idx], val[idx], A, B)
+    bound = oracle_lib.abs_dot_bound(rows, col[idx], val[idx], A, B)
+    err = np.abs(p[idx].astype(np.float64) - want)
     worst = max(worst, float(np.max(err / (max(tol, 2e-6) * bound + 1e-30))))
     if not np.isfinite(p).all():
         worst = float("inf")
@@ -455,8 +462,8 @@ def main():
 
     cfg, K = args.config, args.k or CONFIG_K[args.config]
     d = Dataset(cfg, K, args.scale)
-    sh = shard_of(d, rank, world)
-    r0, r1, j0, j1, rp_local, Mloc, nnz_loc = sh["r0"], sh["r1"], sh["j0"], sh["j1"], sh["rp"], sh["M"], sh["nnz"]
+    sh = shard_of(d, rank, world, args.mode)
+    rp_local, Mloc, Nloc, nnz_loc, grid = sh["rp"], sh["M"], sh["N"], sh["nnz"], sh["grid"]
     if Mloc < 1:
         raise SystemExit(f"rank {rank}: empty row range; use fewer GPUs for this workload")
 
@@ -464,10 +471,10 @@ def main():
     eng = Engine(local, args.mode)
     # pinned host copies of this rank's shard (the buffers a host caller would own)
     h_rp, _ = pinned_copy(lib, rp_local)
-    h_ci, _ = pinned_copy(lib, d.col_idx[j0:j1])
-    h_sv, _ = pinned_copy(lib, d.s_val[j0:j1])
-    h_A, _ = pinned_copy(lib, d.A[r0:r1])
-    h_B, _ = pinned_copy(lib, d.B)
+    h_ci, _ = pinned_copy(lib, sh["col"])
+    h_sv, _ = pinned_copy(lib, sh["val"])
+    h_A, _ = pinned_copy(lib, sh["A"])
+    h_B, _ = pinned_copy(lib, sh["B"])
     h_P, p_view = pinned_copy(lib, np.zeros(max(nnz_loc, 1), np.float32))
 
     # ---- resident operands: B broadcast once over NCCL (N > 1), then a device-to-device upload
@@ -477,14 +484,16 @@ def main():
             tB.copy_(torch.from_numpy(np.ascontiguousarray(d.B)))
         dist.broadcast(tB, src=0)
         t_rp = torch.from_numpy(rp_local).cuda()
-        t_ci = torch.from_numpy(np.ascontiguousarray(d.col_idx[j0:j1])).cuda()
-        t_sv = torch.from_numpy(np.ascontiguousarray(d.s_val[j0:j1])).cuda()
-        t_A = torch.from_numpy(np.ascontiguousarray(d.A[r0:r1])).cuda()
+        t_ci = torch.from_numpy(np.ascontiguousarray(sh["col"])).cuda()
+        t_sv = torch.from_numpy(np.ascontiguousarray(sh["val"])).cuda()
+        t_A = torch.from_numpy(np.ascontiguousarray(sh["A"])).cuda()
         torch.cuda.synchronize()
-        eng.upload_csr_device(Mloc, d.N, K, nnz_loc, t_rp.data_ptr(), t_ci.data_ptr(), t_sv.data_ptr(), t_A.data_ptr(), tB.data_ptr())
+        # (a column block takes its rows of the broadcast B: a contiguous piece of it)
+        eng.upload_csr_device(Mloc, Nloc, K, nnz_loc, t_rp.data_ptr(), t_ci.data_ptr(), t_sv.data_ptr(), t_A.data_ptr(),
+                              tB.data_ptr() + 4 * K * sh["c0"])
         del t_rp, t_ci, t_sv, t_A, tB
     else:
-        eng.upload_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B)
+        eng.upload_csr_raw(Mloc, Nloc, K, h_rp, h_ci, h_sv, h_A, h_B)
     eng.nnz = nnz_loc
     plan = eng.plan()
 
@@ -550,7 +559,7 @@ def main():
         try:
             eng.run()
             p_shard = eng.download()
-            checked, worst = parity_sample(p_shard, d, sh, args.mode)
+            checked, worst = parity_sample(p_shard, sh, K, args.mode)
             del p_shard
         except Exception as ex:  # report, never hide (the collectives below still run on every rank)
             sys.stderr.write(f"rank {rank}: parity check failed to run: {ex}\n")
@@ -577,7 +586,7 @@ def main():
             return max_over_ranks(float(np.mean(ts)))
 
         def e2e_step():
-            eng.upload_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B)
+            eng.upload_csr_raw(Mloc, Nloc, K, h_rp, h_ci, h_sv, h_A, h_B)
             eng.run()
             eng.download_raw(h_P)
         t_e2e = timed(e2e_step, 2)
@@ -590,12 +599,12 @@ def main():
         t_reuse = timed(reuse_step, 1)
         # the one-call form of the same sequence: row chunks whose upload, plan + run and download overlap on the full-duplex host link
         pipe = Pipeline(local, args.mode, chunks=4)
-        t_pipe = timed(lambda: pipe.sddmm_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B, h_P), 2)
+        t_pipe = timed(lambda: pipe.sddmm_csr_raw(Mloc, Nloc, K, h_rp, h_ci, h_sv, h_A, h_B, h_P), 2)
         pipe_chunks = pipe.last_chunks()
         # ... and when the pattern stays: only the numbers travel, chunk by chunk
         t_pipe_reuse = timed(lambda: pipe.update_csr_raw(h_sv, h_A, h_B, h_P), 1)
         pipe.close()
-        h2d = 4 * (Mloc + 1) + 8 * nnz_loc + 4 * K * (Mloc + d.N)
+        h2d = 4 * (Mloc + 1) + 8 * nnz_loc + 4 * K * (Mloc + Nloc)
         e2e = {"value": flops / t_pipe / 1e9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(4 * nnz_loc),
                "ms_per_step": t_pipe * 1e3, "steps": n_e2e, "chunks": pipe_chunks,
                "what": "sddmm_b200_pipeline_sddmm_csr: pinned host S, A, B -> HBM, device-side validation + plan, run, P.val -> pinned host, "
@@ -603,7 +612,7 @@ def main():
                "single_engine": {"value": flops / t_e2e / 1e9, "unit": "GFLOP/s", "ms_per_step": t_e2e * 1e3,
                                  "what": "upload_csr + run + download on one engine, one phase after the other"},
                "pattern_reuse": {"value": flops / t_pipe_reuse / 1e9, "unit": "GFLOP/s", "ms_per_step": t_pipe_reuse * 1e3,
-                                 "h2d_bytes_per_step": int(4 * nnz_loc + 4 * K * (Mloc + d.N)), "d2h_bytes_per_step": int(4 * nnz_loc),
+                                 "h2d_bytes_per_step": int(4 * nnz_loc + 4 * K * (Mloc + Nloc)), "d2h_bytes_per_step": int(4 * nnz_loc),
                                  "what": "sddmm_b200_pipeline_update_csr (pinned host A, B, S.val -> HBM; pattern and plans kept; run; "
                                          "P.val -> pinned host; row chunks overlapped)",
                                  "single_engine": {"value": flops / t_reuse / 1e9, "unit": "GFLOP/s", "ms_per_step": t_reuse * 1e3,
@@ -613,7 +622,7 @@ def main():
             h_Y, _ = pinned_copy(lib, np.zeros((Mloc, K), np.float32))
 
             def fused_step():
-                eng.upload_csr_raw(Mloc, d.N, K, h_rp, h_ci, h_sv, h_A, h_B)
+                eng.upload_csr_raw(Mloc, Nloc, K, h_rp, h_ci, h_sv, h_A, h_B)
                 eng.run()
                 eng.spmm_raw(K, 0, h_Y)
             t_fused = timed(fused_step, 1)
@@ -638,7 +647,7 @@ def main():
             "metric": "SDDMM GFLOP/s (2*nnz*K/t)", "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": {"fp32": "f32", "fp32_tc": "f32 (tf32x3 on dense tiles)", "tf32": "tf32", "bf16": "bf16"}[args.mode],
-            "data": "synthetic", "config": workload_config(cfg, K, args.mode, world),
+            "data": "synthetic", "config": workload_config(cfg, K, args.mode, world, grid),
             "e2e": e2e, "gpu_launches": int(args.steps * (plan["n_kernels"] + max(0, plan.get("rowseg_passes", 1) - 1))), "roofline": roofline, "clocks": clocks,
             "wall_s_timed_region": wall, "per_rank": per_rank, "parity": parity,
             "plan": {k: plan[k] for k in ("nnz", "rows_nonempty", "cols_touched", "max_row_nnz", "rowtile_nnz", "rowtile_items",
@@ -669,11 +678,10 @@ def main():
                     cache[(c, k_c)] = d if (c, k_c) == (cfg, K) else Dataset(c, k_c, 1.0)
                 dd = cache[(c, k_c)]
                 nnz_c = int(dd.nnz)
-                s2 = shard_of(dd, rank, world)
+                s2 = shard_of(dd, rank, world, m)
                 if s2["M"] > 0 and s2["nnz"] > 0:
                     e2 = Engine(local, m)
-                    e2.upload_csr(s2["M"], dd.N, dd.K, s2["rp"], dd.col_idx[s2["j0"]:s2["j1"]], dd.s_val[s2["j0"]:s2["j1"]],
-                                  dd.A[s2["r0"]:s2["r1"]], dd.B)
+                    e2.upload_csr(s2["M"], s2["N"], dd.K, s2["rp"], s2["col"], s2["val"], s2["A"], s2["B"])
                 else:
                     ms_local = 0.0
             except Exception as ex:  # report, never hide (the collectives below still run on every rank)
@@ -703,7 +711,7 @@ def main():
                 else:
                     per[key] = {"ms": ms, "gflops": 2.0 * nnz_c * k_c / ms / 1e6, "gb_per_s": alg / ms / 1e6, "hbm_frac": alg / ms / 1e6 / (peak * world),
                                 "kernels_ms_rank0": kern_c, "kernel": dominant_kernel(kern_c, plan_c) if plan_c else None,
-                                "what": f"{world} nnz-balanced row shard(s), max over ranks; fraction = algorithmic bytes of all shards / time / "
+                                "what": f"{world} block(s) (nnz-balanced row ranges, column ranges where B is far larger than L2), max over ranks; fraction = algorithmic bytes of all blocks / time / "
                                         f"({world} x HBM peak)"}
         for dd_old in cache.values():
             if dd_old is not d:

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from dphpc_b200 import Dataset
-from dphpc_b200.partition import coo_cuts, row_cuts, shard
+from dphpc_b200.partition import block_grid, block_shard, coo_cuts, row_cuts, shard
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -64,6 +64,44 @@ def test_coo_cuts_find_row_boundaries_without_a_row_ptr(parts):
     assert c[[0, -1]].tolist() == [0, 4] and o.tolist() == [0, 0, 0]   # empty matrix
     with pytest.raises(ValueError):
         coo_cuts(np.array([0, 1, 2, 9, 3, 3], np.int32), 4, 2)          # the entry a cut looks at lies outside [0, M)
+
+
+def test_block_grid_cuts_columns_only_where_b_exceeds_l2_and_rows_are_long():
+    assert block_grid(8, 1453908, 1453908, 32, 37497844) == (2, 4)      # Poisson rows, B 186 MB: slices of 46 MB
+    assert block_grid(4, 1453908, 1453908, 32, 37497844) == (1, 4)
+    assert block_grid(2, 1453908, 1453908, 32, 37497844) == (1, 2)
+    assert block_grid(1, 1453908, 1453908, 32, 37497844) == (1, 1)
+    assert block_grid(8, 2601977, 2601977, 32, 36200056) == (8, 1)      # power-law rows, mean 14: row ranges (the engine cuts the long rows itself)
+    assert block_grid(8, 14340, 14340, 32, 18070000) == (8, 1)          # B fits L2
+    assert block_grid(8, 503712, 503712, 64, 36799047) == (8, 1)        # B about the size of L2
+    assert block_grid(8, 1453908, 1453908, 64, 37497844) == (2, 4)
+    assert block_grid(8, 1453908, 1453908, 128, 37497844) == (8, 1)     # rows of 512 bytes: A would be re-read once per column part
+    assert block_grid(8, 1453908, 1453908, 64, 37497844, elem_bytes=2) == (8, 1)   # bf16 storage
+
+
+@pytest.mark.parametrize("world,grid", [(4, (1, 4)), (8, (2, 4)), (2, (2, 1)), (6, (3, 2))])
+def test_blocks_of_a_grid_assemble_the_whole_result(world, grid):
+    """Every block is a problem of its own (local row_ptr, re-based columns, its rows of A and B); computing each with
+    the CPU oracle and writing the pieces back through `sel` gives the unsharded result bit for bit."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import oracle_lib
+    orc = oracle_lib.Oracle()
+    d = Dataset(5, 8, 0.02)
+    want = orc.sddmm_csr(d.M, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    got = np.full(d.nnz, np.nan, np.float32)
+    total = 0
+    for r in range(world):
+        b = block_shard(d.row_ptr, d.col_idx, d.s_val, d.A, d.B, r, grid)
+        assert b["rp"][0] == 0 and b["rp"][-1] == b["nnz"] == b["col"].size == b["val"].size
+        assert b["A"].shape[0] == b["M"] and b["B"].shape[0] == b["N"] == b["c1"] - b["c0"]
+        assert b["nnz"] == 0 or (0 <= b["col"].min() and b["col"].max() < b["N"])
+        p = orc.sddmm_csr(b["M"], d.K, b["rp"], b["col"], b["val"], np.ascontiguousarray(b["A"]), np.ascontiguousarray(b["B"]))
+        if b["sel"] is None:
+            got[b["j0"]:b["j1"]] = p
+        else:
+            got[b["sel"]] = p
+        total += b["nnz"]
+    assert total == d.nnz and np.array_equal(got, want)
 
 
 def test_shard_slices_rebase_row_ptr():
