@@ -76,6 +76,8 @@ def block_grid(world: int, M: int, N: int, K: int, nnz: int, elem_bytes: int = 4
     if elem_bytes == 4 and K * elem_bytes <= 256 and b_bytes > 1.25 * l2_bytes and mean_row >= 16:
         while cols * 2 <= min(world, 4) and b_bytes / cols > 0.5 * l2_bytes and mean_row / (2 * cols) >= 3:   # (measured up to 4 column parts)
             cols *= 2
+        if b_bytes / cols > l2_bytes:   # the slice would still not fit (2 GPUs, K = 64: 549 us with row ranges, 574 us with 1 x 2)
+            cols = 1
     return world // cols, cols
 
 

@@ -75,6 +75,7 @@ def test_block_grid_cuts_columns_only_where_b_exceeds_l2_and_rows_are_long():
     assert block_grid(8, 14340, 14340, 32, 18070000) == (8, 1)          # B fits L2
     assert block_grid(8, 503712, 503712, 64, 36799047) == (8, 1)        # B about the size of L2
     assert block_grid(8, 1453908, 1453908, 64, 37497844) == (2, 4)
+    assert block_grid(2, 1453908, 1453908, 64, 37497844) == (2, 1)      # a half of B (186 MB) would still not fit L2
     assert block_grid(8, 1453908, 1453908, 128, 37497844) == (8, 1)     # rows of 512 bytes: A would be re-read once per column part
     assert block_grid(8, 1453908, 1453908, 64, 37497844, elem_bytes=2) == (8, 1)   # bf16 storage
 
