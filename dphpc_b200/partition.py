@@ -70,6 +70,12 @@ def block_grid(world: int, M: int, N: int, K: int, nnz: int, elem_bytes: int = 4
     rows of A and B longer than 256 bytes, where re-reading A once per column part costs more than the gathers save, and
     bf16 storage, whose kernels are bound by their arithmetic (measured on 4 GPUs, Poisson rows: fp32 K = 32 145 -> 131 us,
     K = 64 285 -> 258 us per step, but K = 128 584 -> 616 us, bf16 K = 64 190 -> 196 us)."""
+    import os
+    forced = os.environ.get("SDDMM_B200_GRID")   # "RxC": experiments with other grids
+    if forced:
+        r, c = (int(v) for v in forced.lower().split("x"))
+        if r * c == world:
+            return r, c
     mean_row = nnz / max(1, M)
     b_bytes = N * K * elem_bytes
     cols = 1
