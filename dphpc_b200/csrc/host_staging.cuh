@@ -11,9 +11,13 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#if defined(__SSE2__)
+#include <emmintrin.h>
+#endif
 #include <atomic>
 #include <condition_variable>
 #include <cstdlib>
+#include <cstdint>
 #include <cstring>
 #include <functional>
 #include <mutex>
@@ -107,18 +111,49 @@ private:
     bool stop_ = false;
 };
 
-inline void parallel_memcpy(void *dst, const void *src, size_t bytes) {
+// memcpy whose stores bypass the cache (x86): the destination is a pinned staging buffer that the DMA engine reads next,
+// no host thread does, so write-allocating its lines would only add a read of memory per line written.
+// SDDMM_B200_STREAM_STORES=0 switches back to plain memcpy.
+inline void stream_copy(void *dst, const void *src, size_t bytes) {
+#if defined(__SSE2__)
+    static const bool enabled = [] { const char *e = std::getenv("SDDMM_B200_STREAM_STORES"); return !(e && e[0] == '0'); }();
+    char *d = static_cast<char *>(dst);
+    const char *s = static_cast<const char *>(src);
+    if (enabled && bytes >= 4096 && (reinterpret_cast<uintptr_t>(d) & 15) == 0) {
+        size_t n = bytes / 64;
+        for (; n; --n, d += 64, s += 64) {
+            const __m128i a = _mm_loadu_si128(reinterpret_cast<const __m128i *>(s));
+            const __m128i b = _mm_loadu_si128(reinterpret_cast<const __m128i *>(s + 16));
+            const __m128i c = _mm_loadu_si128(reinterpret_cast<const __m128i *>(s + 32));
+            const __m128i e = _mm_loadu_si128(reinterpret_cast<const __m128i *>(s + 48));
+            _mm_stream_si128(reinterpret_cast<__m128i *>(d), a);
+            _mm_stream_si128(reinterpret_cast<__m128i *>(d + 16), b);
+            _mm_stream_si128(reinterpret_cast<__m128i *>(d + 32), c);
+            _mm_stream_si128(reinterpret_cast<__m128i *>(d + 48), e);
+        }
+        _mm_sfence();
+        bytes &= 63;
+    }
+    if (bytes) std::memcpy(d, s, bytes);
+#else
+    std::memcpy(dst, src, bytes);
+#endif
+}
+
+inline void parallel_memcpy(void *dst, const void *src, size_t bytes, bool stream_stores = false) {
     HostPool &pool = HostPool::instance();
     const int parts = static_cast<int>(std::min<size_t>(pool.width(), std::max<size_t>(1, bytes >> 20)));   // >= 1 MiB per slice
     if (parts <= 1) {
-        std::memcpy(dst, src, bytes);
+        if (stream_stores) stream_copy(dst, src, bytes); else std::memcpy(dst, src, bytes);
         return;
     }
     const size_t per = (bytes / parts + 4095) & ~size_t(4095);
     pool.run(parts, [&](int k) {
         const size_t off = std::min(bytes, per * static_cast<size_t>(k));
         const size_t len = std::min(per, bytes - off);
-        if (len) std::memcpy(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, len);
+        if (!len) return;
+        if (stream_stores) stream_copy(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, len);
+        else std::memcpy(static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, len);
     });
 }
 
@@ -180,7 +215,7 @@ struct HostStager {
                 const cudaError_t st = cudaEventSynchronize(ev[b]);
                 if (st != cudaSuccess) return st;
             }
-            parallel_memcpy(buf[b], static_cast<const char *>(src) + off, len);
+            parallel_memcpy(buf[b], static_cast<const char *>(src) + off, len, /*stream_stores=*/true);
             cudaError_t st = cudaMemcpyAsync(static_cast<char *>(dst) + off, buf[b], len, cudaMemcpyHostToDevice, stream);
             if (st == cudaSuccess) st = cudaEventRecord(ev[b], stream);
             if (st != cudaSuccess) return st;
