@@ -825,3 +825,21 @@ def test_column_panels_for_the_long_rows_only(oracle, cfg, scale, panels, thresh
     d.close()
 
 
+@pytest.mark.gpu
+def test_full_size_chunked_call_on_power_law_rows(engines, oracle):
+    """The chunked host-to-host call on the full-size power-law configuration: every row range plans for itself (column
+    panels for its long rows only) and the whole result still equals the one-engine result bit for bit and the oracle within
+    the fp32 bar, the COO form included."""
+    d = Dataset(4, 32, 1.0)
+    with Pipeline(0, "fp32", chunks=4) as pl:
+        p = pl.sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+        assert pl.last_chunks() == 4
+        p_coo = pl.sddmm_coo(d.M, d.N, d.K, d.row_idx(), d.col_idx, d.s_val, d.A, d.B)
+    full_compare(p, d, oracle, TOL["fp32"], "chunked call, power-law rows, full size")
+    p_one = engines["fp32"].sddmm_csr(d.M, d.N, d.K, d.row_ptr, d.col_idx, d.s_val, d.A, d.B)
+    assert engines["fp32"].plan()["rowseg_panels"] > 1   # (the long-row panels are in use on the whole matrix)
+    np.testing.assert_array_equal(p, p_one)
+    np.testing.assert_array_equal(p_coo, p_one)
+    d.close()
+
+
