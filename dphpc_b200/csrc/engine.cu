@@ -572,9 +572,16 @@ int build_dense_plan(sddmm_b200_engine *e, const PlanCounters &base_pc, int item
     auto describe = [&]() -> int {
         CU_TRY(e, cudaMemsetAsync(&e->d_pc->dense_nnz, 0, sizeof(unsigned long long), s));
         CU_TRY(e, cudaMemsetAsync(e->d_anchor_counts, 0, static_cast<size_t>(n_dense) * 4, s));
+        // overlapping tiles: one owner key per nonzero, kept in P.val's storage (unused until the first run)
+        uint32_t *owner = offsets_used ? reinterpret_cast<uint32_t *>(e->d_pval) : nullptr;
+        if (owner) {
+            CU_TRY(e, cudaMemsetAsync(owner, 0xFF, static_cast<size_t>(e->nnz) * 4, s));
+            k_tile_propose<<<grid_for(static_cast<int64_t>(n_dense) * 64, kBlock, 1 << 30), kBlock, 0, s>>>(e->d_rp, e->d_col, M, e->dense_origin,
+                                                                                                             n_dense, owner);
+        }
         k_tile_rows<DenseTileDesc><<<grid_for(static_cast<int64_t>(n_dense) * 64, kBlock, 1 << 30), kBlock, 0, s>>>(
             e->d_rp, e->d_col, M, e->dense_origin, n_dense, e->d_dense_descs, e->d_covered, item_nnz, e->d_item_covered, e->d_anchor_counts,
-            e->d_pc);
+            e->d_pc, owner);
         return cuda_status(e, cudaGetLastError());
     };
     if (int rc = describe()) return rc;

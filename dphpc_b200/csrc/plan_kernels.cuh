@@ -278,13 +278,35 @@ __global__ void k_anchor_select(const int2 *__restrict__ anchors, const int32_t 
     }
 }
 
+// Overlapping tiles (windows at arbitrary offsets): who computes a nonzero that lies in several of them is decided by a
+// key, not by a race -- every (tile, row) proposes (row offset << 6 | column offset) for each of its nonzeros, the
+// smallest key wins (two tiles that hold the same nonzero differ in their origin, hence in the key), so the same matrix
+// always gets the same owners and the same tiles survive k_tile_keep.  owner: one word per nonzero, preset to ~0.
+__global__ void k_tile_propose(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, const int2 *__restrict__ origins,
+                               int32_t n_dense, uint32_t *__restrict__ owner) {
+    const int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (g >= static_cast<int64_t>(n_dense) * 64) return;
+    const int t = static_cast<int>(g >> 6), r = static_cast<int>(g & 63);
+    const int2 o = origins[t];
+    const int row = o.x + r;
+    if (row >= M) return;
+    const int end = rp[row + 1];
+    for (int j = lower_col(col, rp[row], end, o.y); j < end; ++j) {
+        const int c = col[j] - o.y;
+        if (c >= 64) break;
+        atomicMin(&owner[j], (static_cast<uint32_t>(r) << 6) | static_cast<uint32_t>(c));
+    }
+}
+
 // one thread per (dense tile, row): first CSR position of the row inside the tile's column range, presence mask of its 64
-// columns, and the OWN mask -- the nonzeros this tile computes.  Tiles at arbitrary offsets may overlap: a nonzero belongs
-// to the tile that claims its bit in the `covered` bitmap first.  Owned nonzeros are credited to their work items.
+// columns, and the OWN mask -- the nonzeros this tile computes.  Tiles on the 64-grid never overlap (owner == nullptr: a
+// nonzero is claimed in the `covered` bitmap and every claim succeeds); overlapping tiles own what k_tile_propose gave
+// them.  Owned nonzeros are credited to their work items.
 template <typename Desc>
 __global__ void k_tile_rows(const int32_t *__restrict__ rp, const int32_t *__restrict__ col, int32_t M, const int2 *__restrict__ origins,
                             int32_t n_dense, Desc *__restrict__ descs, uint32_t *__restrict__ covered, int32_t item_nnz,
-                            int32_t *__restrict__ item_covered, int32_t *__restrict__ tile_owned, PlanCounters *__restrict__ pc) {
+                            int32_t *__restrict__ item_covered, int32_t *__restrict__ tile_owned, PlanCounters *__restrict__ pc,
+                            const uint32_t *__restrict__ owner) {
     const int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (g >= static_cast<int64_t>(n_dense) * 64) return;
     const int t = static_cast<int>(g >> 6), r = static_cast<int>(g & 63);
@@ -303,14 +325,24 @@ __global__ void k_tile_rows(const int32_t *__restrict__ rp, const int32_t *__res
             mask |= 1ull << c;
             ++n;
         }
-        // claim [start, start + n) word by word; bit k of `got` = nonzero start + k is ours
+        // bit k of `got` = nonzero start + k is ours: by its key (overlapping tiles), else by claiming [start, start + n)
+        // in the bitmap word by word
         unsigned long long got = 0ull;
+        if (owner) {
+            for (int k = 0; k < n; ++k)
+                if (owner[start + k] == ((static_cast<uint32_t>(r) << 6) | static_cast<uint32_t>(col[start + k] - c0))) got |= 1ull << k;
+        }
         for (int j = start; j < start + n;) {
             const int w = j >> 5, first = j & 31;
             const int take = min(32 - first, start + n - j);
-            const uint32_t bits = (take == 32 ? 0xffffffffu : ((1u << take) - 1u)) << first;
-            const uint32_t old = atomicOr(&covered[w], bits);
-            got |= static_cast<unsigned long long>((bits & ~old) >> first) << (j - start);
+            uint32_t bits = (take == 32 ? 0xffffffffu : ((1u << take) - 1u)) << first;
+            if (owner) {
+                bits &= static_cast<uint32_t>(got >> (j - start)) << first;   // mark what is ours as covered
+                if (bits) atomicOr(&covered[w], bits);
+            } else {
+                const uint32_t old = atomicOr(&covered[w], bits);
+                got |= static_cast<unsigned long long>((bits & ~old) >> first) << (j - start);
+            }
             j += take;
         }
         // rank k of the run -> its column bit
