@@ -23,6 +23,18 @@ def compile_cpp(name, sources, extra=()):
     return exe
 
 
+def test_host_staging_cpp():
+    """Thread pool and copies of dphpc_b200/csrc/host_staging.cuh (host code only: compiled with g++ against the CUDA headers)."""
+    cuda_inc = Path("/usr/local/cuda/include")
+    if not (cuda_inc / "cuda_runtime.h").exists():
+        pytest.skip("CUDA headers not found")
+    exe = compile_cpp("host_staging_tests", [ROOT / "tests" / "cpp" / "host_staging_tests.cpp"],
+                      extra=["-x", "c++", "-I", str(ROOT / "dphpc_b200" / "csrc"), "-I", str(cuda_inc), "-msse2"])
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-4000:]
+    assert "0 failures" in res.stdout
+
+
 def test_containers_and_dispatcher_cpp():
     exe = compile_cpp("container_tests", [ROOT / "tests" / "cpp" / "container_tests.cpp"])
     res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
